@@ -1,0 +1,76 @@
+// Shared host/device helpers of libfrnnt_sm100.so.
+#pragma once
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "frnnt.h"
+
+namespace frnnt {
+
+// ---- host: error reporting --------------------------------------------------
+void set_error(const char *fmt, ...);
+
+#define FRNNT_REQUIRE(cond, code, ...)      \
+  do {                                      \
+    if (!(cond)) {                          \
+      ::frnnt::set_error(__VA_ARGS__);      \
+      return (code);                        \
+    }                                       \
+  } while (0)
+
+#define FRNNT_CUDA(call)                                                        \
+  do {                                                                          \
+    cudaError_t err__ = (call);                                                 \
+    if (err__ != cudaSuccess) {                                                 \
+      ::frnnt::set_error("%s failed: %s", #call, cudaGetErrorString(err__));    \
+      return FRNNT_ECUDA;                                                       \
+    }                                                                           \
+  } while (0)
+
+inline int check_dtype(int dtype) { return dtype == FRNNT_F32 || dtype == FRNNT_F64; }
+inline size_t dtype_size(int dtype) { return dtype == FRNNT_F64 ? 8 : 4; }
+
+// ---- device: math in the reference's operation order ------------------------
+template <typename real> __device__ __forceinline__ real neg_inf();
+template <> __device__ __forceinline__ float neg_inf<float>() { return -INFINITY; }
+template <> __device__ __forceinline__ double neg_inf<double>() { return -(double)INFINITY; }
+
+__device__ __forceinline__ float exp_r(float x) { return expf(x); }
+__device__ __forceinline__ double exp_r(double x) { return exp(x); }
+__device__ __forceinline__ float log1p_r(float x) { return log1pf(x); }
+__device__ __forceinline__ double log1p_r(double x) { return log1p(x); }
+__device__ __forceinline__ float log_r(float x) { return logf(x); }
+__device__ __forceinline__ double log_r(double x) { return log(x); }
+
+// log(exp(x) + exp(y)) with the guards of the reference's LogAdd
+// (fast_rnnt/csrc/mutual_information.h:36-65): when the difference is not
+// finite (an operand is -inf) the larger operand is returned unchanged.
+template <typename real>
+__device__ __forceinline__ real log_add(real x, real y) {
+  real diff;
+  if (x < y) {
+    diff = x - y;
+    x = y;
+  } else {
+    diff = y - x;
+  }
+  if (diff - diff != 0) return x;
+  return x + log1p_r(exp_r(diff));
+}
+
+template <typename T>
+__device__ __forceinline__ T warp_max(T v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = max(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+template <typename T>
+__device__ __forceinline__ T warp_sum(T v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+}  // namespace frnnt

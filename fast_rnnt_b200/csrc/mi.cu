@@ -1,0 +1,485 @@
+// Mutual-information recursion on sm_100a: anti-diagonal wavefront kernels.
+//
+// What is computed (semantics of the reference's CPU implementation,
+// fast_rnnt/csrc/mutual_information_cpu.cu:50-256):
+//   forward   p[s0][t0] = 0
+//             p[s][t]   = LogAdd(p[s-1][t+o] + px[s-1][t+o], p[s][t-1] + py[s][t-1])
+//             (o = 0 regular, -1 modified; out-of-range terms are -inf)
+//   backward  d1 = exp(p[s-1][t+o] + px[s-1][t+o] - p[s][t]),  d2 = 1 - d1
+//             px_grad[s-1][t+o] = d1 * g[s][t],  py_grad[s][t-1] = d2 * g[s][t]
+//             g[s][t] = (x-gradient arriving from row s+1) + (y-gradient from column t+1)
+//
+// How it is mapped to the GPU (not the reference's tile-per-launch scheme):
+//   * one CTA per utterance, ONE launch per sweep;
+//   * thread i owns lattice row s0+i; at step k all threads work on
+//     anti-diagonal k (cell (i, k-i)), so the "row above" value arrives by a
+//     warp shuffle and the "column before" value stays in a register;
+//   * the hand-off between the last lane of a warp and the first lane of the
+//     next goes through a 4-deep shared-memory slot and one named barrier per
+//     step among the compute warps only;
+//   * px / py are re-laid by dedicated loader warps into a skewed shared-memory
+//     ring (row i, diagonal k), 32 diagonals per chunk, double buffered: global
+//     reads are contiguous row segments, ring reads by the diagonal are
+//     bank-conflict free (pitch 33);
+//   * the forward sweep stores d1 for every cell in a diagonal-major scratch
+//     ("branch"), fully coalesced; the backward sweep then needs neither exp()
+//     nor p, and its dependent chain per step is shuffle + add + multiply;
+//   * gradients leave through the same kind of skewed ring, written back as
+//     contiguous row segments by the storer warps, which also write the exact
+//     zeros outside the boundary box.
+#include "common.cuh"
+
+namespace frnnt {
+
+constexpr int kChunk = 32;      // anti-diagonals staged per chunk
+constexpr int kPitch = 33;      // ring row pitch in elements
+constexpr int kIoWarps = 4;     // loader / storer warps per CTA
+constexpr int kMaxComputeWarps = 8;
+
+struct MiBox {
+  int s0, t0, sb, tb;  // origin and extents (s_end - s_begin, t_end - t_begin)
+};
+
+__device__ __forceinline__ MiBox load_box(const int64_t *boundary, int b, int S, int T) {
+  MiBox box{0, 0, S, T};
+  if (boundary != nullptr) {
+    // clamped so that a malformed row can never index outside the tensors
+    int s0 = (int)boundary[4 * b + 0], t0 = (int)boundary[4 * b + 1];
+    int s1 = (int)boundary[4 * b + 2], t1 = (int)boundary[4 * b + 3];
+    s0 = max(0, min(s0, S));
+    t0 = max(0, min(t0, T));
+    s1 = max(s0, min(s1, S));
+    t1 = max(t0, min(t1, T));
+    box = MiBox{s0, t0, s1 - s0, t1 - t0};
+  }
+  return box;
+}
+
+__host__ __device__ inline int branch_pitch(int S) { return (S + 1 + 31) & ~31; }
+__host__ __device__ inline size_t branch_elems_per_utt(int S, int T) {
+  return (size_t)(S + T + 1) * branch_pitch(S);
+}
+
+__device__ __forceinline__ void bar_sync_named(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// -----------------------------------------------------------------------------
+// forward
+// -----------------------------------------------------------------------------
+template <typename real, int NCW, bool MODIFIED>
+__global__ void __launch_bounds__((NCW + kIoWarps) * 32)
+mi_forward_kernel(const real *__restrict__ px, const real *__restrict__ py,
+                  const int64_t *__restrict__ boundary, real *__restrict__ p,
+                  real *__restrict__ ans, real *__restrict__ branch, int S, int T) {
+  constexpr int ROWS = NCW * 32;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  real *ringx = reinterpret_cast<real *>(smem_raw);  // [2][ROWS][kPitch]
+  real *ringy = ringx + 2 * ROWS * kPitch;           // [2][ROWS][kPitch]
+  real *xchg = ringy + 2 * ROWS * kPitch;            // [4][NCW]
+
+  const int b = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int T1 = MODIFIED ? T : T + 1;
+  constexpr int off = MODIFIED ? -1 : 0;
+  const MiBox box = load_box(boundary, b, S, T);
+  const int nd = box.sb + box.tb + 1;  // anti-diagonals of this utterance
+  const int nchunks = (nd + kChunk - 1) / kChunk;
+  const real *X = px + (size_t)b * S * T1;
+  const real *Y = py + (size_t)b * (S + 1) * T;
+  real *P = p ? p + (size_t)b * (S + 1) * (T + 1) : nullptr;
+  const int bpitch = branch_pitch(S);
+  real *BR = branch ? branch + (size_t)b * branch_elems_per_utt(S, T) : nullptr;
+  const bool is_io = warp >= NCW;
+  const real ninf = neg_inf<real>();
+
+  if (threadIdx.x < 4 * NCW) xchg[threadIdx.x] = ninf;
+
+  // ring[slot][i][j] holds, for consumer cell (row i, diagonal 32c+j):
+  //   x = px[s0+i-1][t0+t'+o]   and   y = py[s0+i][t0+t'-1],   t' = 32c+j-i
+  auto load_chunk = [&](int c) {
+    const int slot = c & 1;
+    const int k = c * kChunk + lane;
+#pragma unroll 4
+    for (int i = warp - NCW; i <= box.sb; i += kIoWarps) {
+      const int tp = k - i;
+      real vx = 0, vy = 0;
+      if (tp >= 0 && tp <= box.tb) {
+        if (i >= 1 && tp + off >= 0)
+          vx = X[(size_t)(box.s0 + i - 1) * T1 + (box.t0 + tp + off)];
+        if (tp >= 1) vy = Y[(size_t)(box.s0 + i) * T + box.t0 + tp - 1];
+      }
+      ringx[(slot * ROWS + i) * kPitch + lane] = vx;
+      ringy[(slot * ROWS + i) * kPitch + lane] = vy;
+    }
+  };
+
+  if (is_io) load_chunk(0);
+  __syncthreads();
+
+  const int i = threadIdx.x;     // lattice row (compute threads only)
+  real p_cur = ninf, p_old = ninf;  // this row's cells at t'-1 and t'-2
+
+  for (int c = 0; c < nchunks; ++c) {
+    if (is_io) {
+      if (c + 1 < nchunks) load_chunk(c + 1);
+    } else {
+      const real *rx = ringx + ((c & 1) * ROWS + i) * kPitch;
+      const real *ry = ringy + ((c & 1) * ROWS + i) * kPitch;
+#pragma unroll 1
+      for (int j0 = 0; j0 < kChunk; j0 += 8) {
+        real xv[8], yv[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          xv[u] = rx[j0 + u];
+          yv[u] = ry[j0 + u];
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int k = c * kChunk + j0 + u;
+          const int tp = k - i;
+          // p of the row above: one step back (regular) or two (modified)
+          const real hist = MODIFIED ? p_old : p_cur;
+          real up = __shfl_up_sync(0xffffffffu, hist, 1);
+          if (NCW > 1 && lane == 0 && warp > 0)
+            up = xchg[((k - 1 + off) & 3) * NCW + warp - 1];
+          const bool active = (i <= box.sb) && tp >= 0 && tp <= box.tb;
+          const real a = (i > 0) ? up + xv[u] : ninf;
+          const real bb = p_cur + yv[u];
+          real pn = log_add(a, bb);
+          if (i == 0 && tp == 0) pn = 0;
+          if (!active) pn = ninf;
+          if (active) {
+            if (BR != nullptr) {
+              const real tot = (pn - pn != 0) ? (real)0 : pn;
+              BR[(size_t)k * bpitch + i] = exp_r(a - tot);
+            }
+            if (P != nullptr) P[(size_t)(box.s0 + i) * (T + 1) + box.t0 + tp] = pn;
+            if (i == box.sb && tp == box.tb) ans[b] = pn;
+          }
+          p_old = p_cur;
+          p_cur = pn;
+          if (NCW > 1) {
+            if (lane == 31) xchg[(k & 3) * NCW + warp] = pn;
+            bar_sync_named(1, NCW * 32);
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// -----------------------------------------------------------------------------
+// backward (from the branch weights)
+// -----------------------------------------------------------------------------
+template <typename real, int NCW, bool MODIFIED>
+__global__ void __launch_bounds__((NCW + kIoWarps) * 32)
+mi_backward_kernel(const real *__restrict__ branch, const int64_t *__restrict__ boundary,
+                   const real *__restrict__ ans_grad, real *__restrict__ px_grad,
+                   real *__restrict__ py_grad, real *__restrict__ origin_grad, int S, int T) {
+  constexpr int ROWS = NCW * 32;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  real *ringx = reinterpret_cast<real *>(smem_raw);  // [2][ROWS][kPitch]  d/dpx
+  real *ringy = ringx + 2 * ROWS * kPitch;           // [2][ROWS][kPitch]  d/dpy
+  real *xchg = ringy + 2 * ROWS * kPitch;            // [4][NCW]
+
+  const int b = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int T1 = MODIFIED ? T : T + 1;
+  constexpr int off = MODIFIED ? -1 : 0;
+  constexpr int tp_min_x = MODIFIED ? 1 : 0;  // first t' whose cell has an x-predecessor
+  const MiBox box = load_box(boundary, b, S, T);
+  const int nd = box.sb + box.tb + 1;
+  const int nchunks = (nd + kChunk - 1) / kChunk;
+  real *GX = px_grad + (size_t)b * S * T1;
+  real *GY = py_grad + (size_t)b * (S + 1) * T;
+  const int bpitch = branch_pitch(S);
+  const real *BR = branch + (size_t)b * branch_elems_per_utt(S, T);
+  const bool is_io = warp >= NCW;
+
+  if (threadIdx.x < 4 * NCW) xchg[threadIdx.x] = 0;
+
+  // cells (row i, diagonal 32c+j) -> px_grad[s0+i-1][t0+t'+o], py_grad[s0+i][t0+t'-1]
+  auto drain_chunk = [&](int c) {
+    const int slot = c & 1;
+    const int k = c * kChunk + lane;
+#pragma unroll 4
+    for (int i = warp - NCW; i <= box.sb; i += kIoWarps) {
+      const int tp = k - i;
+      if (tp <= box.tb) {
+        if (i >= 1 && tp >= tp_min_x)
+          GX[(size_t)(box.s0 + i - 1) * T1 + (box.t0 + tp + off)] =
+              ringx[(slot * ROWS + i) * kPitch + lane];
+        if (tp >= 1)
+          GY[(size_t)(box.s0 + i) * T + box.t0 + tp - 1] =
+              ringy[(slot * ROWS + i) * kPitch + lane];
+      }
+    }
+  };
+
+  __syncthreads();
+
+  if (is_io) {
+    // exact zeros outside the boundary box (mutual_information_cpu.cu:161-166);
+    // overlaps with the compute warps' first chunk
+    const int lw = warp - NCW;
+    const int cx_lo = box.t0, cx_hi = box.t0 + box.tb + off;  // inclusive, in-box columns of px_grad
+    for (int r = lw; r < S; r += kIoWarps) {
+      const bool in_rows = r >= box.s0 && r < box.s0 + box.sb;
+      for (int col = lane; col < T1; col += 32)
+        if (!in_rows || col < cx_lo || col > cx_hi) GX[(size_t)r * T1 + col] = 0;
+    }
+    const int cy_lo = box.t0, cy_hi = box.t0 + box.tb - 1;
+    for (int r = lw; r <= S; r += kIoWarps) {
+      const bool in_rows = r >= box.s0 && r <= box.s0 + box.sb;
+      for (int col = lane; col < T; col += 32)
+        if (!in_rows || col < cy_lo || col > cy_hi) GY[(size_t)r * T + col] = 0;
+    }
+  }
+
+  const int i = threadIdx.x;
+  real g1_cur = 0, g1_old = 0;  // x-gradients this row sent up at the last two steps
+  real g2_cur = 0;              // y-gradient this row sent left at the last step
+  const real g_end = ans_grad[b];
+
+  for (int c = nchunks - 1; c >= 0; --c) {
+    if (is_io) {
+      if (c + 1 < nchunks) drain_chunk(c + 1);
+    } else {
+      real *rx = ringx + ((c & 1) * ROWS + i) * kPitch;
+      real *ry = ringy + ((c & 1) * ROWS + i) * kPitch;
+#pragma unroll 1
+      for (int j0 = kChunk - 8; j0 >= 0; j0 -= 8) {
+        real br[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int k = c * kChunk + j0 + u;
+          const int tp = k - i;
+          br[u] = (i >= 1 && i <= box.sb && tp >= 1 && tp <= box.tb)
+                      ? BR[(size_t)k * bpitch + i]
+                      : (real)0;
+        }
+#pragma unroll
+        for (int u = 7; u >= 0; --u) {
+          const int k = c * kChunk + j0 + u;
+          const int tp = k - i;
+          const real hist = MODIFIED ? g1_old : g1_cur;
+          real below = __shfl_down_sync(0xffffffffu, hist, 1);
+          if (lane == 31)
+            below = (NCW > 1 && warp + 1 < NCW) ? xchg[((k + 1 - off) & 3) * NCW + warp + 1]
+                                                : (real)0;
+          const bool active = (i <= box.sb) && tp >= 0 && tp <= box.tb;
+          real g = below + g2_cur;
+          if (i == box.sb && tp == box.tb) g = g_end;
+          real d1, d2;
+          if (i == 0) {  // first row: only a y-predecessor
+            d1 = 0;
+            d2 = 1;
+          } else if (tp == 0) {  // first column: only an x-predecessor (regular) or none
+            d1 = MODIFIED ? 0 : 1;
+            d2 = 0;
+          } else {
+            d1 = br[u];
+            if (d1 - d1 == 0) {
+              d2 = (real)1 - d1;
+            } else {
+              d1 = 0;
+              d2 = 0;
+            }
+          }
+          real g1 = d1 * g, g2 = d2 * g;
+          if (!active) {
+            g1 = 0;
+            g2 = 0;
+          }
+          if (active && i == 0 && tp == 0 && origin_grad != nullptr) origin_grad[b] = g;
+          rx[j0 + u] = g1;
+          ry[j0 + u] = g2;
+          g1_old = g1_cur;
+          g1_cur = g1;
+          g2_cur = g2;
+          if (NCW > 1) {
+            if (lane == 0) xchg[(k & 3) * NCW + warp] = g1;
+            bar_sync_named(1, NCW * 32);
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  if (is_io && nchunks > 0) drain_chunk(0);
+}
+
+// branch weights from a lattice p in the reference's [B][S+1][T+1] layout
+template <typename real, bool MODIFIED>
+__global__ void mi_branch_from_p_kernel(const real *__restrict__ px, const real *__restrict__ p,
+                                        const int64_t *__restrict__ boundary,
+                                        real *__restrict__ branch, int S, int T) {
+  const int b = blockIdx.y;
+  const int T1 = MODIFIED ? T : T + 1;
+  constexpr int off = MODIFIED ? -1 : 0;
+  const MiBox box = load_box(boundary, b, S, T);
+  const real *X = px + (size_t)b * S * T1;
+  const real *P = p + (size_t)b * (S + 1) * (T + 1);
+  const int bpitch = branch_pitch(S);
+  real *BR = branch + (size_t)b * branch_elems_per_utt(S, T);
+  const int ncell = box.sb * box.tb;  // cells with both predecessors
+  for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < ncell;
+       idx += gridDim.x * blockDim.x) {
+    const int i = 1 + idx / box.tb, tp = 1 + idx % box.tb;
+    const int s = box.s0 + i, t = box.t0 + tp;
+    const real term1 = P[(size_t)(s - 1) * (T + 1) + (t + off)] + X[(size_t)(s - 1) * T1 + (t + off)];
+    real tot = P[(size_t)s * (T + 1) + t];
+    if (tot - tot != 0) tot = 0;
+    BR[(size_t)(i + tp) * bpitch + i] = exp_r(term1 - tot);
+  }
+}
+
+// -----------------------------------------------------------------------------
+// host side
+// -----------------------------------------------------------------------------
+template <typename real>
+static size_t mi_smem_bytes(int ncw) {
+  return (size_t)(4 * ncw * 32 * kPitch + 4 * ncw) * sizeof(real);
+}
+
+template <typename real, int NCW, bool MODIFIED>
+static int launch_forward(const void *px, const void *py, const int64_t *boundary, void *p,
+                          void *ans, void *branch, int B, int S, int T, cudaStream_t st) {
+  auto kern = mi_forward_kernel<real, NCW, MODIFIED>;
+  const size_t smem = mi_smem_bytes<real>(NCW);
+  FRNNT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<B, (NCW + kIoWarps) * 32, smem, st>>>((const real *)px, (const real *)py, boundary,
+                                               (real *)p, (real *)ans, (real *)branch, S, T);
+  FRNNT_CUDA(cudaGetLastError());
+  return FRNNT_OK;
+}
+
+template <typename real, int NCW, bool MODIFIED>
+static int launch_backward(const void *branch, const int64_t *boundary, const void *ans_grad,
+                           void *px_grad, void *py_grad, void *origin_grad, int B, int S, int T,
+                           cudaStream_t st) {
+  auto kern = mi_backward_kernel<real, NCW, MODIFIED>;
+  const size_t smem = mi_smem_bytes<real>(NCW);
+  FRNNT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<B, (NCW + kIoWarps) * 32, smem, st>>>((const real *)branch, boundary,
+                                               (const real *)ans_grad, (real *)px_grad,
+                                               (real *)py_grad, (real *)origin_grad, S, T);
+  FRNNT_CUDA(cudaGetLastError());
+  return FRNNT_OK;
+}
+
+#define MI_DISPATCH_NCW(FN, real, MOD, ncw, ...)                          \
+  switch (ncw) {                                                          \
+    case 1: return FN<real, 1, MOD>(__VA_ARGS__);                         \
+    case 2: return FN<real, 2, MOD>(__VA_ARGS__);                         \
+    case 3: return FN<real, 3, MOD>(__VA_ARGS__);                         \
+    case 4: return FN<real, 4, MOD>(__VA_ARGS__);                         \
+    case 5: return FN<real, 5, MOD>(__VA_ARGS__);                         \
+    case 6: return FN<real, 6, MOD>(__VA_ARGS__);                         \
+    case 7: return FN<real, 7, MOD>(__VA_ARGS__);                         \
+    default: return FN<real, 8, MOD>(__VA_ARGS__);                        \
+  }
+
+#define MI_DISPATCH(FN, dtype, modified, ncw, ...)                        \
+  do {                                                                    \
+    if ((dtype) == FRNNT_F32) {                                           \
+      if (modified) { MI_DISPATCH_NCW(FN, float, true, ncw, __VA_ARGS__) }  \
+      else { MI_DISPATCH_NCW(FN, float, false, ncw, __VA_ARGS__) }          \
+    } else {                                                              \
+      if (modified) { MI_DISPATCH_NCW(FN, double, true, ncw, __VA_ARGS__) } \
+      else { MI_DISPATCH_NCW(FN, double, false, ncw, __VA_ARGS__) }         \
+    }                                                                     \
+  } while (0)
+
+static int mi_check_sizes(int dtype, int B, int S, int T, int modified, int *ncw) {
+  FRNNT_REQUIRE(check_dtype(dtype), FRNNT_EINVAL, "dtype must be FRNNT_F32 or FRNNT_F64, got %d",
+                dtype);
+  FRNNT_REQUIRE(B >= 0 && S >= 0 && T >= 0, FRNNT_EINVAL, "negative size B=%d S=%d T=%d", B, S, T);
+  FRNNT_REQUIRE(modified == 0 || modified == 1, FRNNT_EINVAL, "modified must be 0 or 1");
+  const int rows_max = (dtype == FRNNT_F64 ? 6 : kMaxComputeWarps) * 32;
+  FRNNT_REQUIRE(S + 1 <= rows_max, FRNNT_EUNSUPPORTED,
+                "S+1=%d exceeds the %d lattice rows one CTA holds for this dtype", S + 1,
+                rows_max);
+  *ncw = (S + 1 + 31) / 32;
+  return FRNNT_OK;
+}
+
+}  // namespace frnnt
+
+using namespace frnnt;
+
+extern "C" size_t frnnt_mi_branch_bytes(int dtype, int B, int S, int T) {
+  if (!check_dtype(dtype) || B < 0 || S < 0 || T < 0) return 0;
+  return (size_t)B * branch_elems_per_utt(S, T) * dtype_size(dtype);
+}
+
+extern "C" int frnnt_mi_forward(int dtype, const void *px, const void *py,
+                                const int64_t *boundary, void *p, void *ans, void *branch, int B,
+                                int S, int T, int modified, void *stream) {
+  int ncw = 0;
+  int rc = mi_check_sizes(dtype, B, S, T, modified, &ncw);
+  if (rc != FRNNT_OK) return rc;
+  if (B == 0) return FRNNT_OK;
+  FRNNT_REQUIRE(ans != nullptr, FRNNT_EINVAL, "ans is NULL");
+  FRNNT_REQUIRE((px != nullptr || S == 0 || (modified && T == 0)) && (py != nullptr || T == 0),
+                FRNNT_EINVAL, "px or py is NULL");
+  cudaStream_t st = (cudaStream_t)stream;
+  MI_DISPATCH(launch_forward, dtype, modified, ncw, px, py, boundary, p, ans, branch, B, S, T, st);
+  return FRNNT_OK;
+}
+
+extern "C" int frnnt_mi_backward_from_branch(int dtype, const void *branch,
+                                             const int64_t *boundary, const void *ans_grad,
+                                             void *px_grad, void *py_grad, void *origin_grad,
+                                             int B, int S, int T, int modified, void *stream) {
+  int ncw = 0;
+  int rc = mi_check_sizes(dtype, B, S, T, modified, &ncw);
+  if (rc != FRNNT_OK) return rc;
+  if (B == 0) return FRNNT_OK;
+  FRNNT_REQUIRE(branch != nullptr && ans_grad != nullptr, FRNNT_EINVAL,
+                "branch or ans_grad is NULL");
+  FRNNT_REQUIRE((px_grad != nullptr || S == 0 || (modified && T == 0)) &&
+                    (py_grad != nullptr || T == 0),
+                FRNNT_EINVAL, "px_grad or py_grad is NULL");
+  cudaStream_t st = (cudaStream_t)stream;
+  MI_DISPATCH(launch_backward, dtype, modified, ncw, branch, boundary, ans_grad, px_grad, py_grad,
+              origin_grad, B, S, T, st);
+  return FRNNT_OK;
+}
+
+extern "C" int frnnt_mi_backward(int dtype, const void *px, const void *py,
+                                 const int64_t *boundary, const void *p, const void *ans_grad,
+                                 void *px_grad, void *py_grad, void *origin_grad, void *branch,
+                                 int B, int S, int T, int modified, void *stream) {
+  (void)py;
+  int ncw = 0;
+  int rc = mi_check_sizes(dtype, B, S, T, modified, &ncw);
+  if (rc != FRNNT_OK) return rc;
+  if (B == 0) return FRNNT_OK;
+  FRNNT_REQUIRE(p != nullptr && branch != nullptr, FRNNT_EINVAL, "p or branch is NULL");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (S > 0 && T > 0) {
+    FRNNT_REQUIRE(px != nullptr, FRNNT_EINVAL, "px is NULL");
+    dim3 grid((unsigned)min(64, (S * T + 255) / 256), (unsigned)B);
+    if (dtype == FRNNT_F32) {
+      if (modified)
+        mi_branch_from_p_kernel<float, true><<<grid, 256, 0, st>>>(
+            (const float *)px, (const float *)p, boundary, (float *)branch, S, T);
+      else
+        mi_branch_from_p_kernel<float, false><<<grid, 256, 0, st>>>(
+            (const float *)px, (const float *)p, boundary, (float *)branch, S, T);
+    } else {
+      if (modified)
+        mi_branch_from_p_kernel<double, true><<<grid, 256, 0, st>>>(
+            (const double *)px, (const double *)p, boundary, (double *)branch, S, T);
+      else
+        mi_branch_from_p_kernel<double, false><<<grid, 256, 0, st>>>(
+            (const double *)px, (const double *)p, boundary, (double *)branch, S, T);
+    }
+    FRNNT_CUDA(cudaGetLastError());
+  }
+  return frnnt_mi_backward_from_branch(dtype, branch, boundary, ans_grad, px_grad, py_grad,
+                                       origin_grad, B, S, T, modified, stream);
+}
