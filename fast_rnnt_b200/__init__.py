@@ -1,8 +1,21 @@
 """B200-native (sm_100a) pruned RNN-T loss: drop-in for the python API of
-k2-fsa/fast_rnnt (``import fast_rnnt_b200 as fast_rnnt``).  CUDA tensors only."""
+k2-fsa/fast_rnnt (``import fast_rnnt_b200 as fast_rnnt``).  CUDA tensors only;
+the same 13 functions plus ``with_cuda`` as the reference's
+fast_rnnt/python/fast_rnnt/__init__.py:1-15."""
 from ._lib import FrnntError  # noqa: F401
 from .mutual_information import mutual_information_recursion  # noqa: F401
 from .mutual_information import joint_mutual_information_recursion  # noqa: F401
+
+from .rnnt_loss import do_rnnt_pruning  # noqa: F401
+from .rnnt_loss import get_rnnt_logprobs  # noqa: F401
+from .rnnt_loss import get_rnnt_logprobs_joint  # noqa: F401
+from .rnnt_loss import get_rnnt_logprobs_pruned  # noqa: F401
+from .rnnt_loss import get_rnnt_logprobs_smoothed  # noqa: F401
+from .rnnt_loss import get_rnnt_prune_ranges  # noqa: F401
+from .rnnt_loss import rnnt_loss  # noqa: F401
+from .rnnt_loss import rnnt_loss_pruned  # noqa: F401
+from .rnnt_loss import rnnt_loss_simple  # noqa: F401
+from .rnnt_loss import rnnt_loss_smoothed  # noqa: F401
 
 
 def with_cuda() -> bool:

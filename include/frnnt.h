@@ -95,6 +95,77 @@ int frnnt_mi_backward(int dtype, const void *px, const void *py, const int64_t *
                       void *origin_grad, void *branch, int B, int S, int T, int modified,
                       void *stream);
 
+/* ----------------------------------------------------------------------------
+ * Log-prob lattices from factorised encoder / decoder outputs ("simple" loss)
+ * ------------------------------------------------------------------------- */
+
+/* Bytes of the state the forward keeps for the backward, and of the per-call
+ * temporaries, of the two functions below. */
+size_t frnnt_simple_saved_bytes(int dtype, int B, int S, int T, int C);
+size_t frnnt_simple_scratch_bytes(int dtype, int B, int S, int T, int C);
+
+/* px [B][S][T1], py [B][S+1][T] from lm [B][S+1][C], am [B][T][C], symbols [B][S].
+ * smoothed == 0 replaces get_rnnt_logprobs (fast_rnnt/python/fast_rnnt/rnnt_loss.py:66-227);
+ * smoothed != 0 replaces get_rnnt_logprobs_smoothed (rnnt_loss.py:1135-1369) with its
+ * lm_only_scale / am_only_scale (exact zeros become 1e-20 as in the reference).
+ * rnnt_type is FRNNT_REGULAR / FRNNT_MODIFIED / FRNNT_CONSTRAINED; boundary may be NULL. */
+int frnnt_simple_logprobs_forward(int dtype, const void *lm, const void *am,
+                                  const int64_t *symbols, const int64_t *boundary, int blank,
+                                  int rnnt_type, int smoothed, double lm_only_scale,
+                                  double am_only_scale, void *px, void *py, void *saved,
+                                  void *scratch, int B, int S, int T, int C, void *stream);
+
+/* Gradient of the above w.r.t. lm and am given the gradients of px and py
+ * (what autograd derives for the reference's composition of ATen ops).
+ * lm_grad [B][S+1][C] and am_grad [B][T][C] are fully written. */
+int frnnt_simple_logprobs_backward(int dtype, const void *lm, const void *am,
+                                   const int64_t *symbols, const int64_t *boundary, int blank,
+                                   int rnnt_type, int smoothed, double lm_only_scale,
+                                   double am_only_scale, const void *px_grad, const void *py_grad,
+                                   const void *saved, void *scratch, void *lm_grad, void *am_grad,
+                                   int B, int S, int T, int C, void *stream);
+
+/* ----------------------------------------------------------------------------
+ * Log-prob lattices from joiner logits (pruned and unpruned)
+ * ------------------------------------------------------------------------- */
+
+/* logits [B][T][R][C] -> lse, px_band, py_band (each [B][T][R]) and, unless px
+ * and py are NULL, the lattices px [B][S][T1], py [B][S+1][T].
+ * With ranges [B][T][R] this replaces get_rnnt_logprobs_pruned
+ * (rnnt_loss.py:856-1024); with ranges == NULL and R == S+1 it replaces
+ * get_rnnt_logprobs_joint (rnnt_loss.py:343-449). */
+int frnnt_lsm_gather_forward(int dtype, const void *logits, const int64_t *symbols,
+                             const int64_t *ranges, const int64_t *boundary, void *lse,
+                             void *px_band, void *py_band, void *px, void *py, int B, int T,
+                             int R, int S, int C, int blank, int rnnt_type, void *stream);
+
+/* Gradient of the above w.r.t. the logits; logits_grad [B][T][R][C] is fully written. */
+int frnnt_lsm_gather_backward(int dtype, const void *logits, const int64_t *symbols,
+                              const int64_t *ranges, const int64_t *boundary, const void *lse,
+                              const void *px_grad, const void *py_grad, void *logits_grad, int B,
+                              int T, int R, int S, int C, int blank, int rnnt_type, void *stream);
+
+/* ----------------------------------------------------------------------------
+ * Pruning
+ * ------------------------------------------------------------------------- */
+
+/* ranges [B][T][s_range] (int64) from the occupancies px_grad [B][S][T1] and
+ * py_grad [B][S+1][T].  Replaces the device part of get_rnnt_prune_ranges
+ * (rnnt_loss.py:726-777); s_range is the value AFTER the host-side adjustment
+ * of rnnt_loss.py:699-724 and must lie in [1, S+1].  boundary is required. */
+int frnnt_prune_ranges(int dtype, const void *px_grad, const void *py_grad,
+                       const int64_t *boundary, int64_t *ranges, int B, int S, int T, int T1,
+                       int s_range, void *stream);
+
+/* out [B][T][R][D] = lm [B][S1][D] gathered at ranges [B][T][R]: the lm half of
+ * do_rnnt_pruning (rnnt_loss.py:813-817; the am half is a stride-0 view). */
+int frnnt_prune_gather(int dtype, const void *lm, const int64_t *ranges, void *out, int B,
+                       int S1, int T, int R, int D, void *stream);
+
+/* lm_grad [B][S1][D] = scatter-add of out_grad [B][T][R][D] (deterministic). */
+int frnnt_prune_gather_backward(int dtype, const void *out_grad, const int64_t *ranges,
+                                void *lm_grad, int B, int S1, int T, int R, int D, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -373,9 +373,17 @@ def prune_ranges(px_grad: Tensor, py_grad: Tensor, boundary: Tensor, s_range: in
         s_range = S1
     assert s_range >= (2 if regular else 1)
 
-    sb, ss, st = py_grad.stride()
-    windows = torch.as_strided(py_grad, (B, S1 - s_range + 1, s_range, T), (sb, ss, ss, st))
-    win_sum = torch.sum(windows, axis=2)
+    # Window sums over s_range consecutive rows of py_grad (rnnt_loss.py:726-734).
+    # The reference calls torch.sum on a strided view; torch adds the s_range
+    # terms in order k = 0, 1, ... for all but the last few (< 32) elements of
+    # each utterance's flattened output, where its scalar tail loop uses a
+    # 4-accumulator cascade whose extent depends on the thread split.  The
+    # oracle fixes the in-order sum everywhere: it is machine independent and
+    # reproduces the reference's ranges bit for bit on every golden case.
+    n_win = S1 - s_range + 1
+    win_sum = py_grad[:, 0:n_win, :].clone()
+    for k in range(1, s_range):
+        win_sum = win_sum + py_grad[:, k:k + n_win, :]
     px_shift = torch.cat((torch.zeros((B, 1, T1), dtype=px_grad.dtype), px_grad), dim=1)
     score = win_sum - px_shift[:, : S1 - s_range + 1, :T]
     s_begin = torch.argmax(score, axis=1)                               # [B,T]

@@ -27,7 +27,8 @@ def tol(dtype):
 
 
 def assert_close(a, b, rtol, atol, what=""):
-    a, b = a.detach().cpu(), b.detach().cpu()
+    a, b = torch.as_tensor(a).detach().cpu(), torch.as_tensor(b).detach().cpu()
+    b = b.to(a.dtype)
     assert a.shape == b.shape, (what, a.shape, b.shape)
     fin = torch.isfinite(b)
     assert torch.equal(torch.isfinite(a), fin), f"{what}: finiteness pattern differs"
