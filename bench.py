@@ -1,0 +1,439 @@
+#!/usr/bin/env python
+"""Benchmark of the pruned RNN-T loss hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload c3|c5] [--no-stages] [--no-cpu-baseline]
+
+One "step" is the whole pruned pipeline of the reference's documented usage,
+forward and backward, on one batch of synthetic utterances:
+  rnnt_loss_smoothed(return_grad) -> get_rnnt_prune_ranges -> do_rnnt_pruning ->
+  joiner Linear(tanh(enc+dec)) -> rnnt_loss_pruned -> (simple+pruned).backward()
+The joiner is the caller's network (plain torch, cuBLAS fp32); everything else
+runs in libfrnnt_sm100.so.  Rank 0 prints ONE JSON line.
+
+Under torchrun every rank works on its own batch (weak scaling); the only
+collective is an NCCL all-reduce of the scalar loss.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+from tests import workloads  # noqa: E402  (seeded synthetic inputs)
+
+L2_FLUSH_BYTES = 512 << 20
+
+# DRAM traffic per launch measured once with ncu (dram__bytes_read.sum +
+# dram__bytes_write.sum, profiles/); keyed by stage name, bytes for workload c3.
+NCU_TRAFFIC_C3 = {}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while timing runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------
+# the step
+# ------------------------------------------------------------------------------
+def make_step(fr, wl):
+    """Returns step(inputs) -> loss for the pruned pipeline; `fr` is the loss
+    package (ours on CUDA, or the CPU oracle wrapped to the same names)."""
+    blank, R = wl["blank"], wl["s_range"]
+    ls, as_ = wl["lm_only_scale"], wl["am_only_scale"]
+
+    def step(t):
+        am = t["am"].requires_grad_(True)
+        lm = t["lm"].requires_grad_(True)
+        enc = t["enc"].requires_grad_(True)
+        dec = t["dec"].requires_grad_(True)
+        W = t["joiner_w"].requires_grad_(True)
+        bias = t["joiner_b"].requires_grad_(True)
+        for x in (am, lm, enc, dec, W, bias):
+            x.grad = None
+        simple, (gx, gy) = fr.rnnt_loss_smoothed(
+            lm=lm, am=am, symbols=t["symbols"], termination_symbol=blank, lm_only_scale=ls,
+            am_only_scale=as_, boundary=t["boundary"], reduction="sum", return_grad=True)
+        ranges = fr.get_rnnt_prune_ranges(px_grad=gx, py_grad=gy, boundary=t["boundary"], s_range=R)
+        am_p, lm_p = fr.do_rnnt_pruning(am=enc, lm=dec, ranges=ranges)
+        logits = torch.nn.functional.linear(torch.tanh(am_p + lm_p), W, bias)
+        pruned = fr.rnnt_loss_pruned(logits=logits, symbols=t["symbols"], ranges=ranges,
+                                     termination_symbol=blank, boundary=t["boundary"],
+                                     reduction="sum")
+        loss = simple + pruned
+        loss.backward()
+        return loss.detach()
+
+    return step
+
+
+class OracleApi:
+    """The CPU oracle under the reference's function names (CPU baseline only)."""
+
+    def __init__(self):
+        from oracle import rnnt_oracle as orc
+        self.orc = orc
+
+    def rnnt_loss_smoothed(self, lm, am, symbols, termination_symbol, lm_only_scale,
+                           am_only_scale, boundary, reduction, return_grad):
+        return self.orc.loss_smoothed(lm, am, symbols, termination_symbol, lm_only_scale,
+                                      am_only_scale, boundary, "regular", 0.0, reduction,
+                                      return_grad)
+
+    def get_rnnt_prune_ranges(self, px_grad, py_grad, boundary, s_range):
+        return self.orc.prune_ranges(px_grad, py_grad, boundary, s_range)
+
+    def do_rnnt_pruning(self, am, lm, ranges):
+        return self.orc.prune(am, lm, ranges)
+
+    def rnnt_loss_pruned(self, logits, symbols, ranges, termination_symbol, boundary, reduction):
+        return self.orc.loss_pruned(logits, symbols, ranges, termination_symbol, boundary,
+                                    "regular", 0.0, reduction)
+
+
+TENSOR_KEYS = ("am", "lm", "enc", "dec", "joiner_w", "joiner_b", "symbols", "boundary")
+
+
+def cpu_reference_run(workload, sample_batch, steps, warmup):
+    """Times the CPU oracle (the reference's algorithm on the host cores)."""
+    wl = workloads.pipeline_workload(workload, batch=sample_batch)
+    step = make_step(OracleApi(), wl)
+    t = {k: wl[k].clone() for k in TENSOR_KEYS}
+    for _ in range(warmup):
+        step(t)
+    times = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        step(t)
+        times.append(time.perf_counter() - t0)
+    sec = sum(times) / len(times)
+    return sample_batch / sec, sec * 1e3
+
+
+# ------------------------------------------------------------------------------
+# per-stage timing (each C-ABI stage alone, CUDA events, L2 flushed in between)
+# ------------------------------------------------------------------------------
+def time_call(fn, flush, reps=10, warm=3):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    ms = []
+    for _ in range(reps):
+        flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        e.synchronize()
+        ms.append(s.elapsed_time(e))
+    return statistics.median(ms)
+
+
+def stage_table(fr, wl, dev, flush, hbm_gbs):
+    """Times every stage of the loss path alone and relates it to its
+    algorithmic bytes (each input read once, each output written once)."""
+    from fast_rnnt_b200 import mutual_information as mi
+    t = {k: wl[k].to(dev) for k in TENSOR_KEYS}
+    B, T, C = t["am"].shape
+    S = t["lm"].shape[1] - 1
+    D = t["enc"].shape[2]
+    R = wl["s_range"]
+    ls, as_ = wl["lm_only_scale"], wl["am_only_scale"]
+    es = 4
+    cells_box = workloads.lattice_cells(wl["boundary"], B, S, T)
+    lat = es * B * (S * (T + 1) + (S + 1) * T)
+
+    lm = t["lm"].clone().requires_grad_(True)
+    am = t["am"].clone().requires_grad_(True)
+    px, py = fr.get_rnnt_logprobs_smoothed(lm=lm, am=am, symbols=t["symbols"],
+                                           termination_symbol=0, lm_only_scale=ls,
+                                           am_only_scale=as_, boundary=t["boundary"])
+    gpx, gpy = torch.rand_like(px), torch.rand_like(py)
+    pxd, pyd = px.detach(), py.detach()
+    _, _, branch = mi.mi_forward(pxd, pyd, t["boundary"])
+    ones = torch.ones(B, device=dev)
+    ox, oy = mi.mi_backward_from_branch(branch, t["boundary"], ones, px.shape, py.shape, px.dtype)
+    ranges = fr.get_rnnt_prune_ranges(px_grad=ox, py_grad=oy, boundary=t["boundary"], s_range=R)
+    dec = t["dec"].clone().requires_grad_(True)
+    _, lm_p = fr.do_rnnt_pruning(am=t["enc"], lm=dec, ranges=ranges)
+    g_lm_p = torch.rand_like(lm_p)
+    logits = torch.randn(B, T, R, C, device=dev).requires_grad_(True)
+    ppx, ppy = fr.get_rnnt_logprobs_pruned(logits=logits, symbols=t["symbols"], ranges=ranges,
+                                           termination_symbol=0, boundary=t["boundary"])
+    ppxd, ppyd = ppx.detach(), ppy.detach()
+    _, _, pbranch = mi.mi_forward(ppxd, ppyd, t["boundary"])
+
+    def fwd_simple():
+        fr.get_rnnt_logprobs_smoothed(lm=t["lm"], am=t["am"], symbols=t["symbols"],
+                                      termination_symbol=0, lm_only_scale=ls, am_only_scale=as_,
+                                      boundary=t["boundary"])
+
+    stages = [
+        # name, callable, algorithmic bytes, flops (for the contraction) or None
+        ("simple_logprobs_fwd", fwd_simple, es * B * (T + S + 1) * C + lat, 2.0 * B * (S + 1) * T * C),
+        ("simple_logprobs_bwd",
+         lambda: torch.autograd.grad((px, py), (lm, am), (gpx, gpy), retain_graph=True),
+         2 * es * B * (T + S + 1) * C + lat, 4.0 * B * (S + 1) * T * C),
+        ("mi_forward", lambda: mi.mi_forward(pxd, pyd, t["boundary"]), 12 * cells_box, None),
+        ("mi_backward", lambda: mi.mi_backward_from_branch(branch, t["boundary"], ones, px.shape,
+                                                           py.shape, px.dtype), 4 * cells_box + lat, None),
+        ("mi_forward_pruned", lambda: mi.mi_forward(ppxd, ppyd, t["boundary"]), 12 * cells_box, None),
+        ("mi_backward_pruned", lambda: mi.mi_backward_from_branch(pbranch, t["boundary"], ones,
+                                                                  px.shape, py.shape, px.dtype),
+         4 * cells_box + lat, None),
+        ("prune_ranges", lambda: fr.get_rnnt_prune_ranges(px_grad=ox, py_grad=oy,
+                                                          boundary=t["boundary"], s_range=R),
+         lat + 8 * B * T * R, None),
+        ("prune_gather_fwd", lambda: fr.do_rnnt_pruning(am=t["enc"], lm=t["dec"], ranges=ranges),
+         es * B * T * R * D + es * B * (S + 1) * D + 8 * B * T * R, None),
+        ("prune_gather_bwd", lambda: torch.autograd.grad(lm_p, dec, g_lm_p, retain_graph=True),
+         es * B * T * R * D + es * B * (S + 1) * D, None),
+        ("lsm_gather_fwd", lambda: fr.get_rnnt_logprobs_pruned(
+            logits=logits.detach(), symbols=t["symbols"], ranges=ranges, termination_symbol=0,
+            boundary=t["boundary"]), es * B * T * R * C + lat + 3 * es * B * T * R, None),
+        ("lsm_gather_bwd", lambda: torch.autograd.grad((ppx, ppy), logits, (gpx, gpy),
+                                                       retain_graph=True),
+         2 * es * B * T * R * C, None),
+    ]
+    out = {}
+    for name, fn, nbytes, flops in stages:
+        ms = time_call(fn, flush)
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out[name] = {"ms": round(ms, 4), "alg_bytes": int(nbytes), "gbs": round(gbs, 1),
+                     "hbm_frac": round(gbs / hbm_gbs, 4)}
+        if flops:
+            out[name]["tflops"] = round(flops / (ms * 1e-3) / 1e12, 2)
+    return out, cells_box
+
+
+# ------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c3", choices=["c3", "c5", "small"])
+    ap.add_argument("--batch", type=int, default=None, help="utterances per GPU")
+    ap.add_argument("--no-stages", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    sizes = workloads.PIPELINE_SIZES[args.workload]
+    batch = args.batch or (sizes[0] if args.workload != "c5" else sizes[0] // 8)
+    cfg = {"workload": f"{args.workload}: pruned RNN-T loss pipeline fwd+bwd (smoothed simple loss, "
+                       f"prune ranges, pruning, joiner, pruned loss)",
+           "B_per_gpu": batch, "T": sizes[1], "S": sizes[2], "C": sizes[3], "D": sizes[4],
+           "s_range": sizes[5], "global_batch": batch * world,
+           "parallelism": f"batch sharded over {world} GPU(s), scalar-loss all-reduce",
+           "joiner": "torch Linear(tanh(enc+dec)), cuBLAS fp32 (caller's network)",
+           "l2": f"flushed between timed steps ({L2_FLUSH_BYTES >> 20} MiB write)"}
+
+    # -------------------------------------------------------------- reference arm
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        torch.set_num_threads(os.cpu_count() or 1)
+        sample = min(batch, 16)
+        value, ms = cpu_reference_run(args.workload, sample, max(1, args.steps), args.warmup)
+        cores = torch.get_num_threads()
+        line = {"impl": "reference", "metric": "utterances/sec", "value": round(value, 3),
+                "unit": "utt/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": cfg,
+                "cpu_baseline": {"value": round(value, 3), "unit": "utt/s", "cores": cores,
+                                 "kind": "port",
+                                 "sample": f"{sample} utterances of the {args.workload} batch per step "
+                                           f"(CPU oracle: torch CPU ops + C recursion)"},
+                "e2e": {"value": round(value, 3), "unit": "utt/s", "h2d_bytes_per_step": 0,
+                        "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
+        return
+
+    # ----------------------------------------------------------------------- ours
+    import fast_rnnt_b200 as fr
+    from fast_rnnt_b200 import _lib
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (no CPU path)"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _lib.lib()
+    lib.frnnt_launch_count.restype = __import__("ctypes").c_longlong
+
+    wl = workloads.pipeline_workload(args.workload, batch=batch, seed=rank)
+    host = {k: wl[k].pin_memory() for k in TENSOR_KEYS}
+    resident = {k: v.to(dev) for k, v in host.items()}
+    inner = make_step(fr, wl)
+
+    def step(t):
+        loss = inner(t)
+        if world > 1:
+            dist.all_reduce(loss)
+        return loss
+
+    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(run_one, steps, warmup):
+        for _ in range(warmup):
+            run_one()
+        barrier()
+        pairs = []
+        for _ in range(steps):
+            flush.zero_()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            run_one()
+            e.record()
+            pairs.append((s, e))
+        barrier()
+        total_ms = sum(s.elapsed_time(e) for s, e in pairs)
+        if world > 1:
+            tt = torch.tensor([total_ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            total_ms = float(tt.item())
+        return total_ms
+
+    # value: inputs resident in HBM
+    with ClockSampler(local_rank) as clocks:
+        n0 = lib.frnnt_launch_count()
+        total_ms = timed(lambda: step(resident), args.steps, args.warmup)
+        launches = (lib.frnnt_launch_count() - n0) // (args.steps + args.warmup)
+    ms_per_step = total_ms / args.steps
+    value = batch * world / (ms_per_step * 1e-3)
+
+    # e2e: host (pinned) inputs, H2D of every input and D2H of the loss inside the timed region
+    loss_host = torch.empty((), dtype=torch.float32).pin_memory()
+    io_keys = ("am", "lm", "enc", "dec", "symbols", "boundary")
+
+    def e2e_one():
+        t = dict(resident)
+        for k in io_keys:
+            t[k] = host[k].to(dev, non_blocking=True)
+        loss = step(t)
+        loss_host.copy_(loss, non_blocking=True)
+
+    e2e_ms = timed(e2e_one, args.steps, args.warmup) / args.steps
+    h2d = sum(host[k].numel() * host[k].element_size() for k in io_keys)
+    e2e_value = batch * world / (e2e_ms * 1e-3)
+
+    hbm_gbs, peak_kind = measured_peaks()
+    line = {"metric": "utterances/sec", "value": round(value, 1), "unit": "utt/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": cfg,
+            "clocks": clocks.summary(),
+            "e2e": {"value": round(e2e_value, 1), "unit": "utt/s", "h2d_bytes_per_step": int(h2d),
+                    "d2h_bytes_per_step": 4, "ms_per_step": round(e2e_ms, 4)},
+            "gpu_launches": int(launches)}
+
+    if rank == 0 and not args.no_stages:
+        stages, cells = stage_table(fr, wl, dev, flush, hbm_gbs)
+        loss_path_ms = sum(v["ms"] for v in stages.values())
+        line["stages"] = stages
+        line["loss_path"] = {"ms_per_step": round(loss_path_ms, 4),
+                             "value": round(batch / (loss_path_ms * 1e-3), 1), "unit": "utt/s",
+                             "note": "sum of the library's stages timed alone (no joiner)"}
+        mi_ms = stages["mi_forward"]["ms"] + stages["mi_backward"]["ms"]
+        line["mi_cells_per_s"] = round(cells / (mi_ms * 1e-3), 1)
+        single = [k for k in stages if not k.startswith("simple_")]
+        top = max(single, key=lambda k: stages[k]["ms"])
+        line["roofline"] = {"kernel": top, "bound": "hbm", "achieved": stages[top]["gbs"],
+                            "peak": hbm_gbs, "unit": "GB/s", "frac": stages[top]["hbm_frac"],
+                            "peak_kind": f"of {peak_kind}",
+                            "traffic": NCU_TRAFFIC_C3.get(top) if args.workload == "c3" else None}
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        torch.set_num_threads(os.cpu_count() or 1)
+        sample = min(batch, 16)
+        v, ms = cpu_reference_run(args.workload, sample, 3, 1)
+        line["cpu_baseline"] = {"value": round(v, 3), "unit": "utt/s",
+                                "cores": torch.get_num_threads(), "kind": "port",
+                                "sample": f"{sample} utterances of the {args.workload} batch, 3 steps "
+                                          f"(CPU oracle: torch CPU ops + C recursion)",
+                                "ms_per_step": round(ms, 2)}
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

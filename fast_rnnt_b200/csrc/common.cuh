@@ -29,6 +29,11 @@ void set_error(const char *fmt, ...);
     }                                                                           \
   } while (0)
 
+// every kernel launch goes through this macro so that callers can ask how many
+// kernels the library has launched (frnnt_launch_count)
+void count_launch();
+#define FRNNT_KERNEL(...) (::frnnt::count_launch(), __VA_ARGS__)
+
 inline int check_dtype(int dtype) { return dtype == FRNNT_F32 || dtype == FRNNT_F64; }
 inline size_t dtype_size(int dtype) { return dtype == FRNNT_F64 ? 8 : 4; }
 

@@ -266,9 +266,9 @@ static int lsm_forward_impl(const void *logits, const int64_t *symbols, const in
   long long want = (rows + gpc - 1) / gpc;
   const int grid = (int)(want < 148LL * 64 ? (want > 0 ? want : 1) : 148LL * 64);
 #define LSM_FWD(VW, G)                                                                         \
-  lsm_rows_forward_kernel<real, VW, G><<<grid, kRowCta, 0, st>>>(                                \
+  FRNNT_KERNEL(lsm_rows_forward_kernel<real, VW, G><<<grid, kRowCta, 0, st>>>(                                \
       (const real *)logits, symbols, ranges, (real *)lse, (real *)pxb, (real *)pyb, rows, T, R, \
-      S, C, blank)
+      S, C, blank))
   if (rows > 0) {
     if (vec_ok) {
       if (group == 32) LSM_FWD(VWMAX, 32);
@@ -286,9 +286,9 @@ static int lsm_forward_impl(const void *logits, const int64_t *symbols, const in
 #undef LSM_FWD
   if (px != nullptr && py != nullptr && B > 0) {
     dim3 grid2((unsigned)((T + 1 + 127) / 128), (unsigned)(S + 1), (unsigned)B);
-    band_to_lattice_kernel<real><<<grid2, 128, 0, st>>>((const real *)pxb, (const real *)pyb,
+    FRNNT_KERNEL(band_to_lattice_kernel<real><<<grid2, 128, 0, st>>>((const real *)pxb, (const real *)pyb,
                                                        ranges, boundary, (real *)px, (real *)py,
-                                                       S, T, R, rnnt_type);
+                                                       S, T, R, rnnt_type));
     FRNNT_CUDA(cudaGetLastError());
   }
   return FRNNT_OK;
@@ -307,13 +307,13 @@ static int lsm_backward_impl(const void *logits, const int64_t *symbols, const i
   long long want = (rows + 7) / 8;
   const int grid = (int)(want < 148LL * 64 ? want : 148LL * 64);
   if (vec_ok)
-    lsm_rows_backward_kernel<real, VWMAX><<<grid, kRowCta, 0, st>>>(
+    FRNNT_KERNEL(lsm_rows_backward_kernel<real, VWMAX><<<grid, kRowCta, 0, st>>>(
         (const real *)logits, symbols, ranges, boundary, (const real *)lse, (const real *)g_px,
-        (const real *)g_py, (real *)g_logits, rows, T, R, S, C, blank, rnnt_type);
+        (const real *)g_py, (real *)g_logits, rows, T, R, S, C, blank, rnnt_type));
   else
-    lsm_rows_backward_kernel<real, 1><<<grid, kRowCta, 0, st>>>(
+    FRNNT_KERNEL(lsm_rows_backward_kernel<real, 1><<<grid, kRowCta, 0, st>>>(
         (const real *)logits, symbols, ranges, boundary, (const real *)lse, (const real *)g_px,
-        (const real *)g_py, (real *)g_logits, rows, T, R, S, C, blank, rnnt_type);
+        (const real *)g_py, (real *)g_logits, rows, T, R, S, C, blank, rnnt_type));
   FRNNT_CUDA(cudaGetLastError());
   return FRNNT_OK;
 }

@@ -350,8 +350,8 @@ static int launch_forward(const void *px, const void *py, const int64_t *boundar
   auto kern = mi_forward_kernel<real, NCW, MODIFIED>;
   const size_t smem = mi_smem_bytes<real>(NCW);
   FRNNT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<B, (NCW + kIoWarps) * 32, smem, st>>>((const real *)px, (const real *)py, boundary,
-                                               (real *)p, (real *)ans, (real *)branch, S, T);
+  FRNNT_KERNEL(kern<<<B, (NCW + kIoWarps) * 32, smem, st>>>((const real *)px, (const real *)py, boundary,
+                                               (real *)p, (real *)ans, (real *)branch, S, T));
   FRNNT_CUDA(cudaGetLastError());
   return FRNNT_OK;
 }
@@ -363,9 +363,9 @@ static int launch_backward(const void *branch, const int64_t *boundary, const vo
   auto kern = mi_backward_kernel<real, NCW, MODIFIED>;
   const size_t smem = mi_smem_bytes<real>(NCW);
   FRNNT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<B, (NCW + kIoWarps) * 32, smem, st>>>((const real *)branch, boundary,
+  FRNNT_KERNEL(kern<<<B, (NCW + kIoWarps) * 32, smem, st>>>((const real *)branch, boundary,
                                                (const real *)ans_grad, (real *)px_grad,
-                                               (real *)py_grad, (real *)origin_grad, S, T);
+                                               (real *)py_grad, (real *)origin_grad, S, T));
   FRNNT_CUDA(cudaGetLastError());
   return FRNNT_OK;
 }
@@ -465,18 +465,18 @@ extern "C" int frnnt_mi_backward(int dtype, const void *px, const void *py,
     dim3 grid((unsigned)min(64, (S * T + 255) / 256), (unsigned)B);
     if (dtype == FRNNT_F32) {
       if (modified)
-        mi_branch_from_p_kernel<float, true><<<grid, 256, 0, st>>>(
-            (const float *)px, (const float *)p, boundary, (float *)branch, S, T);
+        FRNNT_KERNEL(mi_branch_from_p_kernel<float, true><<<grid, 256, 0, st>>>(
+            (const float *)px, (const float *)p, boundary, (float *)branch, S, T));
       else
-        mi_branch_from_p_kernel<float, false><<<grid, 256, 0, st>>>(
-            (const float *)px, (const float *)p, boundary, (float *)branch, S, T);
+        FRNNT_KERNEL(mi_branch_from_p_kernel<float, false><<<grid, 256, 0, st>>>(
+            (const float *)px, (const float *)p, boundary, (float *)branch, S, T));
     } else {
       if (modified)
-        mi_branch_from_p_kernel<double, true><<<grid, 256, 0, st>>>(
-            (const double *)px, (const double *)p, boundary, (double *)branch, S, T);
+        FRNNT_KERNEL(mi_branch_from_p_kernel<double, true><<<grid, 256, 0, st>>>(
+            (const double *)px, (const double *)p, boundary, (double *)branch, S, T));
       else
-        mi_branch_from_p_kernel<double, false><<<grid, 256, 0, st>>>(
-            (const double *)px, (const double *)p, boundary, (double *)branch, S, T);
+        FRNNT_KERNEL(mi_branch_from_p_kernel<double, false><<<grid, 256, 0, st>>>(
+            (const double *)px, (const double *)p, boundary, (double *)branch, S, T));
     }
     FRNNT_CUDA(cudaGetLastError());
   }

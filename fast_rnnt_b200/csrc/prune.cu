@@ -169,14 +169,14 @@ extern "C" int frnnt_prune_ranges(int dtype, const void *px_grad, const void *py
     auto kern = prune_ranges_kernel<float>;
     if (smem > 48 * 1024)
       FRNNT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<B, kPruneThreads, smem, st>>>((const float *)px_grad, (const float *)py_grad, boundary,
-                                         ranges, S, T, T1, s_range);
+    FRNNT_KERNEL(kern<<<B, kPruneThreads, smem, st>>>((const float *)px_grad, (const float *)py_grad, boundary,
+                                         ranges, S, T, T1, s_range));
   } else {
     auto kern = prune_ranges_kernel<double>;
     if (smem > 48 * 1024)
       FRNNT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<B, kPruneThreads, smem, st>>>((const double *)px_grad, (const double *)py_grad,
-                                         boundary, ranges, S, T, T1, s_range);
+    FRNNT_KERNEL(kern<<<B, kPruneThreads, smem, st>>>((const double *)px_grad, (const double *)py_grad,
+                                         boundary, ranges, S, T, T1, s_range));
   }
   FRNNT_CUDA(cudaGetLastError());
   return FRNNT_OK;
@@ -194,14 +194,14 @@ extern "C" int frnnt_prune_gather(int dtype, const void *lm, const int64_t *rang
   long long want = (rows + 7) / 8;
   const int grid = (int)(want < 148LL * 32 ? want : 148LL * 32);
   if (row_bytes % 16 == 0 && (uintptr_t)lm % 16 == 0 && (uintptr_t)out % 16 == 0) {
-    prune_gather_kernel<float4><<<grid, 256, 0, st>>>((const float4 *)lm, ranges, (float4 *)out,
-                                                     rows, T * R, S1, (int)(row_bytes / 16));
+    FRNNT_KERNEL(prune_gather_kernel<float4><<<grid, 256, 0, st>>>((const float4 *)lm, ranges, (float4 *)out,
+                                                     rows, T * R, S1, (int)(row_bytes / 16)));
   } else if (dtype == FRNNT_F32) {
-    prune_gather_kernel<float><<<grid, 256, 0, st>>>((const float *)lm, ranges, (float *)out, rows,
-                                                    T * R, S1, D);
+    FRNNT_KERNEL(prune_gather_kernel<float><<<grid, 256, 0, st>>>((const float *)lm, ranges, (float *)out, rows,
+                                                    T * R, S1, D));
   } else {
-    prune_gather_kernel<double><<<grid, 256, 0, st>>>((const double *)lm, ranges, (double *)out,
-                                                     rows, T * R, S1, D);
+    FRNNT_KERNEL(prune_gather_kernel<double><<<grid, 256, 0, st>>>((const double *)lm, ranges, (double *)out,
+                                                     rows, T * R, S1, D));
   }
   FRNNT_CUDA(cudaGetLastError());
   return FRNNT_OK;
@@ -219,11 +219,11 @@ extern "C" int frnnt_prune_gather_backward(int dtype, const void *out_grad, cons
   cudaStream_t st = (cudaStream_t)stream;
   dim3 grid((unsigned)S1, (unsigned)B);
   if (dtype == FRNNT_F32)
-    prune_gather_backward_kernel<float><<<grid, 128, 0, st>>>((const float *)out_grad, ranges,
-                                                             (float *)lm_grad, T * R, S1, D);
+    FRNNT_KERNEL(prune_gather_backward_kernel<float><<<grid, 128, 0, st>>>((const float *)out_grad, ranges,
+                                                             (float *)lm_grad, T * R, S1, D));
   else
-    prune_gather_backward_kernel<double><<<grid, 128, 0, st>>>((const double *)out_grad, ranges,
-                                                              (double *)lm_grad, T * R, S1, D);
+    FRNNT_KERNEL(prune_gather_backward_kernel<double><<<grid, 128, 0, st>>>((const double *)out_grad, ranges,
+                                                              (double *)lm_grad, T * R, S1, D));
   FRNNT_CUDA(cudaGetLastError());
   return FRNNT_OK;
 }

@@ -305,8 +305,8 @@ static int launch_contraction(const Prob &prob, int M, int N, int B, cudaStream_
   using Cfg = TileCfg<real>;
   dim3 grid((unsigned)((N + Cfg::BN - 1) / Cfg::BN), (unsigned)((M + Cfg::BM - 1) / Cfg::BM),
             (unsigned)B);
-  contraction_kernel<real, Cfg::BM, Cfg::BN, Cfg::BK, Cfg::TM, Cfg::TN, Prob>
-      <<<grid, (Cfg::BM / Cfg::TM) * (Cfg::BN / Cfg::TN), 0, st>>>(prob);
+  FRNNT_KERNEL(contraction_kernel<real, Cfg::BM, Cfg::BN, Cfg::BK, Cfg::TM, Cfg::TN, Prob>
+               <<<grid, (Cfg::BM / Cfg::TM) * (Cfg::BN / Cfg::TN), 0, st>>>(prob));
   FRNNT_CUDA(cudaGetLastError());
   return FRNNT_OK;
 }
@@ -585,25 +585,25 @@ static int simple_forward_impl(const void *lm_, const void *am_, const int64_t *
   real *loguni = (real *)(svb + sv.loguni), *partial = (real *)(scb + sc.partial);
   const long long lm_rows = (long long)B * S1, am_rows = (long long)B * T;
 
-  row_stats_kernel<real><<<warps_grid(lm_rows), 256, 0, st>>>(lm, lmmax, lmsum, lm_rows, C);
+  FRNNT_KERNEL(row_stats_kernel<real><<<warps_grid(lm_rows), 256, 0, st>>>(lm, lmmax, lmsum, lm_rows, C));
   // the am row sums land in the (not yet used) am-only buffer and are overwritten below
-  row_stats_kernel<real><<<warps_grid(am_rows), 256, 0, st>>>(am, ammax, amonly, am_rows, C);
+  FRNNT_KERNEL(row_stats_kernel<real><<<warps_grid(am_rows), 256, 0, st>>>(am, ammax, amonly, am_rows, C));
   FRNNT_CUDA(cudaGetLastError());
   if (cfg.smoothed) {
     const int nchunk = (int)((lm_rows + kColChunkRows - 1) / kColChunkRows);
     dim3 g1((unsigned)((C + 127) / 128), (unsigned)nchunk);
-    column_partial_kernel<real, 0><<<g1, 128, 0, st>>>(lm, lmmax, lmsum, nullptr, partial, lm_rows, C);
-    unigram_final_kernel<real><<<(C + 127) / 128, 128, 0, st>>>(partial, nchunk, lm_rows, C, uni, loguni);
-    am_only_norm_kernel<real><<<warps_grid(am_rows), 256, 0, st>>>(am, ammax, uni, amonly, am_rows, C);
+    FRNNT_KERNEL(column_partial_kernel<real, 0><<<g1, 128, 0, st>>>(lm, lmmax, lmsum, nullptr, partial, lm_rows, C));
+    FRNNT_KERNEL(unigram_final_kernel<real><<<(C + 127) / 128, 128, 0, st>>>(partial, nchunk, lm_rows, C, uni, loguni));
+    FRNNT_KERNEL(am_only_norm_kernel<real><<<warps_grid(am_rows), 256, 0, st>>>(am, ammax, uni, amonly, am_rows, C));
     FRNNT_CUDA(cudaGetLastError());
   }
   NormProb<real> prob{lm, am, lmmax, ammax, norm, S1, T, C};
   int rc = launch_contraction<real>(prob, S1, T, B, st);
   if (rc != FRNNT_OK) return rc;
   dim3 g2((unsigned)((T + 1 + 127) / 128), (unsigned)S1, (unsigned)B);
-  assemble_kernel<real><<<g2, 128, 0, st>>>(lm, am, symbols, boundary, norm, lmmax, lmsum, amonly,
+  FRNNT_KERNEL(assemble_kernel<real><<<g2, 128, 0, st>>>(lm, am, symbols, boundary, norm, lmmax, lmsum, amonly,
                                             loguni, (real *)px, (real *)py, S, T, C, blank,
-                                            rnnt_type, cfg);
+                                            rnnt_type, cfg));
   FRNNT_CUDA(cudaGetLastError());
   return FRNNT_OK;
 }
@@ -635,29 +635,29 @@ static int simple_backward_impl(const void *lm_, const void *am_, const int64_t 
 
   dim3 g3((unsigned)((T + 127) / 128), (unsigned)S1, (unsigned)B);
   if (T > 0)
-    grad_weight_kernel<real><<<g3, 128, 0, st>>>(eg, norm, lmmax, ammax, rw, (real)cfg.both);
-  grad_row_sums_kernel<real><<<(int)((lm_rows * 32 + 255) / 256), 256, 0, st>>>(eg, sgx, sgy, B);
+    FRNNT_KERNEL(grad_weight_kernel<real><<<g3, 128, 0, st>>>(eg, norm, lmmax, ammax, rw, (real)cfg.both));
+  FRNNT_KERNEL(grad_row_sums_kernel<real><<<(int)((lm_rows * 32 + 255) / 256), 256, 0, st>>>(eg, sgx, sgy, B));
   if (T > 0)
-    grad_col_sums_kernel<real><<<(int)((am_rows + 127) / 128), 128, 0, st>>>(eg, cgx, cgy, B);
+    FRNNT_KERNEL(grad_col_sums_kernel<real><<<(int)((am_rows + 127) / 128), 128, 0, st>>>(eg, cgx, cgy, B));
   FRNNT_CUDA(cudaGetLastError());
 
   const real *gl_p = nullptr, *h_p = nullptr, *dp_p = nullptr, *rowdot_p = nullptr;
   if (cfg.smoothed) {
     // gl[b,s] = ls * (sgx + sgy);  h[b,t] = as * (cgx + cgy)
-    scaled_sum_kernel<real><<<(int)((lm_rows + 255) / 256), 256, 0, st>>>(sgx, sgy, gl, (real)cfg.ls,
-                                                                      lm_rows);
+    FRNNT_KERNEL(scaled_sum_kernel<real><<<(int)((lm_rows + 255) / 256), 256, 0, st>>>(sgx, sgy, gl, (real)cfg.ls,
+                                                                      lm_rows));
     gl_p = gl;
     if (am_only_active && T > 0) {
-      scaled_sum_kernel<real><<<(int)((am_rows + 255) / 256), 256, 0, st>>>(cgx, cgy, h, (real)cfg.as,
-                                                                        am_rows);
+      FRNNT_KERNEL(scaled_sum_kernel<real><<<(int)((am_rows + 255) / 256), 256, 0, st>>>(cgx, cgy, h, (real)cfg.as,
+                                                                        am_rows));
       h_p = h;
       const int nchunk = (int)((am_rows + kColChunkRows - 1) / kColChunkRows);
       dim3 g1((unsigned)((C + 127) / 128), (unsigned)nchunk);
-      column_partial_kernel<real, 1><<<g1, 128, 0, st>>>(am, ammax, amonly, h, partial, am_rows, C);
-      unigram_grad_kernel<real><<<(C + 127) / 128, 128, 0, st>>>(symbols, sgx, sgy, partial, nchunk,
-                                                            uni, dp, B, S, C, blank, (real)cfg.as);
-      row_dot_kernel<real><<<(int)((lm_rows * 32 + 255) / 256), 256, 0, st>>>(lm, lmmax, lmsum, dp,
-                                                                         rowdot, lm_rows, C);
+      FRNNT_KERNEL(column_partial_kernel<real, 1><<<g1, 128, 0, st>>>(am, ammax, amonly, h, partial, am_rows, C));
+      FRNNT_KERNEL(unigram_grad_kernel<real><<<(C + 127) / 128, 128, 0, st>>>(symbols, sgx, sgy, partial, nchunk,
+                                                            uni, dp, B, S, C, blank, (real)cfg.as));
+      FRNNT_KERNEL(row_dot_kernel<real><<<(int)((lm_rows * 32 + 255) / 256), 256, 0, st>>>(lm, lmmax, lmsum, dp,
+                                                                         rowdot, lm_rows, C));
       dp_p = dp;
       rowdot_p = rowdot;
     }
@@ -673,10 +673,10 @@ static int simple_backward_impl(const void *lm_, const void *am_, const int64_t 
 
   const real coef_lm = (real)cfg.both + (real)cfg.ls;
   const real coef_am = (real)cfg.both + (am_only_active || !cfg.smoothed ? (real)cfg.as : (real)0);
-  lm_onehot_kernel<real><<<(int)((lm_rows + 127) / 128), 128, 0, st>>>(symbols, sgx, sgy, lm_grad, B, S, C,
-                                                                   blank, coef_lm);
-  am_onehot_kernel<real><<<(int)((am_rows + 127) / 128), 128, 0, st>>>(eg, symbols, cgy, am_grad, B, C,
-                                                                   blank, coef_am);
+  FRNNT_KERNEL(lm_onehot_kernel<real><<<(int)((lm_rows + 127) / 128), 128, 0, st>>>(symbols, sgx, sgy, lm_grad, B, S, C,
+                                                                   blank, coef_lm));
+  FRNNT_KERNEL(am_onehot_kernel<real><<<(int)((am_rows + 127) / 128), 128, 0, st>>>(eg, symbols, cgy, am_grad, B, C,
+                                                                   blank, coef_am));
   FRNNT_CUDA(cudaGetLastError());
   return FRNNT_OK;
 }

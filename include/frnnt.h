@@ -51,6 +51,10 @@ int frnnt_version(void);
 /* Message of the last failure on this thread ("" if none). */
 const char *frnnt_last_error(void);
 
+/* Number of CUDA kernels this library has launched in this process so far
+ * (diagnostic; no counterpart in the reference). */
+long long frnnt_launch_count(void);
+
 /* Replaces the pybind function with_cuda()
  * (fast_rnnt/python/csrc/mutual_information.cu:69-75): always 1. */
 int frnnt_with_cuda(void);
