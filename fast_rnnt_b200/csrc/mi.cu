@@ -27,6 +27,8 @@
 //   * gradients leave through the same kind of skewed ring, written back as
 //     contiguous row segments by the storer warps, which also write the exact
 //     zeros outside the boundary box.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace frnnt {
@@ -406,6 +408,36 @@ static int mi_check_sizes(int dtype, int B, int S, int T, int modified, int *ncw
   return FRNNT_OK;
 }
 
+// -----------------------------------------------------------------------------
+// scratch for the entry point that allocates nothing
+// -----------------------------------------------------------------------------
+// A fixed region of device memory that belongs to the library image: it exists
+// on every GPU whose context loads the library, from load until the process
+// ends.  Host code may not use the symbol as a pointer (on the host it is only
+// a stand-in); its device address is looked up once per device below.
+static __device__ __align__(256) unsigned char g_mi_static_scratch[FRNNT_MI_NOALLOC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+static std::mutex g_static_mutex;
+static void *g_static_ptr[kMaxDevices] = {nullptr};
+
+// Device address of the static scratch on the CURRENT device (looked up on the
+// first call per device, with that device current).
+static int static_scratch_address(void **out) {
+  int dev = -1;
+  FRNNT_CUDA(cudaGetDevice(&dev));
+  FRNNT_REQUIRE(dev >= 0 && dev < kMaxDevices, FRNNT_EUNSUPPORTED, "device index %d too large", dev);
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (g_static_ptr[dev] == nullptr) {
+    void *ptr = nullptr;
+    FRNNT_CUDA(cudaGetSymbolAddress(&ptr, g_mi_static_scratch));
+    FRNNT_REQUIRE(ptr != nullptr, FRNNT_ECUDA, "cudaGetSymbolAddress returned a null address");
+    g_static_ptr[dev] = ptr;
+  }
+  *out = g_static_ptr[dev];
+  return FRNNT_OK;
+}
+
 }  // namespace frnnt
 
 using namespace frnnt;
@@ -482,4 +514,30 @@ extern "C" int frnnt_mi_backward(int dtype, const void *px, const void *py,
   }
   return frnnt_mi_backward_from_branch(dtype, branch, boundary, ans_grad, px_grad, py_grad,
                                        origin_grad, B, S, T, modified, stream);
+}
+
+extern "C" int frnnt_mi_fwd_bwd_noalloc(int dtype, const void *px, const void *py,
+                                        const int64_t *boundary, const void *ans_grad, void *ans,
+                                        void *px_grad, void *py_grad, int B, int S, int T,
+                                        int modified, void *stream) {
+  int ncw = 0;
+  int rc = mi_check_sizes(dtype, B, S, T, modified, &ncw);
+  if (rc != FRNNT_OK) return rc;
+  const size_t need = frnnt_mi_branch_bytes(dtype, B, S, T);
+  FRNNT_REQUIRE(need <= (size_t)FRNNT_MI_NOALLOC_SCRATCH_BYTES, FRNNT_EUNSUPPORTED,
+                "lattice B=%d S=%d T=%d needs %zu bytes of scratch, the built-in region holds %zu; "
+                "use frnnt_mi_forward + frnnt_mi_backward_from_branch with your own buffer",
+                B, S, T, need, (size_t)FRNNT_MI_NOALLOC_SCRATCH_BYTES);
+  if (B == 0) return FRNNT_OK;
+  FRNNT_REQUIRE(ans != nullptr && ans_grad != nullptr, FRNNT_EINVAL, "ans or ans_grad is NULL");
+  void *scratch = nullptr;
+  rc = static_scratch_address(&scratch);
+  if (rc != FRNNT_OK) return rc;
+  // Nothing in the region has to start at zero: the forward sweep writes every
+  // weight that the backward sweep reads, so the previous call's contents are
+  // simply overwritten.
+  rc = frnnt_mi_forward(dtype, px, py, boundary, nullptr, ans, scratch, B, S, T, modified, stream);
+  if (rc != FRNNT_OK) return rc;
+  return frnnt_mi_backward_from_branch(dtype, scratch, boundary, ans_grad, px_grad, py_grad,
+                                       nullptr, B, S, T, modified, stream);
 }

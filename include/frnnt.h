@@ -99,6 +99,39 @@ int frnnt_mi_backward(int dtype, const void *px, const void *py, const int64_t *
                       void *origin_grad, void *branch, int B, int S, int T, int modified,
                       void *stream);
 
+/* Size of the scratch region built into the library for frnnt_mi_fwd_bwd_noalloc. */
+#define FRNNT_MI_NOALLOC_SCRATCH_BYTES (32u << 20)
+
+/* Forward + reverse sweep in one call, for callers that may not allocate.
+ * (No counterpart in the reference, whose extension allocates its outputs and
+ * its p_grad work array itself.)
+ *
+ * Who needs it: a host program that hands this library a fixed set of buffers
+ * and cannot obtain one more -- e.g. a C/C++ training or scoring loop that
+ * carved up all of its device memory at start-up, or a plugin host that bans
+ * cudaMalloc after initialisation because an allocation stalls every stream of
+ * the device.  frnnt_mi_forward / frnnt_mi_backward_from_branch need a
+ * caller-provided scratch of frnnt_mi_branch_bytes(); this entry point instead
+ * keeps the per-cell weights in a region of FRNNT_MI_NOALLOC_SCRATCH_BYTES
+ * (32 MiB) that is part of the library image: every GPU that loads the library
+ * holds those 32 MiB from load until the process exits.
+ *
+ *   - inputs px, py, boundary, ans_grad [B] and outputs ans [B], px_grad, py_grad
+ *     are the caller's, exactly as for the two functions it combines;
+ *   - a lattice with frnnt_mi_branch_bytes(dtype,B,S,T) above the limit is
+ *     refused with FRNNT_EUNSUPPORTED before anything is launched;
+ *   - it calls no cudaMalloc / cudaFree and no allocating library routine;
+ *   - the FIRST call on each device looks up the region's device address (with
+ *     that device current); make that first call outside of any stream capture;
+ *   - all calls on a device share the one region, which still holds the previous
+ *     call's weights when the next call starts (nothing needs clearing: each
+ *     call overwrites what it later reads).  Two calls whose kernels overlap on
+ *     the GPU (different streams, or different host threads on different
+ *     streams) race on it: issue them on one stream, or order them yourself. */
+int frnnt_mi_fwd_bwd_noalloc(int dtype, const void *px, const void *py, const int64_t *boundary,
+                             const void *ans_grad, void *ans, void *px_grad, void *py_grad,
+                             int B, int S, int T, int modified, void *stream);
+
 /* ----------------------------------------------------------------------------
  * Log-prob lattices from factorised encoder / decoder outputs ("simple" loss)
  * ------------------------------------------------------------------------- */
