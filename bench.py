@@ -219,7 +219,7 @@ def stage_table(fr, wl, dev, flush, hbm_gbs):
     pxd, pyd = px.detach(), py.detach()
     _, _, branch = mi.mi_forward(pxd, pyd, t["boundary"])
     ones = torch.ones(B, device=dev)
-    ox, oy = mi.mi_backward_from_branch(branch, t["boundary"], ones, px.shape, py.shape, px.dtype)
+    ox, oy = mi.mi_backward_from_lattice(pxd, branch, t["boundary"], ones, py.shape)
     ranges = fr.get_rnnt_prune_ranges(px_grad=ox, py_grad=oy, boundary=t["boundary"], s_range=R)
     dec = t["dec"].clone().requires_grad_(True)
     _, lm_p = fr.do_rnnt_pruning(am=t["enc"], lm=dec, ranges=ranges)
@@ -242,12 +242,12 @@ def stage_table(fr, wl, dev, flush, hbm_gbs):
          lambda: torch.autograd.grad((px, py), (lm, am), (gpx, gpy), retain_graph=True),
          2 * es * B * (T + S + 1) * C + lat, 4.0 * B * (S + 1) * T * C),
         ("mi_forward", lambda: mi.mi_forward(pxd, pyd, t["boundary"]), 12 * cells_box, None),
-        ("mi_backward", lambda: mi.mi_backward_from_branch(branch, t["boundary"], ones, px.shape,
-                                                           py.shape, px.dtype), 4 * cells_box + lat, None),
+        ("mi_backward", lambda: mi.mi_backward_from_lattice(pxd, branch, t["boundary"], ones,
+                                                            py.shape), 8 * cells_box + lat, None),
         ("mi_forward_pruned", lambda: mi.mi_forward(ppxd, ppyd, t["boundary"]), 12 * cells_box, None),
-        ("mi_backward_pruned", lambda: mi.mi_backward_from_branch(pbranch, t["boundary"], ones,
-                                                                  px.shape, py.shape, px.dtype),
-         4 * cells_box + lat, None),
+        ("mi_backward_pruned", lambda: mi.mi_backward_from_lattice(ppxd, pbranch, t["boundary"],
+                                                                   ones, py.shape),
+         8 * cells_box + lat, None),
         ("prune_ranges", lambda: fr.get_rnnt_prune_ranges(px_grad=ox, py_grad=oy,
                                                           boundary=t["boundary"], s_range=R),
          lat + 8 * B * T * R, None),

@@ -31,7 +31,7 @@ def lib():
                 "(needs nvcc; sm_100a). There is no CPU or PyTorch fallback.")
         _lib = ctypes.CDLL(LIB_PATH)
         _lib.frnnt_last_error.restype = ctypes.c_char_p
-        for name in ("frnnt_mi_branch_bytes", "frnnt_simple_saved_bytes",
+        for name in ("frnnt_mi_lattice_bytes", "frnnt_simple_saved_bytes",
                      "frnnt_simple_scratch_bytes"):
             if hasattr(_lib, name):
                 getattr(_lib, name).restype = _c_sz

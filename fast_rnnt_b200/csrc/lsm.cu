@@ -134,14 +134,14 @@ lsm_rows_forward_kernel(const real *__restrict__ logits, const int64_t *__restri
         const int v = lig + j * GROUP;
         if (valid && v < nvec) {
 #pragma unroll
-          for (int e = 0; e < VW; ++e) sum += exp_r(elem<real>(reg[j], e) - m0);
+          for (int e = 0; e < VW; ++e) sum += exp_sum(elem<real>(reg[j], e) - m0);
         }
       }
     } else if (valid) {
       for (int v = lig; v < nvec; v += GROUP) {
         const vec x = src[v];
 #pragma unroll
-        for (int e = 0; e < VW; ++e) sum += exp_r(elem<real>(x, e) - m0);
+        for (int e = 0; e < VW; ++e) sum += exp_sum(elem<real>(x, e) - m0);
       }
     }
     sum = group_reduce<real, GROUP>(sum, false, scratch, gid, lig);
@@ -241,7 +241,7 @@ lsm_rows_backward_kernel(const real *__restrict__ logits, const int64_t *__restr
 #pragma unroll
       for (int e = 0; e < VW; ++e) {
         const int c = v * VW + e;
-        real g = neg * exp_r(elem<real>(x, e) - l);
+        real g = neg * exp_sum(elem<real>(x, e) - l);
         if (c == y) g += gx;
         if (c == blank) g += gy;
         set_elem(o, e, g);

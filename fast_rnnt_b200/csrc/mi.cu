@@ -11,21 +11,24 @@
 //
 // How it is mapped to the GPU (not the reference's tile-per-launch scheme):
 //   * one CTA per utterance, ONE launch per sweep;
-//   * thread i owns lattice row s0+i; at step k all threads work on
-//     anti-diagonal k (cell (i, k-i)), so the "row above" value arrives by a
-//     warp shuffle and the "column before" value stays in a register;
-//   * the hand-off between the last lane of a warp and the first lane of the
-//     next goes through a 4-deep shared-memory slot and one named barrier per
-//     step among the compute warps only;
+//   * thread i owns lattice row s0+i; at step k it works on anti-diagonal k
+//     (cell (i, k-i)), so the "row above" value arrives by a warp shuffle and the
+//     "column before" value stays in a register;
+//   * between the last lane of a warp and the first lane of the next the value
+//     travels through shared memory.  float: a 64-bit word {step tag, value} per
+//     step that the consumer polls (bounded), so the warps run as a pipeline and
+//     never meet at a per-step barrier.  double: a value ring plus one named
+//     barrier per step among the compute warps;
 //   * px / py are re-laid by dedicated loader warps into a skewed shared-memory
 //     ring (row i, diagonal k), 32 diagonals per chunk, double buffered: global
 //     reads are contiguous row segments, ring reads by the diagonal are
 //     bank-conflict free (pitch 33);
-//   * the forward sweep stores d1 for every cell in a diagonal-major scratch
-//     ("branch"), fully coalesced; the backward sweep then needs neither exp()
-//     nor p, and its dependent chain per step is shuffle + add + multiply;
+//   * the forward sweep stores p by anti-diagonal in a scratch ("lattice"),
+//     fully coalesced.  In the backward sweep the helper warps turn it into the
+//     weights d1 (the only exp() of the backward) one chunk ahead of the compute
+//     warps, whose dependent chain per step is shuffle + add + multiply;
 //   * gradients leave through the same kind of skewed ring, written back as
-//     contiguous row segments by the storer warps, which also write the exact
+//     contiguous row segments by the helper warps, which also write the exact
 //     zeros outside the boundary box.
 #include <mutex>
 
@@ -36,7 +39,8 @@ namespace frnnt {
 constexpr int kChunk = 32;      // anti-diagonals staged per chunk
 constexpr int kPitch = 33;      // ring row pitch in elements
 constexpr int kIoWarps = 4;     // loader / storer warps per CTA
-constexpr int kMaxComputeWarps = 8;
+constexpr int kHandRing = 64;   // hand-off slots per warp (two chunks deep)
+constexpr int kSpinLimit = 1 << 22;
 
 struct MiBox {
   int s0, t0, sb, tb;  // origin and extents (s_end - s_begin, t_end - t_begin)
@@ -57,13 +61,83 @@ __device__ __forceinline__ MiBox load_box(const int64_t *boundary, int b, int S,
   return box;
 }
 
-__host__ __device__ inline int branch_pitch(int S) { return (S + 1 + 31) & ~31; }
-__host__ __device__ inline size_t branch_elems_per_utt(int S, int T) {
-  return (size_t)(S + T + 1) * branch_pitch(S);
+// lattice scratch: p by anti-diagonal, [B][S+T+1][pitch]
+__host__ __device__ inline int lattice_pitch(int S) { return (S + 1 + 31) & ~31; }
+__host__ __device__ inline size_t lattice_elems_per_utt(int S, int T) {
+  return (size_t)(S + T + 1) * lattice_pitch(S);
 }
 
 __device__ __forceinline__ void bar_sync_named(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// ---- asynchronous global -> shared copies of single elements ---------------------
+// (the loader warps keep dozens of these in flight; a plain load + store loop
+// would wait a full memory latency per element)
+template <typename real>
+__device__ __forceinline__ void async_copy_or_zero(real *smem_dst, const real *gsrc, bool valid) {
+  const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+  const int src_bytes = valid ? (int)sizeof(real) : 0;  // 0 -> the destination is zero-filled
+  if (sizeof(real) == 4)
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(gsrc), "r"(src_bytes)
+                 : "memory");
+  else
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(dst), "l"(gsrc), "r"(src_bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void async_copy_wait_all() {
+  asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
+}
+
+// ---- hand-off between neighbouring warps --------------------------------------
+// float: tagged 64-bit slots, polled.  double: plain slots + a barrier per step.
+template <typename real> struct Hand;
+
+template <> struct Hand<float> {
+  static constexpr bool kBarrier = false;
+  using slot_t = unsigned long long;
+  static constexpr int kSlotsPerWarp = kHandRing;
+  __device__ static void init(volatile slot_t *q, int n, float) {
+    for (int j = threadIdx.x; j < n; j += blockDim.x) q[j] = ~0ull;
+  }
+  __device__ static void put(volatile slot_t *q, int warp, int step, float v) {
+    q[warp * kHandRing + (step & (kHandRing - 1))] =
+        ((unsigned long long)(unsigned)step << 32) | (unsigned long long)__float_as_uint(v);
+  }
+  // value the neighbour published at `step`; gives up after kSpinLimit polls
+  __device__ static float get(volatile slot_t *q, int warp, int step, volatile int *failed) {
+    volatile slot_t *slot = q + warp * kHandRing + (step & (kHandRing - 1));
+    unsigned long long v = *slot;
+    int spins = 0;
+    while ((unsigned)(v >> 32) != (unsigned)step) {
+      if (++spins > kSpinLimit) {
+        *failed = 1;
+        break;
+      }
+      v = *slot;
+    }
+    return __uint_as_float((unsigned)v);
+  }
+};
+
+template <> struct Hand<double> {
+  static constexpr bool kBarrier = true;
+  using slot_t = double;
+  static constexpr int kSlotsPerWarp = 4;
+  __device__ static void init(volatile slot_t *q, int n, double fill) {
+    for (int j = threadIdx.x; j < n; j += blockDim.x) q[j] = fill;
+  }
+  __device__ static void put(volatile slot_t *q, int warp, int step, double v) {
+    q[warp * 4 + (step & 3)] = v;
+  }
+  __device__ static double get(volatile slot_t *q, int warp, int step, volatile int *) {
+    return q[warp * 4 + (step & 3)];
+  }
+};
+
+template <typename real, int NCW>
+__host__ __device__ constexpr size_t hand_bytes() {
+  return (size_t)NCW * Hand<real>::kSlotsPerWarp * sizeof(typename Hand<real>::slot_t);
 }
 
 // -----------------------------------------------------------------------------
@@ -73,12 +147,15 @@ template <typename real, int NCW, bool MODIFIED>
 __global__ void __launch_bounds__((NCW + kIoWarps) * 32)
 mi_forward_kernel(const real *__restrict__ px, const real *__restrict__ py,
                   const int64_t *__restrict__ boundary, real *__restrict__ p,
-                  real *__restrict__ ans, real *__restrict__ branch, int S, int T) {
+                  real *__restrict__ ans, real *__restrict__ lattice, int S, int T) {
   constexpr int ROWS = NCW * 32;
+  using H = Hand<real>;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   real *ringx = reinterpret_cast<real *>(smem_raw);  // [2][ROWS][kPitch]
   real *ringy = ringx + 2 * ROWS * kPitch;           // [2][ROWS][kPitch]
-  real *xchg = ringy + 2 * ROWS * kPitch;            // [4][NCW]
+  volatile typename H::slot_t *hand =
+      reinterpret_cast<volatile typename H::slot_t *>(ringy + 2 * ROWS * kPitch);
+  __shared__ int failed;
 
   const int b = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -90,37 +167,40 @@ mi_forward_kernel(const real *__restrict__ px, const real *__restrict__ py,
   const real *X = px + (size_t)b * S * T1;
   const real *Y = py + (size_t)b * (S + 1) * T;
   real *P = p ? p + (size_t)b * (S + 1) * (T + 1) : nullptr;
-  const int bpitch = branch_pitch(S);
-  real *BR = branch ? branch + (size_t)b * branch_elems_per_utt(S, T) : nullptr;
+  const int lpitch = lattice_pitch(S);
   const bool is_io = warp >= NCW;
   const real ninf = neg_inf<real>();
 
-  if (threadIdx.x < 4 * NCW) xchg[threadIdx.x] = ninf;
+  H::init(hand, NCW * H::kSlotsPerWarp, ninf);
+  if (threadIdx.x == 0) failed = 0;
 
   // ring[slot][i][j] holds, for consumer cell (row i, diagonal 32c+j):
   //   x = px[s0+i-1][t0+t'+o]   and   y = py[s0+i][t0+t'-1],   t' = 32c+j-i
   auto load_chunk = [&](int c) {
     const int slot = c & 1;
     const int k = c * kChunk + lane;
-#pragma unroll 4
     for (int i = warp - NCW; i <= box.sb; i += kIoWarps) {
       const int tp = k - i;
-      real vx = 0, vy = 0;
-      if (tp >= 0 && tp <= box.tb) {
-        if (i >= 1 && tp + off >= 0)
-          vx = X[(size_t)(box.s0 + i - 1) * T1 + (box.t0 + tp + off)];
-        if (tp >= 1) vy = Y[(size_t)(box.s0 + i) * T + box.t0 + tp - 1];
-      }
-      ringx[(slot * ROWS + i) * kPitch + lane] = vx;
-      ringy[(slot * ROWS + i) * kPitch + lane] = vy;
+      const bool in_box = tp >= 0 && tp <= box.tb;
+      const bool vx = in_box && i >= 1 && tp + off >= 0;
+      const bool vy = in_box && tp >= 1;
+      async_copy_or_zero(&ringx[(slot * ROWS + i) * kPitch + lane],
+                         vx ? X + (size_t)(box.s0 + i - 1) * T1 + (box.t0 + tp + off) : X, vx);
+      async_copy_or_zero(&ringy[(slot * ROWS + i) * kPitch + lane],
+                         vy ? Y + (size_t)(box.s0 + i) * T + box.t0 + tp - 1 : Y, vy);
     }
+    async_copy_wait_all();
   };
 
   if (is_io) load_chunk(0);
   __syncthreads();
 
-  const int i = threadIdx.x;     // lattice row (compute threads only)
-  real p_cur = ninf, p_old = ninf;  // this row's cells at t'-1 and t'-2
+  const int i = threadIdx.x;          // lattice row (compute threads only)
+  const bool row_ok = i <= box.sb;
+  const int k_first = i, k_last = i + box.tb;  // this row is active for k in [k_first, k_last]
+  real p_cur = ninf, p_old = ninf;    // this row's cells at t'-1 and t'-2
+  real p_last = ninf;                 // the last active value (the answer for row sb)
+  real *L = lattice ? lattice + (size_t)b * lattice_elems_per_utt(S, T) + i : nullptr;
 
   for (int c = 0; c < nchunks; ++c) {
     if (is_io) {
@@ -139,52 +219,56 @@ mi_forward_kernel(const real *__restrict__ px, const real *__restrict__ py,
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
           const int k = c * kChunk + j0 + u;
-          const int tp = k - i;
           // p of the row above: one step back (regular) or two (modified)
           const real hist = MODIFIED ? p_old : p_cur;
           real up = __shfl_up_sync(0xffffffffu, hist, 1);
-          if (NCW > 1 && lane == 0 && warp > 0)
-            up = xchg[((k - 1 + off) & 3) * NCW + warp - 1];
-          const bool active = (i <= box.sb) && tp >= 0 && tp <= box.tb;
+          if (NCW > 1 && lane == 0 && warp > 0) {
+            const int src = k - 1 + off;
+            up = src >= 0 ? H::get(hand, warp - 1, src, &failed) : ninf;
+          }
+          const bool active = row_ok && k >= k_first && k <= k_last;
           const real a = (i > 0) ? up + xv[u] : ninf;
           const real bb = p_cur + yv[u];
           real pn = log_add(a, bb);
-          if (i == 0 && tp == 0) pn = 0;
+          if (k == 0 && i == 0) pn = 0;
           if (!active) pn = ninf;
           if (active) {
-            if (BR != nullptr) {
-              const real tot = (pn - pn != 0) ? (real)0 : pn;
-              BR[(size_t)k * bpitch + i] = exp_r(a - tot);
-            }
-            if (P != nullptr) P[(size_t)(box.s0 + i) * (T + 1) + box.t0 + tp] = pn;
-            if (i == box.sb && tp == box.tb) ans[b] = pn;
+            p_last = pn;
+            if (L != nullptr) L[(size_t)k * lpitch] = pn;
+            if (P != nullptr) P[(size_t)(box.s0 + i) * (T + 1) + box.t0 + (k - i)] = pn;
           }
           p_old = p_cur;
           p_cur = pn;
           if (NCW > 1) {
-            if (lane == 31) xchg[(k & 3) * NCW + warp] = pn;
-            bar_sync_named(1, NCW * 32);
+            if (lane == 31 && warp + 1 < NCW) H::put(hand, warp, k, pn);
+            if (H::kBarrier) bar_sync_named(1, NCW * 32);
           }
         }
       }
     }
     __syncthreads();
   }
+  if (!is_io && i == box.sb) ans[b] = failed ? (real)NAN : p_last;
 }
 
 // -----------------------------------------------------------------------------
-// backward (from the branch weights)
+// backward (from the diagonal-major lattice)
 // -----------------------------------------------------------------------------
 template <typename real, int NCW, bool MODIFIED>
 __global__ void __launch_bounds__((NCW + kIoWarps) * 32)
-mi_backward_kernel(const real *__restrict__ branch, const int64_t *__restrict__ boundary,
-                   const real *__restrict__ ans_grad, real *__restrict__ px_grad,
-                   real *__restrict__ py_grad, real *__restrict__ origin_grad, int S, int T) {
+mi_backward_kernel(const real *__restrict__ px, const real *__restrict__ lattice,
+                   const int64_t *__restrict__ boundary, const real *__restrict__ ans_grad,
+                   real *__restrict__ px_grad, real *__restrict__ py_grad,
+                   real *__restrict__ origin_grad, int S, int T) {
   constexpr int ROWS = NCW * 32;
+  using H = Hand<real>;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  real *ringx = reinterpret_cast<real *>(smem_raw);  // [2][ROWS][kPitch]  d/dpx
+  real *ringd = reinterpret_cast<real *>(smem_raw);  // [2][ROWS][kPitch]  px, then d1
+  real *ringx = ringd + 2 * ROWS * kPitch;           // [2][ROWS][kPitch]  d/dpx
   real *ringy = ringx + 2 * ROWS * kPitch;           // [2][ROWS][kPitch]  d/dpy
-  real *xchg = ringy + 2 * ROWS * kPitch;            // [4][NCW]
+  volatile typename H::slot_t *hand =
+      reinterpret_cast<volatile typename H::slot_t *>(ringy + 2 * ROWS * kPitch);
+  __shared__ int failed;
 
   const int b = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -194,13 +278,66 @@ mi_backward_kernel(const real *__restrict__ branch, const int64_t *__restrict__ 
   const MiBox box = load_box(boundary, b, S, T);
   const int nd = box.sb + box.tb + 1;
   const int nchunks = (nd + kChunk - 1) / kChunk;
+  const real *X = px + (size_t)b * S * T1;
   real *GX = px_grad + (size_t)b * S * T1;
   real *GY = py_grad + (size_t)b * (S + 1) * T;
-  const int bpitch = branch_pitch(S);
-  const real *BR = branch + (size_t)b * branch_elems_per_utt(S, T);
+  const int lpitch = lattice_pitch(S);
+  const real *LT = lattice + (size_t)b * lattice_elems_per_utt(S, T);
   const bool is_io = warp >= NCW;
 
-  if (threadIdx.x < 4 * NCW) xchg[threadIdx.x] = 0;
+  H::init(hand, NCW * H::kSlotsPerWarp, (real)0);
+  if (threadIdx.x == 0) failed = 0;
+
+  // helper warps: weights d1 of chunk c into ringd[c&1].
+  //   step 1 (lane = diagonal): px row segments, contiguous in memory
+  //   step 2 (lane = row): d1 = exp(p[i-1][k-1+o] + px - p[i][k]), p read by diagonal
+  auto weights_chunk = [&](int c) {
+    const int slot = c & 1;
+    const int iw = warp - NCW;
+    {
+      const int k = c * kChunk + lane;
+      for (int i = 1 + iw; i <= box.sb; i += kIoWarps) {
+        const int tp = k - i;
+        const bool v = tp >= 1 && tp <= box.tb;
+        async_copy_or_zero(&ringd[(slot * ROWS + i) * kPitch + lane],
+                           v ? X + (size_t)(box.s0 + i - 1) * T1 + (box.t0 + tp + off) : X, v);
+      }
+      async_copy_wait_all();
+    }
+    bar_sync_named(2, kIoWarps * 32);
+    // all lattice loads of this warp's diagonals are issued before the first exp
+    constexpr int NJ = kChunk / kIoWarps;   // diagonals per helper warp
+    constexpr int NM = NCW;                 // 32-row blocks
+    real up[NJ][NM], tot[NJ][NM];
+#pragma unroll
+    for (int jj = 0; jj < NJ; ++jj) {
+      const int k = c * kChunk + iw + jj * kIoWarps;
+#pragma unroll
+      for (int m = 0; m < NM; ++m) {
+        const int i = lane + 32 * m;
+        const int tp = k - i;
+        const bool v = i >= 1 && i <= box.sb && tp >= 1 && tp <= box.tb;
+        up[jj][m] = v ? LT[(size_t)(k - 1 + off) * lpitch + i - 1] : (real)0;
+        tot[jj][m] = v ? LT[(size_t)k * lpitch + i] : (real)0;
+      }
+    }
+#pragma unroll
+    for (int jj = 0; jj < NJ; ++jj) {
+      const int j = iw + jj * kIoWarps;
+      const int k = c * kChunk + j;
+#pragma unroll
+      for (int m = 0; m < NM; ++m) {
+        const int i = lane + 32 * m;
+        const int tp = k - i;
+        if (i >= 1 && i <= box.sb && tp >= 1 && tp <= box.tb) {
+          real t = tot[jj][m];
+          if (t - t != 0) t = 0;
+          real *cell = ringd + (slot * ROWS + i) * kPitch + j;
+          *cell = exp_r(up[jj][m] + *cell - t);
+        }
+      }
+    }
+  };
 
   // cells (row i, diagonal 32c+j) -> px_grad[s0+i-1][t0+t'+o], py_grad[s0+i][t0+t'-1]
   auto drain_chunk = [&](int c) {
@@ -220,6 +357,7 @@ mi_backward_kernel(const real *__restrict__ branch, const int64_t *__restrict__ 
     }
   };
 
+  if (is_io && nchunks > 0) weights_chunk(nchunks - 1);
   __syncthreads();
 
   if (is_io) {
@@ -241,48 +379,50 @@ mi_backward_kernel(const real *__restrict__ branch, const int64_t *__restrict__ 
   }
 
   const int i = threadIdx.x;
+  const bool row_ok = i <= box.sb;
+  const int k_first = i, k_last = i + box.tb;
   real g1_cur = 0, g1_old = 0;  // x-gradients this row sent up at the last two steps
   real g2_cur = 0;              // y-gradient this row sent left at the last step
   const real g_end = ans_grad[b];
+  const int k_end = box.sb + box.tb;
+  const int k_top = nchunks * kChunk - 1;  // first diagonal the sweep visits
 
   for (int c = nchunks - 1; c >= 0; --c) {
     if (is_io) {
       if (c + 1 < nchunks) drain_chunk(c + 1);
+      if (c >= 1) weights_chunk(c - 1);
     } else {
+      const real *rd = ringd + ((c & 1) * ROWS + i) * kPitch;
       real *rx = ringx + ((c & 1) * ROWS + i) * kPitch;
       real *ry = ringy + ((c & 1) * ROWS + i) * kPitch;
 #pragma unroll 1
       for (int j0 = kChunk - 8; j0 >= 0; j0 -= 8) {
-        real br[8];
+        real dv[8];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const int k = c * kChunk + j0 + u;
-          const int tp = k - i;
-          br[u] = (i >= 1 && i <= box.sb && tp >= 1 && tp <= box.tb)
-                      ? BR[(size_t)k * bpitch + i]
-                      : (real)0;
-        }
+        for (int u = 0; u < 8; ++u) dv[u] = rd[j0 + u];
 #pragma unroll
         for (int u = 7; u >= 0; --u) {
           const int k = c * kChunk + j0 + u;
-          const int tp = k - i;
           const real hist = MODIFIED ? g1_old : g1_cur;
           real below = __shfl_down_sync(0xffffffffu, hist, 1);
-          if (lane == 31)
-            below = (NCW > 1 && warp + 1 < NCW) ? xchg[((k + 1 - off) & 3) * NCW + warp + 1]
-                                                : (real)0;
-          const bool active = (i <= box.sb) && tp >= 0 && tp <= box.tb;
+          if (lane == 31) {
+            const int src = k + 1 - off;
+            below = (NCW > 1 && warp + 1 < NCW && src <= k_top)
+                        ? H::get(hand, warp + 1, src, &failed)
+                        : (real)0;
+          }
+          const bool active = row_ok && k >= k_first && k <= k_last;
           real g = below + g2_cur;
-          if (i == box.sb && tp == box.tb) g = g_end;
+          if (i == box.sb && k == k_end) g = g_end;
           real d1, d2;
           if (i == 0) {  // first row: only a y-predecessor
             d1 = 0;
             d2 = 1;
-          } else if (tp == 0) {  // first column: only an x-predecessor (regular) or none
+          } else if (k == k_first) {  // first column: only an x-predecessor (regular) or none
             d1 = MODIFIED ? 0 : 1;
             d2 = 0;
           } else {
-            d1 = br[u];
+            d1 = dv[u];
             if (d1 - d1 == 0) {
               d2 = (real)1 - d1;
             } else {
@@ -295,15 +435,15 @@ mi_backward_kernel(const real *__restrict__ branch, const int64_t *__restrict__ 
             g1 = 0;
             g2 = 0;
           }
-          if (active && i == 0 && tp == 0 && origin_grad != nullptr) origin_grad[b] = g;
+          if (i == 0 && k == 0 && origin_grad != nullptr) origin_grad[b] = g;
           rx[j0 + u] = g1;
           ry[j0 + u] = g2;
           g1_old = g1_cur;
           g1_cur = g1;
           g2_cur = g2;
           if (NCW > 1) {
-            if (lane == 0) xchg[(k & 3) * NCW + warp] = g1;
-            bar_sync_named(1, NCW * 32);
+            if (lane == 0 && warp > 0) H::put(hand, warp, k, g1);
+            if (H::kBarrier) bar_sync_named(1, NCW * 32);
           }
         }
       }
@@ -311,63 +451,58 @@ mi_backward_kernel(const real *__restrict__ branch, const int64_t *__restrict__ 
     __syncthreads();
   }
   if (is_io && nchunks > 0) drain_chunk(0);
+  if (failed && threadIdx.x == 0 && origin_grad != nullptr) origin_grad[b] = (real)NAN;
 }
 
-// branch weights from a lattice p in the reference's [B][S+1][T+1] layout
-template <typename real, bool MODIFIED>
-__global__ void mi_branch_from_p_kernel(const real *__restrict__ px, const real *__restrict__ p,
-                                        const int64_t *__restrict__ boundary,
-                                        real *__restrict__ branch, int S, int T) {
+// lattice in the reference's [B][S+1][T+1] layout -> diagonal-major scratch
+template <typename real>
+__global__ void mi_lattice_from_p_kernel(const real *__restrict__ p,
+                                         const int64_t *__restrict__ boundary,
+                                         real *__restrict__ lattice, int S, int T) {
   const int b = blockIdx.y;
-  const int T1 = MODIFIED ? T : T + 1;
-  constexpr int off = MODIFIED ? -1 : 0;
   const MiBox box = load_box(boundary, b, S, T);
-  const real *X = px + (size_t)b * S * T1;
   const real *P = p + (size_t)b * (S + 1) * (T + 1);
-  const int bpitch = branch_pitch(S);
-  real *BR = branch + (size_t)b * branch_elems_per_utt(S, T);
-  const int ncell = box.sb * box.tb;  // cells with both predecessors
+  const int lpitch = lattice_pitch(S);
+  real *LT = lattice + (size_t)b * lattice_elems_per_utt(S, T);
+  const int ncell = (box.sb + 1) * (box.tb + 1);
   for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < ncell;
        idx += gridDim.x * blockDim.x) {
-    const int i = 1 + idx / box.tb, tp = 1 + idx % box.tb;
-    const int s = box.s0 + i, t = box.t0 + tp;
-    const real term1 = P[(size_t)(s - 1) * (T + 1) + (t + off)] + X[(size_t)(s - 1) * T1 + (t + off)];
-    real tot = P[(size_t)s * (T + 1) + t];
-    if (tot - tot != 0) tot = 0;
-    BR[(size_t)(i + tp) * bpitch + i] = exp_r(term1 - tot);
+    const int i = idx / (box.tb + 1), tp = idx % (box.tb + 1);
+    LT[(size_t)(i + tp) * lpitch + i] = P[(size_t)(box.s0 + i) * (T + 1) + box.t0 + tp];
   }
 }
 
 // -----------------------------------------------------------------------------
 // host side
 // -----------------------------------------------------------------------------
-template <typename real>
-static size_t mi_smem_bytes(int ncw) {
-  return (size_t)(4 * ncw * 32 * kPitch + 4 * ncw) * sizeof(real);
+template <typename real, int NCW>
+static size_t mi_smem_bytes(int rings) {
+  return (size_t)rings * 2 * NCW * 32 * kPitch * sizeof(real) + hand_bytes<real, NCW>();
 }
 
 template <typename real, int NCW, bool MODIFIED>
 static int launch_forward(const void *px, const void *py, const int64_t *boundary, void *p,
-                          void *ans, void *branch, int B, int S, int T, cudaStream_t st) {
+                          void *ans, void *lattice, int B, int S, int T, cudaStream_t st) {
   auto kern = mi_forward_kernel<real, NCW, MODIFIED>;
-  const size_t smem = mi_smem_bytes<real>(NCW);
+  const size_t smem = mi_smem_bytes<real, NCW>(2);
   FRNNT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  FRNNT_KERNEL(kern<<<B, (NCW + kIoWarps) * 32, smem, st>>>((const real *)px, (const real *)py, boundary,
-                                               (real *)p, (real *)ans, (real *)branch, S, T));
+  FRNNT_KERNEL(kern<<<B, (NCW + kIoWarps) * 32, smem, st>>>((const real *)px, (const real *)py,
+                                                            boundary, (real *)p, (real *)ans,
+                                                            (real *)lattice, S, T));
   FRNNT_CUDA(cudaGetLastError());
   return FRNNT_OK;
 }
 
 template <typename real, int NCW, bool MODIFIED>
-static int launch_backward(const void *branch, const int64_t *boundary, const void *ans_grad,
-                           void *px_grad, void *py_grad, void *origin_grad, int B, int S, int T,
-                           cudaStream_t st) {
+static int launch_backward(const void *px, const void *lattice, const int64_t *boundary,
+                           const void *ans_grad, void *px_grad, void *py_grad, void *origin_grad,
+                           int B, int S, int T, cudaStream_t st) {
   auto kern = mi_backward_kernel<real, NCW, MODIFIED>;
-  const size_t smem = mi_smem_bytes<real>(NCW);
+  const size_t smem = mi_smem_bytes<real, NCW>(3);
   FRNNT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  FRNNT_KERNEL(kern<<<B, (NCW + kIoWarps) * 32, smem, st>>>((const real *)branch, boundary,
-                                               (const real *)ans_grad, (real *)px_grad,
-                                               (real *)py_grad, (real *)origin_grad, S, T));
+  FRNNT_KERNEL(kern<<<B, (NCW + kIoWarps) * 32, smem, st>>>(
+      (const real *)px, (const real *)lattice, boundary, (const real *)ans_grad, (real *)px_grad,
+      (real *)py_grad, (real *)origin_grad, S, T));
   FRNNT_CUDA(cudaGetLastError());
   return FRNNT_OK;
 }
@@ -384,14 +519,24 @@ static int launch_backward(const void *branch, const int64_t *boundary, const vo
     default: return FN<real, 8, MOD>(__VA_ARGS__);                        \
   }
 
+// double rows are capped at 4 warps (the three rings of the backward sweep fill
+// shared memory beyond that), so only those instantiations exist
+#define MI_DISPATCH_NCW_F64(FN, MOD, ncw, ...)                            \
+  switch (ncw) {                                                          \
+    case 1: return FN<double, 1, MOD>(__VA_ARGS__);                       \
+    case 2: return FN<double, 2, MOD>(__VA_ARGS__);                       \
+    case 3: return FN<double, 3, MOD>(__VA_ARGS__);                       \
+    default: return FN<double, 4, MOD>(__VA_ARGS__);                      \
+  }
+
 #define MI_DISPATCH(FN, dtype, modified, ncw, ...)                        \
   do {                                                                    \
     if ((dtype) == FRNNT_F32) {                                           \
       if (modified) { MI_DISPATCH_NCW(FN, float, true, ncw, __VA_ARGS__) }  \
       else { MI_DISPATCH_NCW(FN, float, false, ncw, __VA_ARGS__) }          \
     } else {                                                              \
-      if (modified) { MI_DISPATCH_NCW(FN, double, true, ncw, __VA_ARGS__) } \
-      else { MI_DISPATCH_NCW(FN, double, false, ncw, __VA_ARGS__) }         \
+      if (modified) { MI_DISPATCH_NCW_F64(FN, true, ncw, __VA_ARGS__) }   \
+      else { MI_DISPATCH_NCW_F64(FN, false, ncw, __VA_ARGS__) }           \
     }                                                                     \
   } while (0)
 
@@ -400,7 +545,7 @@ static int mi_check_sizes(int dtype, int B, int S, int T, int modified, int *ncw
                 dtype);
   FRNNT_REQUIRE(B >= 0 && S >= 0 && T >= 0, FRNNT_EINVAL, "negative size B=%d S=%d T=%d", B, S, T);
   FRNNT_REQUIRE(modified == 0 || modified == 1, FRNNT_EINVAL, "modified must be 0 or 1");
-  const int rows_max = (dtype == FRNNT_F64 ? 6 : kMaxComputeWarps) * 32;
+  const int rows_max = (dtype == FRNNT_F64 ? 4 : 8) * 32;
   FRNNT_REQUIRE(S + 1 <= rows_max, FRNNT_EUNSUPPORTED,
                 "S+1=%d exceeds the %d lattice rows one CTA holds for this dtype", S + 1,
                 rows_max);
@@ -442,13 +587,13 @@ static int static_scratch_address(void **out) {
 
 using namespace frnnt;
 
-extern "C" size_t frnnt_mi_branch_bytes(int dtype, int B, int S, int T) {
+extern "C" size_t frnnt_mi_lattice_bytes(int dtype, int B, int S, int T) {
   if (!check_dtype(dtype) || B < 0 || S < 0 || T < 0) return 0;
-  return (size_t)B * branch_elems_per_utt(S, T) * dtype_size(dtype);
+  return (size_t)B * lattice_elems_per_utt(S, T) * dtype_size(dtype);
 }
 
 extern "C" int frnnt_mi_forward(int dtype, const void *px, const void *py,
-                                const int64_t *boundary, void *p, void *ans, void *branch, int B,
+                                const int64_t *boundary, void *p, void *ans, void *lattice, int B,
                                 int S, int T, int modified, void *stream) {
   int ncw = 0;
   int rc = mi_check_sizes(dtype, B, S, T, modified, &ncw);
@@ -458,62 +603,51 @@ extern "C" int frnnt_mi_forward(int dtype, const void *px, const void *py,
   FRNNT_REQUIRE((px != nullptr || S == 0 || (modified && T == 0)) && (py != nullptr || T == 0),
                 FRNNT_EINVAL, "px or py is NULL");
   cudaStream_t st = (cudaStream_t)stream;
-  MI_DISPATCH(launch_forward, dtype, modified, ncw, px, py, boundary, p, ans, branch, B, S, T, st);
+  MI_DISPATCH(launch_forward, dtype, modified, ncw, px, py, boundary, p, ans, lattice, B, S, T, st);
   return FRNNT_OK;
 }
 
-extern "C" int frnnt_mi_backward_from_branch(int dtype, const void *branch,
-                                             const int64_t *boundary, const void *ans_grad,
-                                             void *px_grad, void *py_grad, void *origin_grad,
-                                             int B, int S, int T, int modified, void *stream) {
+extern "C" int frnnt_mi_backward_from_lattice(int dtype, const void *px, const void *lattice,
+                                              const int64_t *boundary, const void *ans_grad,
+                                              void *px_grad, void *py_grad, void *origin_grad,
+                                              int B, int S, int T, int modified, void *stream) {
   int ncw = 0;
   int rc = mi_check_sizes(dtype, B, S, T, modified, &ncw);
   if (rc != FRNNT_OK) return rc;
   if (B == 0) return FRNNT_OK;
-  FRNNT_REQUIRE(branch != nullptr && ans_grad != nullptr, FRNNT_EINVAL,
-                "branch or ans_grad is NULL");
+  FRNNT_REQUIRE(lattice != nullptr && ans_grad != nullptr, FRNNT_EINVAL,
+                "lattice or ans_grad is NULL");
+  FRNNT_REQUIRE((px != nullptr || S == 0 || (modified && T == 0)), FRNNT_EINVAL, "px is NULL");
   FRNNT_REQUIRE((px_grad != nullptr || S == 0 || (modified && T == 0)) &&
                     (py_grad != nullptr || T == 0),
                 FRNNT_EINVAL, "px_grad or py_grad is NULL");
   cudaStream_t st = (cudaStream_t)stream;
-  MI_DISPATCH(launch_backward, dtype, modified, ncw, branch, boundary, ans_grad, px_grad, py_grad,
-              origin_grad, B, S, T, st);
+  MI_DISPATCH(launch_backward, dtype, modified, ncw, px, lattice, boundary, ans_grad, px_grad,
+              py_grad, origin_grad, B, S, T, st);
   return FRNNT_OK;
 }
 
 extern "C" int frnnt_mi_backward(int dtype, const void *px, const void *py,
                                  const int64_t *boundary, const void *p, const void *ans_grad,
-                                 void *px_grad, void *py_grad, void *origin_grad, void *branch,
+                                 void *px_grad, void *py_grad, void *origin_grad, void *lattice,
                                  int B, int S, int T, int modified, void *stream) {
   (void)py;
   int ncw = 0;
   int rc = mi_check_sizes(dtype, B, S, T, modified, &ncw);
   if (rc != FRNNT_OK) return rc;
   if (B == 0) return FRNNT_OK;
-  FRNNT_REQUIRE(p != nullptr && branch != nullptr, FRNNT_EINVAL, "p or branch is NULL");
+  FRNNT_REQUIRE(p != nullptr && lattice != nullptr, FRNNT_EINVAL, "p or lattice is NULL");
   cudaStream_t st = (cudaStream_t)stream;
-  if (S > 0 && T > 0) {
-    FRNNT_REQUIRE(px != nullptr, FRNNT_EINVAL, "px is NULL");
-    dim3 grid((unsigned)min(64, (S * T + 255) / 256), (unsigned)B);
-    if (dtype == FRNNT_F32) {
-      if (modified)
-        FRNNT_KERNEL(mi_branch_from_p_kernel<float, true><<<grid, 256, 0, st>>>(
-            (const float *)px, (const float *)p, boundary, (float *)branch, S, T));
-      else
-        FRNNT_KERNEL(mi_branch_from_p_kernel<float, false><<<grid, 256, 0, st>>>(
-            (const float *)px, (const float *)p, boundary, (float *)branch, S, T));
-    } else {
-      if (modified)
-        FRNNT_KERNEL(mi_branch_from_p_kernel<double, true><<<grid, 256, 0, st>>>(
-            (const double *)px, (const double *)p, boundary, (double *)branch, S, T));
-      else
-        FRNNT_KERNEL(mi_branch_from_p_kernel<double, false><<<grid, 256, 0, st>>>(
-            (const double *)px, (const double *)p, boundary, (double *)branch, S, T));
-    }
-    FRNNT_CUDA(cudaGetLastError());
-  }
-  return frnnt_mi_backward_from_branch(dtype, branch, boundary, ans_grad, px_grad, py_grad,
-                                       origin_grad, B, S, T, modified, stream);
+  dim3 grid((unsigned)min(64, ((S + 1) * (T + 1) + 255) / 256), (unsigned)B);
+  if (dtype == FRNNT_F32)
+    FRNNT_KERNEL(mi_lattice_from_p_kernel<float><<<grid, 256, 0, st>>>(
+        (const float *)p, boundary, (float *)lattice, S, T));
+  else
+    FRNNT_KERNEL(mi_lattice_from_p_kernel<double><<<grid, 256, 0, st>>>(
+        (const double *)p, boundary, (double *)lattice, S, T));
+  FRNNT_CUDA(cudaGetLastError());
+  return frnnt_mi_backward_from_lattice(dtype, px, lattice, boundary, ans_grad, px_grad, py_grad,
+                                        origin_grad, B, S, T, modified, stream);
 }
 
 extern "C" int frnnt_mi_fwd_bwd_noalloc(int dtype, const void *px, const void *py,
@@ -523,10 +657,10 @@ extern "C" int frnnt_mi_fwd_bwd_noalloc(int dtype, const void *px, const void *p
   int ncw = 0;
   int rc = mi_check_sizes(dtype, B, S, T, modified, &ncw);
   if (rc != FRNNT_OK) return rc;
-  const size_t need = frnnt_mi_branch_bytes(dtype, B, S, T);
+  const size_t need = frnnt_mi_lattice_bytes(dtype, B, S, T);
   FRNNT_REQUIRE(need <= (size_t)FRNNT_MI_NOALLOC_SCRATCH_BYTES, FRNNT_EUNSUPPORTED,
                 "lattice B=%d S=%d T=%d needs %zu bytes of scratch, the built-in region holds %zu; "
-                "use frnnt_mi_forward + frnnt_mi_backward_from_branch with your own buffer",
+                "use frnnt_mi_forward + frnnt_mi_backward_from_lattice with your own buffer",
                 B, S, T, need, (size_t)FRNNT_MI_NOALLOC_SCRATCH_BYTES);
   if (B == 0) return FRNNT_OK;
   FRNNT_REQUIRE(ans != nullptr && ans_grad != nullptr, FRNNT_EINVAL, "ans or ans_grad is NULL");
@@ -534,10 +668,10 @@ extern "C" int frnnt_mi_fwd_bwd_noalloc(int dtype, const void *px, const void *p
   rc = static_scratch_address(&scratch);
   if (rc != FRNNT_OK) return rc;
   // Nothing in the region has to start at zero: the forward sweep writes every
-  // weight that the backward sweep reads, so the previous call's contents are
-  // simply overwritten.
+  // lattice value that the backward sweep reads, so the previous call's contents
+  // are simply overwritten.
   rc = frnnt_mi_forward(dtype, px, py, boundary, nullptr, ans, scratch, B, S, T, modified, stream);
   if (rc != FRNNT_OK) return rc;
-  return frnnt_mi_backward_from_branch(dtype, scratch, boundary, ans_grad, px_grad, py_grad,
-                                       nullptr, B, S, T, modified, stream);
+  return frnnt_mi_backward_from_lattice(dtype, px, scratch, boundary, ans_grad, px_grad, py_grad,
+                                        nullptr, B, S, T, modified, stream);
 }

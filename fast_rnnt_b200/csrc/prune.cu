@@ -41,44 +41,73 @@ __device__ void block_suffix_min(int *arr, int n, int *part) {
   __syncthreads();
 }
 
-template <typename real>
-__global__ void __launch_bounds__(kPruneThreads)
-prune_ranges_kernel(const real *__restrict__ px_grad, const real *__restrict__ py_grad,
+// Stage 1: one thread per frame.  s_begin[b][t] (first maximum of the windowed
+// score) is parked in ranges[b][t][0] for stage 2.  RT > 0: the window width is
+// a compile-time constant and the window lives in registers.
+template <typename real, int RT>
+__global__ void __launch_bounds__(128)
+prune_argmax_kernel(const real *__restrict__ px_grad, const real *__restrict__ py_grad,
                     const int64_t *__restrict__ boundary, int64_t *__restrict__ ranges, int S,
-                    int T, int T1, int R) {
-  extern __shared__ int sm[];
-  int *arr = sm;        // [T]
-  int *part = sm + T;   // [kPruneThreads]
-  const int b = blockIdx.x;
+                    int T, int T1, int Rdyn) {
+  const int b = blockIdx.y;
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= T) return;
+  const int R = RT > 0 ? RT : Rdyn;
   const int S1 = S + 1;
   const int n_win = S1 - R + 1;
-  const real *GX = px_grad + (size_t)b * S * T1;
-  const real *GY = py_grad + (size_t)b * S1 * T;
+  const real *GX = px_grad + (size_t)b * S * T1 + t;
+  const real *GY = py_grad + (size_t)b * S1 * T + t;
   const long long Sb = boundary[4 * b + 2], Tb = boundary[4 * b + 3];
-  long long pad = Sb - R + 1;
-  if (pad < 0) pad = 0;
-  if (pad > n_win - 1) pad = n_win - 1;  // keeps ranges inside [0, S] for malformed rows
-
-  for (int t = threadIdx.x; t < T; t += kPruneThreads) {
-    int best_s = 0;
-    if ((long long)t < Tb - 1) {
-      real best = 0;
+  int best_s = 0;
+  if ((long long)t < Tb - 1) {
+    real best = 0;
+    if (RT > 0) {
+      real w[RT > 0 ? RT : 1];
+#pragma unroll
+      for (int k = 0; k < RT; ++k) w[k] = GY[(size_t)k * T];
       for (int s = 0; s < n_win; ++s) {
-        real acc = GY[(size_t)s * T + t];
-        for (int k = 1; k < R; ++k) acc = acc + GY[(size_t)(s + k) * T + t];
-        const real score = acc - (s == 0 ? (real)0 : GX[(size_t)(s - 1) * T1 + t]);
+        real acc = w[0];
+#pragma unroll
+        for (int k = 1; k < RT; ++k) acc = acc + w[k];
+        const real score = acc - (s == 0 ? (real)0 : GX[(size_t)(s - 1) * T1]);
+        if (s == 0 || score > best) {
+          best = score;
+          best_s = s;
+        }
+#pragma unroll
+        for (int k = 0; k + 1 < RT; ++k) w[k] = w[k + 1];
+        if (s + RT < S1) w[RT - 1] = GY[(size_t)(s + RT) * T];
+      }
+    } else {
+      for (int s = 0; s < n_win; ++s) {
+        real acc = GY[(size_t)s * T];
+        for (int k = 1; k < R; ++k) acc = acc + GY[(size_t)(s + k) * T];
+        const real score = acc - (s == 0 ? (real)0 : GX[(size_t)(s - 1) * T1]);
         if (s == 0 || score > best) {
           best = score;
           best_s = s;
         }
       }
-    } else {
-      best_s = (int)pad;
     }
-    arr[t] = best_s;
+  } else {
+    long long pad = Sb - R + 1;
+    if (pad < 0) pad = 0;
+    if (pad > n_win - 1) pad = n_win - 1;  // keeps ranges inside [0, S] for malformed rows
+    best_s = (int)pad;
   }
-  __syncthreads();
+  ranges[((size_t)b * T + t) * R] = best_s;
+}
 
+// Stage 2: one CTA per utterance: monotone fix-up (integer scans) and expansion.
+__global__ void __launch_bounds__(kPruneThreads)
+prune_fixup_kernel(int64_t *__restrict__ ranges, int T, int T1, int R) {
+  extern __shared__ int sm[];
+  int *arr = sm;        // [T]
+  int *part = sm + T;   // [kPruneThreads]
+  const int b = blockIdx.x;
+  int64_t *out = ranges + (size_t)b * T * R;
+  for (int t = threadIdx.x; t < T; t += kPruneThreads) arr[t] = (int)out[(size_t)t * R];
+  __syncthreads();
   // _adjust_pruning_lower_bound with window 2 (modified shapes) or R (regular)
   const int step = (T1 == T ? 2 : R) - 1;
   block_suffix_min(arr, T, part);
@@ -87,8 +116,6 @@ prune_ranges_kernel(const real *__restrict__ px_grad, const real *__restrict__ p
   block_suffix_min(arr, T, part);
   for (int t = threadIdx.x; t < T; t += kPruneThreads) arr[t] = step * t - max(arr[t], 0);
   __syncthreads();
-
-  int64_t *out = ranges + (size_t)b * T * R;
   for (int idx = threadIdx.x; idx < T * R; idx += kPruneThreads)
     out[idx] = (int64_t)arr[idx / R] + (idx % R);
 }
@@ -112,38 +139,75 @@ __global__ void prune_gather_kernel(const vec *__restrict__ lm, const int64_t *_
 }
 
 // lm_grad[b][s][:] = sum over (t,k) with ranges[b][t][k] == s of g[b][t][k][:]
-template <typename real>
-__global__ void __launch_bounds__(128)
+// One CTA (4 warps) per (b, s).  Step 1: the warps scan the utterance's T*R
+// range entries (a quarter each, 32 entries per ballot) and list the matching
+// entries in shared memory, in entry order.  Step 2: every warp walks the whole
+// list for its share of the D columns, eight gradient rows in flight at a time,
+// adding them in list order.  Deterministic, no atomics, any ranges (not only
+// the monotone ones get_rnnt_prune_ranges produces).
+constexpr int kGbThreads = 128;
+constexpr int kGbSegment = 8192;  // range entries listed per pass
+
+template <typename real, typename vec, int VW>
+__global__ void __launch_bounds__(kGbThreads)
 prune_gather_backward_kernel(const real *__restrict__ g, const int64_t *__restrict__ ranges,
                              real *__restrict__ lm_grad, int TR, int S1, int D) {
-  constexpr int kEntries = 2048;
-  __shared__ int sm_s[kEntries];
+  constexpr int NW = kGbThreads / 32;
+  constexpr int kBatch = 8;
+  __shared__ int list[NW][kGbSegment / NW];
+  __shared__ int count[NW];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b = blockIdx.y, s = blockIdx.x;
   const int64_t *rg = ranges + (size_t)b * TR;
   const real *G = g + (size_t)b * TR * D;
-  real *out = lm_grad + ((size_t)b * S1 + s) * D;
-  for (int d0 = 0; d0 < D; d0 += 4 * 128) {
-    real acc[4] = {0, 0, 0, 0};
-    for (int base = 0; base < TR; base += kEntries) {
-      const int n = min(kEntries, TR - base);
-      __syncthreads();
-      for (int e = threadIdx.x; e < n; e += 128) sm_s[e] = (int)rg[base + e];
-      __syncthreads();
-      for (int e = 0; e < n; ++e) {
-        if (sm_s[e] == s) {
-          const real *row = G + (size_t)(base + e) * D;
+  const int dvec = D / VW;
+  vec *out = reinterpret_cast<vec *>(lm_grad + ((size_t)b * S1 + s) * D);
+
+  for (int v0 = 0; v0 < dvec; v0 += kGbThreads) {
+    const int v = v0 + threadIdx.x;
+    real acc[VW];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int d = d0 + j * 128 + threadIdx.x;
-            if (d < D) acc[j] += row[d];
+    for (int c = 0; c < VW; ++c) acc[c] = 0;
+    for (int seg = 0; seg < TR; seg += kGbSegment) {
+      const int seg_n = min(kGbSegment, TR - seg);
+      const int per = ((seg_n + NW * 32 - 1) / (NW * 32)) * 32;  // entries per warp, multiple of 32
+      __syncthreads();
+      int n = 0;
+      for (int base = warp * per; base < min(seg_n, (warp + 1) * per); base += 32) {
+        const int e = base + lane;
+        const bool hit = e < seg_n && (long long)rg[seg + e] == (long long)s;
+        const unsigned mask = __ballot_sync(0xffffffffu, hit);
+        if (hit) list[warp][n + __popc(mask & ((1u << lane) - 1))] = seg + e;
+        n += __popc(mask);
+      }
+      if (lane == 0) count[warp] = n;
+      __syncthreads();
+      if (v < dvec) {
+        for (int w = 0; w < NW; ++w) {
+          const int cnt = count[w];
+          for (int i0 = 0; i0 < cnt; i0 += kBatch) {
+            vec x[kBatch];
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u)
+              if (i0 + u < cnt)
+                x[u] = reinterpret_cast<const vec *>(G + (size_t)list[w][i0 + u] * D)[v];
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u)
+              if (i0 + u < cnt) {
+                const real *xe = reinterpret_cast<const real *>(&x[u]);
+#pragma unroll
+                for (int c = 0; c < VW; ++c) acc[c] += xe[c];
+              }
           }
         }
       }
     }
+    if (v < dvec) {
+      vec o;
+      real *oe = reinterpret_cast<real *>(&o);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int d = d0 + j * 128 + threadIdx.x;
-      if (d < D) out[d] = acc[j];
+      for (int c = 0; c < VW; ++c) oe[c] = acc[c];
+      out[v] = o;
     }
   }
 }
@@ -164,20 +228,35 @@ extern "C" int frnnt_prune_ranges(int dtype, const void *px_grad, const void *py
   const size_t smem = (size_t)(T + kPruneThreads) * sizeof(int);
   FRNNT_REQUIRE(smem <= 200 * 1024, FRNNT_EUNSUPPORTED, "T=%d too long for one CTA's scan", T);
   if (B == 0) return FRNNT_OK;
+  FRNNT_REQUIRE(B <= 65535, FRNNT_EUNSUPPORTED, "B too large for the grid");
   cudaStream_t st = (cudaStream_t)stream;
-  if (dtype == FRNNT_F32) {
-    auto kern = prune_ranges_kernel<float>;
-    if (smem > 48 * 1024)
-      FRNNT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    FRNNT_KERNEL(kern<<<B, kPruneThreads, smem, st>>>((const float *)px_grad, (const float *)py_grad, boundary,
-                                         ranges, S, T, T1, s_range));
-  } else {
-    auto kern = prune_ranges_kernel<double>;
-    if (smem > 48 * 1024)
-      FRNNT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    FRNNT_KERNEL(kern<<<B, kPruneThreads, smem, st>>>((const double *)px_grad, (const double *)py_grad,
-                                         boundary, ranges, S, T, T1, s_range));
+  dim3 grid1((unsigned)((T + 127) / 128), (unsigned)B);
+#define PRUNE_ARGMAX(real, RT)                                                                  \
+  FRNNT_KERNEL(prune_argmax_kernel<real, RT><<<grid1, 128, 0, st>>>(                              \
+      (const real *)px_grad, (const real *)py_grad, boundary, ranges, S, T, T1, s_range))
+#define PRUNE_ARGMAX_R(real)                                   \
+  switch (s_range) {                                           \
+    case 2: PRUNE_ARGMAX(real, 2); break;                      \
+    case 3: PRUNE_ARGMAX(real, 3); break;                      \
+    case 4: PRUNE_ARGMAX(real, 4); break;                      \
+    case 5: PRUNE_ARGMAX(real, 5); break;                      \
+    case 6: PRUNE_ARGMAX(real, 6); break;                      \
+    case 7: PRUNE_ARGMAX(real, 7); break;                      \
+    case 8: PRUNE_ARGMAX(real, 8); break;                      \
+    default: PRUNE_ARGMAX(real, 0); break;                     \
   }
+  if (dtype == FRNNT_F32) {
+    PRUNE_ARGMAX_R(float)
+  } else {
+    PRUNE_ARGMAX_R(double)
+  }
+#undef PRUNE_ARGMAX_R
+#undef PRUNE_ARGMAX
+  FRNNT_CUDA(cudaGetLastError());
+  if (smem > 48 * 1024)
+    FRNNT_CUDA(cudaFuncSetAttribute(prune_fixup_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    (int)smem));
+  FRNNT_KERNEL(prune_fixup_kernel<<<B, kPruneThreads, smem, st>>>(ranges, T, T1, s_range));
   FRNNT_CUDA(cudaGetLastError());
   return FRNNT_OK;
 }
@@ -218,12 +297,22 @@ extern "C" int frnnt_prune_gather_backward(int dtype, const void *out_grad, cons
                 "NULL argument");
   cudaStream_t st = (cudaStream_t)stream;
   dim3 grid((unsigned)S1, (unsigned)B);
-  if (dtype == FRNNT_F32)
-    FRNNT_KERNEL(prune_gather_backward_kernel<float><<<grid, 128, 0, st>>>((const float *)out_grad, ranges,
-                                                             (float *)lm_grad, T * R, S1, D));
-  else
-    FRNNT_KERNEL(prune_gather_backward_kernel<double><<<grid, 128, 0, st>>>((const double *)out_grad, ranges,
-                                                              (double *)lm_grad, T * R, S1, D));
+  const bool vec_ok = (uintptr_t)out_grad % 16 == 0 && (uintptr_t)lm_grad % 16 == 0;
+  if (dtype == FRNNT_F32) {
+    if (vec_ok && D % 4 == 0)
+      FRNNT_KERNEL(prune_gather_backward_kernel<float, float4, 4><<<grid, kGbThreads, 0, st>>>(
+          (const float *)out_grad, ranges, (float *)lm_grad, T * R, S1, D));
+    else
+      FRNNT_KERNEL(prune_gather_backward_kernel<float, float, 1><<<grid, kGbThreads, 0, st>>>(
+          (const float *)out_grad, ranges, (float *)lm_grad, T * R, S1, D));
+  } else {
+    if (vec_ok && D % 2 == 0)
+      FRNNT_KERNEL(prune_gather_backward_kernel<double, double2, 2><<<grid, kGbThreads, 0, st>>>(
+          (const double *)out_grad, ranges, (double *)lm_grad, T * R, S1, D));
+    else
+      FRNNT_KERNEL(prune_gather_backward_kernel<double, double, 1><<<grid, kGbThreads, 0, st>>>(
+          (const double *)out_grad, ranges, (double *)lm_grad, T * R, S1, D));
+  }
   FRNNT_CUDA(cudaGetLastError());
   return FRNNT_OK;
 }

@@ -46,7 +46,7 @@ struct SavedLayout {
   }
 };
 
-constexpr int kColChunkRows = 256;  // rows folded by one CTA of the column-sum kernels
+constexpr int kColChunkRows = 32;  // rows folded by one CTA of the column-sum kernels
 
 // "scratch": temporaries of one call.
 struct ScratchLayout {
@@ -490,10 +490,12 @@ __global__ void am_onehot_kernel(EffGrads<real> eg, const int64_t *__restrict__ 
   for (int s = 0; s < eg.S; ++s) {
     int y = (int)symbols[(size_t)b * eg.S + s];
     if (y < 0 || y >= C) y = blank;
+    // fire-and-forget adds: this thread owns row (b, t), and adds issued by one
+    // thread to one address are applied in program order, so the sum is deterministic
     const real v = eg.gx(b, s, t);
-    if (v != 0) g[y] += coef * v;
+    if (v != 0) atomicAdd(&g[y], coef * v);
   }
-  g[blank] += coef * cgy[idx];
+  atomicAdd(&g[blank], coef * cgy[idx]);
 }
 
 // d loss / d log-unigram[c] = as * ( sum_{b,s: y_bs = c} sgx[b,s]  +  [c = blank] sum_{b,s} sgy[b,s] )

@@ -31,8 +31,8 @@ def _boundary_rows(boundary: Tensor):
 
 
 def mi_forward(px: Tensor, py: Tensor, boundary: Optional[Tensor], want_p: bool = False,
-               want_branch: bool = True):
-    """Raw forward sweep: returns (ans [B], p or None, branch scratch or None)."""
+               want_lattice: bool = True):
+    """Raw forward sweep: returns (ans [B], p or None, lattice scratch or None)."""
     B, S, T1 = px.shape
     T = py.shape[2]
     modified = int(T1 == T)
@@ -41,28 +41,30 @@ def mi_forward(px: Tensor, py: Tensor, boundary: Optional[Tensor], want_p: bool 
     with torch.cuda.device(dev):
         ans = torch.empty(B, dtype=px.dtype, device=dev)
         p = torch.empty(B, S + 1, T + 1, dtype=px.dtype, device=dev) if want_p else None
-        branch = None
-        if want_branch:
-            nbytes = _lib.lib().frnnt_mi_branch_bytes(dt, B, S, T)
-            branch = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=dev)
+        lattice = None
+        if want_lattice:
+            nbytes = _lib.lib().frnnt_mi_lattice_bytes(dt, B, S, T)
+            lattice = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=dev)
         _lib.call("frnnt_mi_forward", _c_int(dt), _lib.ptr(px), _lib.ptr(py), _lib.ptr(boundary),
-                  _lib.ptr(p), _lib.ptr(ans), _lib.ptr(branch), B, S, T, modified,
+                  _lib.ptr(p), _lib.ptr(ans), _lib.ptr(lattice), B, S, T, modified,
                   _lib.stream_ptr(dev))
-    return ans, p, branch
+    return ans, p, lattice
 
 
-def mi_backward_from_branch(branch: Tensor, boundary: Optional[Tensor], ans_grad: Tensor,
-                            px_shape, py_shape, dtype):
-    B, S, T1 = px_shape
+def mi_backward_from_lattice(px: Tensor, lattice: Tensor, boundary: Optional[Tensor],
+                             ans_grad: Tensor, py_shape):
+    """Reverse sweep from the diagonal-major lattice written by mi_forward."""
+    B, S, T1 = px.shape
     T = py_shape[2]
     modified = int(T1 == T)
-    dev = branch.device
+    dev = px.device
     with torch.cuda.device(dev):
-        px_grad = torch.empty(px_shape, dtype=dtype, device=dev)
-        py_grad = torch.empty(py_shape, dtype=dtype, device=dev)
-        _lib.call("frnnt_mi_backward_from_branch", _c_int(_lib.dtype_code(dtype)),
-                  _lib.ptr(branch), _lib.ptr(boundary), _lib.ptr(ans_grad), _lib.ptr(px_grad),
-                  _lib.ptr(py_grad), None, B, S, T, modified, _lib.stream_ptr(dev))
+        px_grad = torch.empty_like(px)
+        py_grad = torch.empty(py_shape, dtype=px.dtype, device=dev)
+        _lib.call("frnnt_mi_backward_from_lattice", _c_int(_lib.dtype_code(px.dtype)),
+                  _lib.ptr(px), _lib.ptr(lattice), _lib.ptr(boundary), _lib.ptr(ans_grad),
+                  _lib.ptr(px_grad), _lib.ptr(py_grad), None, B, S, T, modified,
+                  _lib.stream_ptr(dev))
     return px_grad, py_grad
 
 
@@ -76,14 +78,14 @@ def mi_backward_from_p(px: Tensor, py: Tensor, boundary: Optional[Tensor], p: Te
     dt = _lib.dtype_code(px.dtype)
     dev = px.device
     with torch.cuda.device(dev):
-        nbytes = _lib.lib().frnnt_mi_branch_bytes(dt, B, S, T)
-        branch = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=dev)
+        nbytes = _lib.lib().frnnt_mi_lattice_bytes(dt, B, S, T)
+        lattice = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=dev)
         px_grad = torch.empty_like(px)
         py_grad = torch.empty_like(py)
         origin = torch.zeros(B, dtype=px.dtype, device=dev) if want_origin_grad else None
         _lib.call("frnnt_mi_backward", _c_int(dt), _lib.ptr(px), _lib.ptr(py), _lib.ptr(boundary),
                   _lib.ptr(p), _lib.ptr(ans_grad), _lib.ptr(px_grad), _lib.ptr(py_grad),
-                  _lib.ptr(origin), _lib.ptr(branch), B, S, T, modified, _lib.stream_ptr(dev))
+                  _lib.ptr(origin), _lib.ptr(lattice), B, S, T, modified, _lib.stream_ptr(dev))
     return (px_grad, py_grad, origin) if want_origin_grad else (px_grad, py_grad)
 
 
@@ -100,12 +102,11 @@ class MutualInformationRecursionFunction(torch.autograd.Function):
         if boundary is not None:
             assert boundary.shape == (B, 4)
         need_grad = return_grad or px.requires_grad or py.requires_grad
-        ans, _, branch = mi_forward(px, py, boundary, want_p=False, want_branch=need_grad)
+        ans, _, lattice = mi_forward(px, py, boundary, want_p=False, want_lattice=need_grad)
         px_grad, py_grad = None, None
         if need_grad:
             ones = torch.ones(B, device=px.device, dtype=px.dtype)
-            px_grad, py_grad = mi_backward_from_branch(branch, boundary, ones, px.shape,
-                                                       py.shape, px.dtype)
+            px_grad, py_grad = mi_backward_from_lattice(px, lattice, boundary, ones, py.shape)
             ctx.save_for_backward(px_grad, py_grad)
         assert len(pxy_grads) == 2
         pxy_grads[0] = px_grad
@@ -182,10 +183,10 @@ def joint_mutual_information_recursion(
         boundary = boundary.contiguous()
 
     with torch.no_grad():
-        tot_probs, _, branch = mi_forward(px_tot.detach(), py_tot.detach(), boundary)
+        tot_probs, _, lattice = mi_forward(px_tot.detach(), py_tot.detach(), boundary)
         ones = torch.ones(B, device=px_tot.device, dtype=px_tot.dtype)
-        px_grad, py_grad = mi_backward_from_branch(branch, boundary, ones, px_tot.shape,
-                                                   py_tot.shape, px_tot.dtype)
+        px_grad, py_grad = mi_backward_from_lattice(px_tot.detach(), lattice, boundary, ones,
+                                                    py_tot.shape)
 
     px_grad = px_grad.reshape(1, B, -1)
     py_grad = py_grad.reshape(1, B, -1)

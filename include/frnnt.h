@@ -63,40 +63,41 @@ int frnnt_with_cuda(void);
  * Mutual-information recursion
  * ------------------------------------------------------------------------- */
 
-/* Bytes of the `branch` scratch of the three functions below: for every lattice
- * cell the weight exp(p[s-1][t']+px[s-1][t']-p[s][t]) of its "x" predecessor,
- * stored by anti-diagonal so that the backward sweep reads it coalesced. */
-size_t frnnt_mi_branch_bytes(int dtype, int B, int S, int T);
+/* Bytes of the `lattice` scratch of the functions below: the forward sweep
+ * stores p there by anti-diagonal ([B][S+T+1][round_up(S+1,32)]), so that it
+ * writes it and the backward sweep reads it fully coalesced. */
+size_t frnnt_mi_lattice_bytes(int dtype, int B, int S, int T);
 
 /* Forward recursion.  Replaces mutual_information_forward(px, py, boundary, p)
  * of the reference's extension module (fast_rnnt/python/csrc/mutual_information.cu:27-45,
  * MutualInformationCuda at fast_rnnt/csrc/mutual_information_cuda.cu:676-728).
- *   p      may be NULL when the caller does not need the lattice;
- *   branch may be NULL when no backward sweep will follow;
- *   ans    [B] receives p[b][s_end][t_end]. */
+ *   p       ([B][S+1][T+1], the reference's layout) may be NULL when the caller
+ *           does not need the lattice;
+ *   lattice (scratch, see above) may be NULL when no backward sweep will follow;
+ *   ans     [B] receives p[b][s_end][t_end]. */
 int frnnt_mi_forward(int dtype, const void *px, const void *py, const int64_t *boundary,
-                     void *p, void *ans, void *branch, int B, int S, int T, int modified,
+                     void *p, void *ans, void *lattice, int B, int S, int T, int modified,
                      void *stream);
 
-/* Reverse sweep from the `branch` weights written by frnnt_mi_forward:
- * px_grad [B][S][T1] and py_grad [B][S+1][T] are fully written (exact zeros
- * outside the boundary box).  origin_grad (may be NULL) receives the gradient
- * that reaches p[s_begin][t_begin], which equals ans_grad[b] up to rounding
- * when the sweep is right (the reference overwrites ans_grad with it,
+/* Reverse sweep from the `lattice` written by frnnt_mi_forward (and the same
+ * px): px_grad [B][S][T1] and py_grad [B][S+1][T] are fully written (exact
+ * zeros outside the boundary box).  origin_grad (may be NULL) receives the
+ * gradient that reaches p[s_begin][t_begin], which equals ans_grad[b] up to
+ * rounding when the sweep is right (the reference overwrites ans_grad with it,
  * mutual_information_cuda.cu:667-669). */
-int frnnt_mi_backward_from_branch(int dtype, const void *branch, const int64_t *boundary,
-                                  const void *ans_grad, void *px_grad, void *py_grad,
-                                  void *origin_grad, int B, int S, int T, int modified,
-                                  void *stream);
+int frnnt_mi_backward_from_lattice(int dtype, const void *px, const void *lattice,
+                                   const int64_t *boundary, const void *ans_grad, void *px_grad,
+                                   void *py_grad, void *origin_grad, int B, int S, int T,
+                                   int modified, void *stream);
 
 /* Reverse sweep from a lattice `p` in the reference's layout.  Replaces
  * mutual_information_backward(px, py, boundary, p, ans_grad)
  * (fast_rnnt/python/csrc/mutual_information.cu:47-67, MutualInformationBackwardCuda
- * at mutual_information_cuda.cu:734-805).  `branch` is scratch of
- * frnnt_mi_branch_bytes() bytes. */
+ * at mutual_information_cuda.cu:734-805).  `lattice` is scratch of
+ * frnnt_mi_lattice_bytes() bytes. */
 int frnnt_mi_backward(int dtype, const void *px, const void *py, const int64_t *boundary,
                       const void *p, const void *ans_grad, void *px_grad, void *py_grad,
-                      void *origin_grad, void *branch, int B, int S, int T, int modified,
+                      void *origin_grad, void *lattice, int B, int S, int T, int modified,
                       void *stream);
 
 /* Size of the scratch region built into the library for frnnt_mi_fwd_bwd_noalloc. */
@@ -110,21 +111,21 @@ int frnnt_mi_backward(int dtype, const void *px, const void *py, const int64_t *
  * and cannot obtain one more -- e.g. a C/C++ training or scoring loop that
  * carved up all of its device memory at start-up, or a plugin host that bans
  * cudaMalloc after initialisation because an allocation stalls every stream of
- * the device.  frnnt_mi_forward / frnnt_mi_backward_from_branch need a
- * caller-provided scratch of frnnt_mi_branch_bytes(); this entry point instead
- * keeps the per-cell weights in a region of FRNNT_MI_NOALLOC_SCRATCH_BYTES
+ * the device.  frnnt_mi_forward / frnnt_mi_backward_from_lattice need a
+ * caller-provided scratch of frnnt_mi_lattice_bytes(); this entry point instead
+ * keeps the lattice in a region of FRNNT_MI_NOALLOC_SCRATCH_BYTES
  * (32 MiB) that is part of the library image: every GPU that loads the library
  * holds those 32 MiB from load until the process exits.
  *
  *   - inputs px, py, boundary, ans_grad [B] and outputs ans [B], px_grad, py_grad
  *     are the caller's, exactly as for the two functions it combines;
- *   - a lattice with frnnt_mi_branch_bytes(dtype,B,S,T) above the limit is
+ *   - a lattice with frnnt_mi_lattice_bytes(dtype,B,S,T) above the limit is
  *     refused with FRNNT_EUNSUPPORTED before anything is launched;
  *   - it calls no cudaMalloc / cudaFree and no allocating library routine;
  *   - the FIRST call on each device looks up the region's device address (with
  *     that device current); make that first call outside of any stream capture;
  *   - all calls on a device share the one region, which still holds the previous
- *     call's weights when the next call starts (nothing needs clearing: each
+ *     call's lattice when the next call starts (nothing needs clearing: each
  *     call overwrites what it later reads).  Two calls whose kernels overlap on
  *     the GPU (different streams, or different host threads on different
  *     streams) race on it: issue them on one stream, or order them yourself. */

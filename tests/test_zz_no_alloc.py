@@ -41,7 +41,7 @@ def _call_noalloc(lib, px, py, boundary, ans_grad):
 def _call_two_step(px, py, boundary, ans_grad):
     from fast_rnnt_b200 import mutual_information as mi
     ans, _, branch = mi.mi_forward(px, py, boundary)
-    gx, gy = mi.mi_backward_from_branch(branch, boundary, ans_grad, px.shape, py.shape, px.dtype)
+    gx, gy = mi.mi_backward_from_lattice(px, branch, boundary, ans_grad, py.shape)
     return ans, gx, gy
 
 
@@ -63,7 +63,7 @@ def test_noalloc_matches_two_step_path_twice_in_a_row():
         bnd = workloads.random_mi_boundary(B, S, T, c["modified"], random.Random(c["seed"]),
                                            allow_empty=False).cuda()
         w = torch.linspace(0.5, 1.5, B, dtype=c["dtype"]).cuda()
-        assert lib.frnnt_mi_branch_bytes(_lib.dtype_code(c["dtype"]), B, S, T) <= LIMIT
+        assert lib.frnnt_mi_lattice_bytes(_lib.dtype_code(c["dtype"]), B, S, T) <= LIMIT
         rc, ans, gx, gy = _call_noalloc(lib, px, py, bnd, w)
         assert rc == 0, lib.frnnt_last_error()
         ans2, gx2, gy2 = _call_two_step(px, py, bnd, w)
@@ -78,7 +78,7 @@ def test_noalloc_refuses_lattices_beyond_the_region():
     from fast_rnnt_b200 import _lib
     lib = _lib.lib()
     B, S, T = 64, 200, 900  # needs far more than 32 MiB of weights
-    assert lib.frnnt_mi_branch_bytes(0, B, S, T) > LIMIT
+    assert lib.frnnt_mi_lattice_bytes(0, B, S, T) > LIMIT
     px = torch.zeros(1, device="cuda")
     # refused on the host before any launch, so the tiny buffers are never touched
     rc = lib.frnnt_mi_fwd_bwd_noalloc(ctypes.c_int(0), _lib.ptr(px), _lib.ptr(px), None,
