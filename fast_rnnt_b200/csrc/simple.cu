@@ -19,6 +19,9 @@
 //
 // This file holds the fp32/fp64 SIMT version of the contraction (FMA pipes,
 // shared-memory tiles); it is the general path for both dtypes.
+#include <stdlib.h>
+#include <string.h>
+
 #include "common.cuh"
 
 namespace frnnt {
@@ -540,6 +543,21 @@ __global__ void row_dot_kernel(const real *__restrict__ lm, const real *__restri
   if (lane == 0) rowdot[row] = acc / lmsum[row];
 }
 
+// tensor-core (tcgen05, 3xTF32) contraction: float32 with 16-byte aligned rows;
+// everything else (float64, odd vocabulary sizes) takes the SIMT path.  The
+// environment variable FRNNT_CONTRACTION=simt forces the SIMT path (for tests).
+bool norm_umma_supported(const void *lm, const void *am, int S1, int T, int C);
+int launch_norm_umma(const float *lm, const float *am, const float *lmmax, const float *ammax,
+                     float *norm, int B, int S1, int T, int C, cudaStream_t st);
+
+template <typename real>
+static bool use_tensor_cores(const void *lm, const void *am, int S1, int T, int C) {
+  if (sizeof(real) != 4) return false;
+  const char *mode = getenv("FRNNT_CONTRACTION");
+  if (mode != nullptr && strcmp(mode, "simt") == 0) return false;
+  return norm_umma_supported(lm, am, S1, T, C);
+}
+
 static int simple_check(int dtype, int B, int S, int T, int C, int blank, int rnnt_type) {
   FRNNT_REQUIRE(check_dtype(dtype), FRNNT_EINVAL, "dtype must be FRNNT_F32 or FRNNT_F64");
   FRNNT_REQUIRE(B >= 0 && S >= 0 && T >= 0 && C >= 1, FRNNT_EINVAL,
@@ -599,8 +617,14 @@ static int simple_forward_impl(const void *lm_, const void *am_, const int64_t *
     FRNNT_KERNEL(am_only_norm_kernel<real><<<warps_grid(am_rows), 256, 0, st>>>(am, ammax, uni, amonly, am_rows, C));
     FRNNT_CUDA(cudaGetLastError());
   }
-  NormProb<real> prob{lm, am, lmmax, ammax, norm, S1, T, C};
-  int rc = launch_contraction<real>(prob, S1, T, B, st);
+  int rc;
+  if (use_tensor_cores<real>(lm, am, S1, T, C)) {
+    rc = launch_norm_umma((const float *)lm, (const float *)am, (const float *)lmmax,
+                          (const float *)ammax, (float *)norm, B, S1, T, C, st);
+  } else {
+    NormProb<real> prob{lm, am, lmmax, ammax, norm, S1, T, C};
+    rc = launch_contraction<real>(prob, S1, T, B, st);
+  }
   if (rc != FRNNT_OK) return rc;
   dim3 g2((unsigned)((T + 1 + 127) / 128), (unsigned)S1, (unsigned)B);
   FRNNT_KERNEL(assemble_kernel<real><<<g2, 128, 0, st>>>(lm, am, symbols, boundary, norm, lmmax, lmsum, amonly,
