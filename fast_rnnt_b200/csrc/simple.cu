@@ -51,6 +51,9 @@ struct SavedLayout {
 
 constexpr int kColChunkRows = 32;  // rows folded by one CTA of the column-sum kernels
 
+// row pitch of the gradient-weight matrix (16-byte aligned rows for the tensor-core path)
+static inline int rw_pitch(int T) { return (T + 3) & ~3; }
+
 // "scratch": temporaries of one call.
 struct ScratchLayout {
   size_t rw, sgx, sgy, cgx, cgy, gl, h, partial, dp, rowdot, total;
@@ -59,7 +62,7 @@ struct ScratchLayout {
     size_t o = 0;
     const size_t rows_max = (size_t)B * (T > S + 1 ? T : S + 1);
     nchunk = (int)((rows_max + kColChunkRows - 1) / kColChunkRows);
-    rw = o;      o += align_up(es * (size_t)B * (S + 1) * T);  // gradient weights of the contraction
+    rw = o;      o += align_up(es * (size_t)B * (S + 1) * rw_pitch(T));  // gradient weights, rows padded to 4
     sgx = o;     o += align_up(es * (size_t)B * (S + 1));      // sum_t gx, sum_t gy
     sgy = o;     o += align_up(es * (size_t)B * (S + 1));
     cgx = o;     o += align_up(es * (size_t)B * T);            // sum_s gx, sum_s gy
@@ -236,9 +239,9 @@ struct LmGradProb {
   static constexpr bool X_K_CONTIG = true, Y_K_CONTIG = false;
   const real *rw, *am, *ammax, *lm, *lmmax, *lmsum, *gl, *dp, *rowdot;
   real *lm_grad;
-  int S1, T, C;
+  int S1, T, C, Tp;
   __device__ void set_batch(int b) {
-    rw += (size_t)b * S1 * T;
+    rw += (size_t)b * S1 * Tp;
     am += (size_t)b * T * C;
     ammax += (size_t)b * T;
     lm += (size_t)b * S1 * C;
@@ -249,7 +252,7 @@ struct LmGradProb {
     lm_grad += (size_t)b * S1 * C;
   }
   __device__ int K() const { return T; }
-  __device__ real x(int s, int t) const { return (s < S1 && t < T) ? rw[(size_t)s * T + t] : (real)0; }
+  __device__ real x(int s, int t) const { return (s < S1 && t < T) ? rw[(size_t)s * Tp + t] : (real)0; }
   __device__ real y(int c, int t) const {
     return (c < C && t < T) ? exp_r(am[(size_t)t * C + c] - ammax[t]) : (real)0;
   }
@@ -272,9 +275,9 @@ struct AmGradProb {
   static constexpr bool X_K_CONTIG = false, Y_K_CONTIG = false;
   const real *rw, *lm, *lmmax, *am, *ammax, *h, *uni, *amonly;
   real *am_grad;
-  int S1, T, C;
+  int S1, T, C, Tp;
   __device__ void set_batch(int b) {
-    rw += (size_t)b * S1 * T;
+    rw += (size_t)b * S1 * Tp;
     lm += (size_t)b * S1 * C;
     lmmax += (size_t)b * S1;
     am += (size_t)b * T * C;
@@ -286,7 +289,7 @@ struct AmGradProb {
     am_grad += (size_t)b * T * C;
   }
   __device__ int K() const { return S1; }
-  __device__ real x(int t, int s) const { return (t < T && s < S1) ? rw[(size_t)s * T + t] : (real)0; }
+  __device__ real x(int t, int s) const { return (t < T && s < S1) ? rw[(size_t)s * Tp + t] : (real)0; }
   __device__ real y(int c, int s) const {
     return (c < C && s < S1) ? exp_r(lm[(size_t)s * C + c] - lmmax[s]) : (real)0;
   }
@@ -410,14 +413,19 @@ struct EffGrads {
 template <typename real>
 __global__ void grad_weight_kernel(EffGrads<real> eg, const real *__restrict__ norm,
                                    const real *__restrict__ lmmax, const real *__restrict__ ammax,
-                                   real *__restrict__ rw, real both) {
+                                   real *__restrict__ rw, real both, int Tp) {
   const int b = blockIdx.z, s = blockIdx.y;
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
-  if (t >= eg.T) return;
+  if (t >= Tp) return;
+  const size_t o = ((size_t)b * (eg.S + 1) + s) * Tp + t;
+  if (t >= eg.T) {  // row padding
+    rw[o] = 0;
+    return;
+  }
   const size_t i = ((size_t)b * (eg.S + 1) + s) * eg.T + t;
   const real w = both * (eg.gx(b, s, t) + eg.gy(b, s, t));
   const real inv = exp_r(lmmax[(size_t)b * (eg.S + 1) + s] + ammax[(size_t)b * eg.T + t] - norm[i]);
-  rw[i] = (w == 0) ? (real)0 : w * inv;
+  rw[o] = (w == 0) ? (real)0 : w * inv;
 }
 
 // one warp per (b, s): sums over t of gx (all T1 columns) and gy
@@ -549,6 +557,11 @@ __global__ void row_dot_kernel(const real *__restrict__ lm, const real *__restri
 bool norm_umma_supported(const void *lm, const void *am, int S1, int T, int C);
 int launch_norm_umma(const float *lm, const float *am, const float *lmmax, const float *ammax,
                      float *norm, int B, int S1, int T, int C, cudaStream_t st);
+int launch_simple_grads_umma(const float *lm, const float *am, const float *lmmax,
+                             const float *lmsum, const float *ammax, const float *amonly,
+                             const float *uni, const float *rw, const float *gl, const float *h,
+                             const float *dp, const float *rowdot, float *lm_grad, float *am_grad,
+                             int B, int S1, int T, int C, int Tp, cudaStream_t st);
 
 template <typename real>
 static bool use_tensor_cores(const void *lm, const void *am, int S1, int T, int C) {
@@ -659,9 +672,10 @@ static int simple_backward_impl(const void *lm_, const void *am_, const int64_t 
   const long long lm_rows = (long long)B * S1, am_rows = (long long)B * T;
   EffGrads<real> eg{(const real *)px_grad, (const real *)py_grad, boundary, S, T, T1, rnnt_type};
 
-  dim3 g3((unsigned)((T + 127) / 128), (unsigned)S1, (unsigned)B);
+  const int Tp = rw_pitch(T);
+  dim3 g3((unsigned)((Tp + 127) / 128), (unsigned)S1, (unsigned)B);
   if (T > 0)
-    FRNNT_KERNEL(grad_weight_kernel<real><<<g3, 128, 0, st>>>(eg, norm, lmmax, ammax, rw, (real)cfg.both));
+    FRNNT_KERNEL(grad_weight_kernel<real><<<g3, 128, 0, st>>>(eg, norm, lmmax, ammax, rw, (real)cfg.both, Tp));
   FRNNT_KERNEL(grad_row_sums_kernel<real><<<(int)((lm_rows * 32 + 255) / 256), 256, 0, st>>>(eg, sgx, sgy, B));
   if (T > 0)
     FRNNT_KERNEL(grad_col_sums_kernel<real><<<(int)((am_rows + 127) / 128), 128, 0, st>>>(eg, cgx, cgy, B));
@@ -690,12 +704,22 @@ static int simple_backward_impl(const void *lm_, const void *am_, const int64_t 
     FRNNT_CUDA(cudaGetLastError());
   }
 
-  LmGradProb<real> p1{rw, am, ammax, lm, lmmax, lmsum, gl_p, dp_p, rowdot_p, lm_grad, S1, T, C};
-  int rc = launch_contraction<real>(p1, S1, C, B, st);
-  if (rc != FRNNT_OK) return rc;
-  AmGradProb<real> p2{rw, lm, lmmax, am, ammax, h_p, uni, amonly, am_grad, S1, T, C};
-  rc = launch_contraction<real>(p2, T, C, B, st);
-  if (rc != FRNNT_OK) return rc;
+  int rc;
+  if (use_tensor_cores<real>(lm, am, S1, T, C)) {
+    rc = launch_simple_grads_umma((const float *)lm, (const float *)am, (const float *)lmmax,
+                                  (const float *)lmsum, (const float *)ammax, (const float *)amonly,
+                                  (const float *)uni, (const float *)rw, (const float *)gl_p,
+                                  (const float *)h_p, (const float *)dp_p, (const float *)rowdot_p,
+                                  (float *)lm_grad, (float *)am_grad, B, S1, T, C, Tp, st);
+    if (rc != FRNNT_OK) return rc;
+  } else {
+    LmGradProb<real> p1{rw, am, ammax, lm, lmmax, lmsum, gl_p, dp_p, rowdot_p, lm_grad, S1, T, C, Tp};
+    rc = launch_contraction<real>(p1, S1, C, B, st);
+    if (rc != FRNNT_OK) return rc;
+    AmGradProb<real> p2{rw, lm, lmmax, am, ammax, h_p, uni, amonly, am_grad, S1, T, C, Tp};
+    rc = launch_contraction<real>(p2, T, C, B, st);
+    if (rc != FRNNT_OK) return rc;
+  }
 
   const real coef_lm = (real)cfg.both + (real)cfg.ls;
   const real coef_am = (real)cfg.both + (am_only_active || !cfg.smoothed ? (real)cfg.as : (real)0);

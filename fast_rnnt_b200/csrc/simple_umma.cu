@@ -27,6 +27,7 @@
 // Every mbarrier wait is bounded; on a timeout the tile is poisoned with NaN.
 #include "common.cuh"
 #include "umma.cuh"
+#include "umma_gemm.cuh"
 
 namespace frnnt {
 
@@ -268,6 +269,137 @@ int launch_norm_umma(const float *lm, const float *am, const float *lmmax, const
   dim3 grid((unsigned)((T + kUmBM - 1) / kUmBM), (unsigned)B, (unsigned)((S1 + kUmBN - 1) / kUmBN));
   FRNNT_KERNEL(norm_umma_kernel<<<grid, kUmThreads, smem, st>>>(lm, am, lmmax, ammax, norm, S1, T, C));
   FRNNT_CUDA(cudaGetLastError());
+  return FRNNT_OK;
+}
+
+// ---- gradient contractions -------------------------------------------------------------
+// dlm[s][c] = -L[s][c] * sum_t Rw[s][t] A[t][c]  (+ lm-only / unigram terms)
+//   tile: M = c (lanes, so the stores along c are contiguous), N = s, K = t
+//   A operand = e^{am[t][c]-ammax[t]}: contiguous along c -> MN-major
+//   B operand = Rw[s][t]:               contiguous along t -> K-major
+struct LmGradUmma {
+  static constexpr bool A_MN = true, B_MN = false;
+  const float *am, *ammax, *rw, *lm, *lmmax, *lmsum, *gl, *dp, *rowdot;
+  float *lm_grad;
+  int S1, T, C, Tp;
+  __device__ void init(int b) {
+    am += (size_t)b * T * C;
+    ammax += (size_t)b * T;
+    rw += (size_t)b * S1 * Tp;
+    lm += (size_t)b * S1 * C;
+    lmmax += (size_t)b * S1;
+    lmsum += (size_t)b * S1;
+    if (gl) gl += (size_t)b * S1;
+    if (rowdot) rowdot += (size_t)b * S1;
+    lm_grad += (size_t)b * S1 * C;
+  }
+  __device__ int K() const { return T; }
+  __device__ float4 a4(int c, int t) const {
+    if (c >= C || t >= T) return make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 v = *reinterpret_cast<const float4 *>(am + (size_t)t * C + c);
+    const float m = ammax[t];
+    return make_float4(expf(v.x - m), expf(v.y - m), expf(v.z - m), expf(v.w - m));
+  }
+  __device__ float4 b4(int s, int t) const {
+    if (s >= S1 || t >= Tp) return make_float4(0.f, 0.f, 0.f, 0.f);
+    return *reinterpret_cast<const float4 *>(rw + (size_t)s * Tp + t);
+  }
+  __device__ void store(int c, int s0, const float (&acc)[16]) const {
+    if (c >= C) return;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int s = s0 + i;
+      if (s >= S1) break;
+      const float L = expf(lm[(size_t)s * C + c] - lmmax[s]);
+      float v = -(L * acc[i]);
+      if (gl != nullptr) {
+        const float P = L / lmsum[s];
+        v -= gl[s] * P;
+        if (dp != nullptr) v += P * (dp[c] - rowdot[s]);
+      }
+      lm_grad[(size_t)s * C + c] = v;
+    }
+  }
+  __device__ void poison(int c, int s0) const {
+    if (c >= C) return;
+    for (int i = 0; i < 16 && s0 + i < S1; ++i) lm_grad[(size_t)(s0 + i) * C + c] = NAN;
+  }
+};
+
+// dam[t][c] = -A[t][c] * sum_s Rw[s][t] L[s][c]  (+ am-only term)
+//   tile: M = c, N = t, K = s;  A operand = e^{lm[s][c]-lmmax[s]} (MN-major),
+//   B operand = Rw[s][t] (contiguous along t = N -> MN-major)
+struct AmGradUmma {
+  static constexpr bool A_MN = true, B_MN = true;
+  const float *lm, *lmmax, *rw, *am, *ammax, *h, *uni, *amonly;
+  float *am_grad;
+  int S1, T, C, Tp;
+  __device__ void init(int b) {
+    lm += (size_t)b * S1 * C;
+    lmmax += (size_t)b * S1;
+    rw += (size_t)b * S1 * Tp;
+    am += (size_t)b * T * C;
+    ammax += (size_t)b * T;
+    if (h) {
+      h += (size_t)b * T;
+      amonly += (size_t)b * T;
+    }
+    am_grad += (size_t)b * T * C;
+  }
+  __device__ int K() const { return S1; }
+  __device__ float4 a4(int c, int s) const {
+    if (c >= C || s >= S1) return make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 v = *reinterpret_cast<const float4 *>(lm + (size_t)s * C + c);
+    const float m = lmmax[s];
+    return make_float4(expf(v.x - m), expf(v.y - m), expf(v.z - m), expf(v.w - m));
+  }
+  __device__ float4 b4(int t, int s) const {
+    if (t >= Tp || s >= S1) return make_float4(0.f, 0.f, 0.f, 0.f);
+    return *reinterpret_cast<const float4 *>(rw + (size_t)s * Tp + t);
+  }
+  __device__ void store(int c, int t0, const float (&acc)[16]) const {
+    if (c >= C) return;
+    const float u = h != nullptr ? uni[c] : 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int t = t0 + i;
+      if (t >= T) break;
+      const float A = expf(am[(size_t)t * C + c] - ammax[t]);
+      float v = -(A * acc[i]);
+      if (h != nullptr) v -= h[t] * A * u * expf(ammax[t] - amonly[t]);
+      am_grad[(size_t)t * C + c] = v;
+    }
+  }
+  __device__ void poison(int c, int t0) const {
+    if (c >= C) return;
+    for (int i = 0; i < 16 && t0 + i < T; ++i) am_grad[(size_t)(t0 + i) * C + c] = NAN;
+  }
+};
+
+int launch_simple_grads_umma(const float *lm, const float *am, const float *lmmax,
+                             const float *lmsum, const float *ammax, const float *amonly,
+                             const float *uni, const float *rw, const float *gl, const float *h,
+                             const float *dp, const float *rowdot, float *lm_grad, float *am_grad,
+                             int B, int S1, int T, int C, int Tp, cudaStream_t st) {
+  const int ctiles = (C + kGemmTile - 1) / kGemmTile;
+  {
+    LmGradUmma pol{am, ammax, rw, lm, lmmax, lmsum, gl, dp, rowdot, lm_grad, S1, T, C, Tp};
+    auto kern = umma_gemm_kernel<LmGradUmma>;
+    FRNNT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    (int)kGemmSmemBytes));
+    dim3 grid((unsigned)ctiles, (unsigned)B, (unsigned)((S1 + kGemmTile - 1) / kGemmTile));
+    FRNNT_KERNEL(kern<<<grid, kGemmThreads, kGemmSmemBytes, st>>>(pol));
+    FRNNT_CUDA(cudaGetLastError());
+  }
+  if (T > 0) {
+    AmGradUmma pol{lm, lmmax, rw, am, ammax, h, uni, amonly, am_grad, S1, T, C, Tp};
+    auto kern = umma_gemm_kernel<AmGradUmma>;
+    FRNNT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    (int)kGemmSmemBytes));
+    dim3 grid((unsigned)ctiles, (unsigned)B, (unsigned)((T + kGemmTile - 1) / kGemmTile));
+    FRNNT_KERNEL(kern<<<grid, kGemmThreads, kGemmSmemBytes, st>>>(pol));
+    FRNNT_CUDA(cudaGetLastError());
+  }
   return FRNNT_OK;
 }
 

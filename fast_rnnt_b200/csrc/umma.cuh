@@ -9,9 +9,11 @@
 //     tiles start on 1024-byte boundaries;
 //   * K-major operand  (the 128-byte rows run along K):   rows = M or N index,
 //     SBO = 1024 (next group of 8 rows);  one K=8 step = 32 bytes further in the row;
-//   * MN-major operand (the 128-byte rows run along M/N): rows = K index,
-//     LBO = bytes to the next block of 32 M/N values, SBO = 1024 (next 8 k);
-//     one K=8 step = one atom (1024 bytes) further;
+//   * MN-major operand (the 128-byte rows run along M/N): rows = K index.  For
+//     32-bit (tf32) data the only MN-major layout is "128B swizzle with 32-byte
+//     base" (layout type 1): atoms of 4 k-rows x 128 bytes, the 32-byte chunk c
+//     of row r sits at chunk (c ^ (r & 3)); LBO = bytes to the next block of 32
+//     M/N values, SBO = 512 (next 4 k); one K=8 step = two atoms (1024 bytes);
 //   * every wait is bounded: a wait that runs out returns false, the kernel
 //     poisons its output, frees its tensor memory and returns.
 #pragma once
@@ -111,15 +113,16 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const float (&v)[16]) 
 }
 
 // ---- descriptors ----------------------------------------------------------------------------
-// shared-memory matrix descriptor, 128-byte swizzle (layout type 2), version 1 (sm_100)
+// shared-memory matrix descriptor, version 1 (sm_100); layout type 2 = 128-byte
+// swizzle (16-byte base), 1 = 128-byte swizzle with 32-byte base
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr, uint32_t lbo_bytes,
-                                                    uint32_t sbo_bytes) {
+                                                    uint32_t sbo_bytes, uint32_t layout_type = 2) {
   uint64_t d = 0;
   d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
   d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
   d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
   d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
+  d |= (uint64_t)layout_type << 61;
   return d;
 }
 // instruction descriptor for kind::tf32, fp32 accumulate
