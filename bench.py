@@ -33,7 +33,12 @@ L2_FLUSH_BYTES = 512 << 20
 
 # DRAM traffic per launch measured once with ncu (dram__bytes_read.sum +
 # dram__bytes_write.sum, profiles/); keyed by stage name, bytes for workload c3.
-NCU_TRAFFIC_C3 = {}
+NCU_TRAFFIC_C3 = {
+    # profiles/kernels_c3_ncu_full.txt
+    "lsm_gather_bwd": 600.2e6, "lsm_gather_fwd": 326.8e6, "prune_gather_fwd": 280.0e6,
+    "prune_gather_bwd": 345.4e6, "mi_forward": 17.3e6, "mi_backward": 19.0e6,
+    "mi_forward_pruned": 17.3e6, "mi_backward_pruned": 19.0e6,
+}
 
 
 def measured_peaks():
@@ -338,11 +343,10 @@ def main():
     resident = {k: v.to(dev) for k, v in host.items()}
     inner = make_step(fr, wl)
 
+    from fast_rnnt_b200 import sharding
+
     def step(t):
-        loss = inner(t)
-        if world > 1:
-            dist.all_reduce(loss)
-        return loss
+        return sharding.allreduce_loss(inner(t))
 
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
 

@@ -294,16 +294,20 @@ struct LmGradUmma {
     lm_grad += (size_t)b * S1 * C;
   }
   __device__ int K() const { return T; }
-  __device__ float4 a4(int c, int t) const {
-    if (c >= C || t >= T) return make_float4(0.f, 0.f, 0.f, 0.f);
-    const float4 v = *reinterpret_cast<const float4 *>(am + (size_t)t * C + c);
-    const float m = ammax[t];
-    return make_float4(expf(v.x - m), expf(v.y - m), expf(v.z - m), expf(v.w - m));
+  // exp(-inf - 0) = 0 outside the matrix
+  __device__ Raw4 a_raw(int c, int t) const {
+    if (c >= C || t >= T) return Raw4{make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY), 0.f};
+    return Raw4{*reinterpret_cast<const float4 *>(am + (size_t)t * C + c), ammax[t]};
   }
-  __device__ float4 b4(int s, int t) const {
-    if (s >= S1 || t >= Tp) return make_float4(0.f, 0.f, 0.f, 0.f);
-    return *reinterpret_cast<const float4 *>(rw + (size_t)s * Tp + t);
+  __device__ float4 a_fix(const Raw4 &r) const {
+    return make_float4(expf(r.v.x - r.aux), expf(r.v.y - r.aux), expf(r.v.z - r.aux),
+                       expf(r.v.w - r.aux));
   }
+  __device__ Raw4 b_raw(int s, int t) const {
+    if (s >= S1 || t >= Tp) return Raw4{make_float4(0.f, 0.f, 0.f, 0.f), 0.f};
+    return Raw4{*reinterpret_cast<const float4 *>(rw + (size_t)s * Tp + t), 0.f};
+  }
+  __device__ float4 b_fix(const Raw4 &r) const { return r.v; }
   __device__ void store(int c, int s0, const float (&acc)[16]) const {
     if (c >= C) return;
 #pragma unroll
@@ -347,16 +351,19 @@ struct AmGradUmma {
     am_grad += (size_t)b * T * C;
   }
   __device__ int K() const { return S1; }
-  __device__ float4 a4(int c, int s) const {
-    if (c >= C || s >= S1) return make_float4(0.f, 0.f, 0.f, 0.f);
-    const float4 v = *reinterpret_cast<const float4 *>(lm + (size_t)s * C + c);
-    const float m = lmmax[s];
-    return make_float4(expf(v.x - m), expf(v.y - m), expf(v.z - m), expf(v.w - m));
+  __device__ Raw4 a_raw(int c, int s) const {
+    if (c >= C || s >= S1) return Raw4{make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY), 0.f};
+    return Raw4{*reinterpret_cast<const float4 *>(lm + (size_t)s * C + c), lmmax[s]};
   }
-  __device__ float4 b4(int t, int s) const {
-    if (t >= Tp || s >= S1) return make_float4(0.f, 0.f, 0.f, 0.f);
-    return *reinterpret_cast<const float4 *>(rw + (size_t)s * Tp + t);
+  __device__ float4 a_fix(const Raw4 &r) const {
+    return make_float4(expf(r.v.x - r.aux), expf(r.v.y - r.aux), expf(r.v.z - r.aux),
+                       expf(r.v.w - r.aux));
   }
+  __device__ Raw4 b_raw(int t, int s) const {
+    if (t >= Tp || s >= S1) return Raw4{make_float4(0.f, 0.f, 0.f, 0.f), 0.f};
+    return Raw4{*reinterpret_cast<const float4 *>(rw + (size_t)s * Tp + t), 0.f};
+  }
+  __device__ float4 b_fix(const Raw4 &r) const { return r.v; }
   __device__ void store(int c, int t0, const float (&acc)[16]) const {
     if (c >= C) return;
     const float u = h != nullptr ? uni[c] : 0.f;

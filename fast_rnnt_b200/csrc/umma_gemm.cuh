@@ -17,8 +17,11 @@
 //   static constexpr bool A_MN, B_MN;      operand is contiguous along M/N (true) or K (false)
 //   void  init(int batch);                  select the batch
 //   int   K() const;
-//   float4 a4(int m, int k) const;          A_MN: (m..m+3, k)   else: (m, k..k+3); zeros outside
-//   float4 b4(int n, int k) const;          likewise
+//   Raw4  a_raw(int m, int k) const;        A_MN: (m..m+3, k)   else: (m, k..k+3): the loads only
+//   float4 a_fix(const Raw4&) const;        the arithmetic on them (zeros outside the matrix)
+//   Raw4  b_raw(int n, int k) const;  float4 b_fix(const Raw4&) const;      likewise
+//     (split so that the loads of the next stage stay in flight across the
+//      barrier and the MMA issue of the current one)
 //   void  store(int m, int n0, const float (&acc)[16]);   columns n0..n0+15 of row m
 //   void  poison(int m, int n0);            same footprint, called instead of store on a timeout
 #pragma once
@@ -32,6 +35,12 @@ constexpr int kGemmTile = 128;   // M and N of a CTA tile
 constexpr int kGemmBK = 32;      // K per stage
 constexpr int kGemmStages = 2;
 constexpr int kGemmGroup = 2;    // stages per accumulator group (K = 64)
+// four raw values plus one per-row scalar (e.g. the row maximum an exp() needs)
+struct Raw4 {
+  float4 v;
+  float aux;
+};
+
 constexpr size_t kGemmSmemBytes = (size_t)kGemmStages * 4 * kGemmTile * 128 + 1024;
 
 // byte offset inside an MN-major [32 k][128 mn] tile of the 16-byte chunk
@@ -80,15 +89,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1) umma_gemm_kernel(Pol pol) {
   // staging assignment of this thread, four 16-byte chunks per operand and stage:
   //   K-major : rows (tid>>3) + 32q, k chunk (tid&7)
   //   MN-major: k rows (tid>>5) + 8q, mn chunk (tid&31)
-  float4 ra[4], rb4[4];
+  Raw4 ra[4], rb4[4];
   auto load_stage = [&](int kb) {
     const int k0 = kb * kGemmBK;
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-      ra[q] = Pol::A_MN ? pol.a4(m0 + 4 * (tid & 31), k0 + (tid >> 5) + 8 * q)
-                        : pol.a4(m0 + (tid >> 3) + 32 * q, k0 + 4 * (tid & 7));
-      rb4[q] = Pol::B_MN ? pol.b4(n0 + 4 * (tid & 31), k0 + (tid >> 5) + 8 * q)
-                         : pol.b4(n0 + (tid >> 3) + 32 * q, k0 + 4 * (tid & 7));
+      ra[q] = Pol::A_MN ? pol.a_raw(m0 + 4 * (tid & 31), k0 + (tid >> 5) + 8 * q)
+                        : pol.a_raw(m0 + (tid >> 3) + 32 * q, k0 + 4 * (tid & 7));
+      rb4[q] = Pol::B_MN ? pol.b_raw(n0 + 4 * (tid & 31), k0 + (tid >> 5) + 8 * q)
+                         : pol.b_raw(n0 + (tid >> 3) + 32 * q, k0 + 4 * (tid & 7));
     }
   };
   auto stage_offset = [&](bool mn, int q) -> uint32_t {
@@ -127,11 +136,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) umma_gemm_kernel(Pol pol) {
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       float4 hi, lo;
-      split_tf32(ra[q], hi, lo);
+      split_tf32(pol.a_fix(ra[q]), hi, lo);
       uint32_t o = stage_offset(Pol::A_MN, q);
       *reinterpret_cast<float4 *>(st + o) = hi;
       *reinterpret_cast<float4 *>(st + op_bytes + o) = lo;
-      split_tf32(rb4[q], hi, lo);
+      split_tf32(pol.b_fix(rb4[q]), hi, lo);
       o = stage_offset(Pol::B_MN, q);
       *reinterpret_cast<float4 *>(st + 2 * op_bytes + o) = hi;
       *reinterpret_cast<float4 *>(st + 3 * op_bytes + o) = lo;
