@@ -8,7 +8,8 @@ One "step" is the whole pruned pipeline of the reference's documented usage,
 forward and backward, on one batch of synthetic utterances:
   rnnt_loss_smoothed(return_grad) -> get_rnnt_prune_ranges -> do_rnnt_pruning ->
   joiner Linear(tanh(enc+dec)) -> rnnt_loss_pruned -> (simple+pruned).backward()
-The joiner is the caller's network (plain torch, cuBLAS fp32); everything else
+The joiner is the caller's network: add and tanh in torch, its projection either on this
+library's 3xTF32 tensor-core linear (default) or torch's fp32 linear; everything else
 runs in libfrnnt_sm100.so.  Rank 0 prints ONE JSON line.
 
 Under torchrun every rank works on its own batch (weak scaling); the only
@@ -35,7 +36,7 @@ L2_FLUSH_BYTES = 512 << 20
 # dram__bytes_write.sum, profiles/); keyed by stage name, bytes for workload c3.
 NCU_TRAFFIC_C3 = {
     # profiles/kernels_c3_ncu_full.txt
-    "lsm_gather_bwd": 600.2e6, "lsm_gather_fwd": 326.8e6, "prune_gather_fwd": 280.0e6,
+    "lsm_gather_bwd": 600.2e6, "lsm_gather_fwd": 327.9e6, "prune_gather_fwd": 280.0e6,
     "prune_gather_bwd": 345.4e6, "mi_forward": 17.3e6, "mi_backward": 19.0e6,
     "mi_forward_pruned": 17.3e6, "mi_backward_pruned": 19.0e6,
 }
@@ -108,9 +109,10 @@ class ClockSampler:
 # ------------------------------------------------------------------------------
 # the step
 # ------------------------------------------------------------------------------
-def make_step(fr, wl):
+def make_step(fr, wl, linear=torch.nn.functional.linear):
     """Returns step(inputs) -> loss for the pruned pipeline; `fr` is the loss
-    package (ours on CUDA, or the CPU oracle wrapped to the same names)."""
+    package (ours on CUDA, or the CPU oracle wrapped to the same names) and
+    `linear` the joiner's projection."""
     blank, R = wl["blank"], wl["s_range"]
     ls, as_ = wl["lm_only_scale"], wl["am_only_scale"]
 
@@ -128,7 +130,7 @@ def make_step(fr, wl):
             am_only_scale=as_, boundary=t["boundary"], reduction="sum", return_grad=True)
         ranges = fr.get_rnnt_prune_ranges(px_grad=gx, py_grad=gy, boundary=t["boundary"], s_range=R)
         am_p, lm_p = fr.do_rnnt_pruning(am=enc, lm=dec, ranges=ranges)
-        logits = torch.nn.functional.linear(torch.tanh(am_p + lm_p), W, bias)
+        logits = linear(torch.tanh(am_p + lm_p), W, bias)
         pruned = fr.rnnt_loss_pruned(logits=logits, symbols=t["symbols"], ranges=ranges,
                                      termination_symbol=blank, boundary=t["boundary"],
                                      reduction="sum")
@@ -287,6 +289,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c3", choices=["c3", "c5", "small"])
     ap.add_argument("--batch", type=int, default=None, help="utterances per GPU")
+    ap.add_argument("--joiner", default="tensorcore", choices=["tensorcore", "torch"],
+                    help="projection of the joiner: this library's 3xTF32 tcgen05 linear, or "
+                         "torch.nn.functional.linear (cuBLAS fp32)")
     ap.add_argument("--no-stages", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -302,7 +307,10 @@ def main():
            "B_per_gpu": batch, "T": sizes[1], "S": sizes[2], "C": sizes[3], "D": sizes[4],
            "s_range": sizes[5], "global_batch": batch * world,
            "parallelism": f"batch sharded over {world} GPU(s), scalar-loss all-reduce",
-           "joiner": "torch Linear(tanh(enc+dec)), cuBLAS fp32 (caller's network)",
+           "joiner": ("Linear(tanh(enc+dec)): tanh/add in torch, projection fwd+bwd on tcgen05 with "
+                      "3xTF32 (fp32-level accuracy), fast_rnnt_b200.linear"
+                      if args.joiner == "tensorcore" and args.impl == "ours" else
+                      "torch Linear(tanh(enc+dec)), fp32"),
            "l2": f"flushed between timed steps ({L2_FLUSH_BYTES >> 20} MiB write)"}
 
     # -------------------------------------------------------------- reference arm
@@ -341,7 +349,11 @@ def main():
     wl = workloads.pipeline_workload(args.workload, batch=batch, seed=rank)
     host = {k: wl[k].pin_memory() for k in TENSOR_KEYS}
     resident = {k: v.to(dev) for k, v in host.items()}
-    inner = make_step(fr, wl)
+    if args.joiner == "tensorcore":
+        from fast_rnnt_b200.linear import linear as joiner_linear
+    else:
+        joiner_linear = torch.nn.functional.linear
+    inner = make_step(fr, wl, joiner_linear)
 
     from fast_rnnt_b200 import sharding
 

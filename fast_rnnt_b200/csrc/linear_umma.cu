@@ -1,0 +1,386 @@
+// fp32-accurate (3xTF32) matrix products on the sm_100a tensor cores for plain
+// row-major float matrices, fed by TMA.  Two entry points, the three products a
+// linear layer needs (the joiner between do_rnnt_pruning and rnnt_loss_pruned):
+//
+//   frnnt_matmul_nt:  D[M][N] = A[M][K] * B[N][K]^T (+ bias[N])     forward, and
+//                     grad_input = grad_out * W with B = W^T
+//   frnnt_matmul_tn:  D[M][N] = A[R][M]^T * B[R][N]                 grad_weight,
+//                     the long reduction over R is split over CTAs (partial sums
+//                     in a caller scratch, added in a fixed order)
+//
+// Kernel structure (one 128x128 output tile per CTA, 10 warps):
+//   warp 0   : TMA producer.  cp.async.bulk.tensor loads the raw fp32 operand
+//              tiles of a 32-wide K slice straight into the 128-byte-swizzled
+//              layouts the tensor core reads (K-major: swizzle 128B; operands
+//              that are contiguous along M/N: swizzle 128B with 32-byte atoms),
+//              completion on an mbarrier; 3-stage ring.
+//   warps 2-9: split every landed value x into tf32 hi = trunc(x) (in place)
+//              and lo = x - hi (second buffer) -- an element-wise pass over
+//              shared memory that does not care about the tile layout.
+//   warp 1   : one thread issues hi*hi, hi*lo, lo*hi tcgen05.mma per K=8 step
+//              into a 128x128 fp32 accumulator in tensor memory; tcgen05.commit
+//              hands the stage back to the producer.  The tensor core adds into
+//              its accumulator with truncation (a bias of ~half an ulp per
+//              step), so every 128-wide K group gets a fresh accumulator and
+//   warps 2-9  fold finished groups into a running sum with round-to-nearest
+//              adds (tcgen05.ld / add / tcgen05.st), one group behind the MMAs;
+//   warps 2-9: epilogue, tcgen05.ld -> (+bias) -> 64-byte row segments.
+// No multicast, no clusters.  Every wait is bounded; a timeout poisons the tile.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include "common.cuh"
+#include "umma.cuh"
+
+namespace frnnt {
+using namespace umma;
+
+constexpr int kLinThreads = 320;   // TMA warp, MMA warp, 8 split / fold / epilogue warps
+constexpr int kLinWorkers = 8;
+constexpr int kLinTile = 128;
+constexpr int kLinBK = 32;
+constexpr int kLinStages = 3;
+constexpr int kLinGroup = 4;   // K slices per accumulator group
+constexpr uint32_t kLinOpBytes = kLinTile * 128;          // one operand tile
+constexpr uint32_t kLinStageBytes = 4 * kLinOpBytes;      // A_raw, B_raw, A_lo, B_lo
+constexpr size_t kLinSmemBytes = (size_t)kLinStages * kLinStageBytes + 1024;
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// 2-D tiled TMA load: box at (x = innermost coordinate, y) -> shared memory, bytes counted on bar
+__device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap *map, int x, int y,
+                                            uint64_t *bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_dst), "l"((uint64_t)map), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+
+struct LinParams {
+  float *out;          // [splits][M][N] (splits == 1: the result itself)
+  const float *bias;   // [N] or nullptr
+  int M, N, K;         // K = reduction length
+  int k_per_split;     // multiple of kLinBK
+};
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kLinThreads, 1)
+linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                   LinParams p) {
+  extern __shared__ uint8_t smem_dyn[];
+  __shared__ __align__(8) uint64_t bar_full[kLinStages];   // TMA bytes have landed
+  __shared__ __align__(8) uint64_t bar_split[kLinStages];  // hi / lo are ready
+  __shared__ __align__(8) uint64_t bar_empty[kLinStages];  // the MMAs are done with the stage
+  __shared__ __align__(8) uint64_t bar_grp[2];             // a group's accumulator is complete
+  __shared__ __align__(8) uint64_t bar_fold[2];            // ... and has been folded away
+  __shared__ uint32_t tmem_slot;
+  __shared__ int failed;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n0 = blockIdx.x * kLinTile, m0 = blockIdx.y * kLinTile;
+  const int k_begin = blockIdx.z * p.k_per_split;
+  const int k_end = min(p.K, k_begin + p.k_per_split);
+  const int KB = k_end > k_begin ? (k_end - k_begin + kLinBK - 1) / kLinBK : 0;
+  const uint32_t tiles = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+  uint8_t *tiles_ptr = smem_dyn + (tiles - smem_u32(smem_dyn));
+  constexpr uint32_t kCols = 512, kAcc1 = 128, kRun = 256;  // two group accumulators + running sum
+  const int NG = (KB + kLinGroup - 1) / kLinGroup;
+
+  if (tid == 0) {
+    for (int s = 0; s < kLinStages; ++s) {
+      mbar_init(&bar_full[s], 1);
+      mbar_init(&bar_split[s], kLinWorkers);
+      mbar_init(&bar_empty[s], 1);
+    }
+    for (int r = 0; r < 2; ++r) {
+      mbar_init(&bar_grp[r], 1);
+      mbar_init(&bar_fold[r], kLinWorkers);
+    }
+    failed = 0;
+    mbar_init_fence();
+  }
+  if (warp == 1) tmem_alloc(&tmem_slot, kCols);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_d = tmem_slot;
+  volatile int *vfailed = &failed;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < KB && !*vfailed; ++kb) {
+        const int s = kb % kLinStages;
+        if (kb >= kLinStages && !mbar_wait(&bar_empty[s], (uint32_t)((kb / kLinStages - 1) & 1))) {
+          *vfailed = 1;
+          break;
+        }
+        const int k0 = k_begin + kb * kLinBK;
+        const uint32_t st = tiles + (uint32_t)s * kLinStageBytes;
+        mbar_expect_tx(&bar_full[s], 2 * kLinOpBytes);
+        if (A_MN) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) tma_load_2d(st + j * 4096, &map_a, m0 + 32 * j, k0, &bar_full[s]);
+        } else {
+          tma_load_2d(st, &map_a, k0, m0, &bar_full[s]);
+        }
+        if (B_MN) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            tma_load_2d(st + kLinOpBytes + j * 4096, &map_b, n0 + 32 * j, k0, &bar_full[s]);
+        } else {
+          tma_load_2d(st + kLinOpBytes, &map_b, k0, n0, &bar_full[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = idesc_tf32(kLinTile, kLinTile, A_MN, B_MN);
+      for (int kb = 0; kb < KB && !*vfailed; ++kb) {
+        const int s = kb % kLinStages;
+        const int g = kb / kLinGroup;
+        const bool group_start = kb % kLinGroup == 0;
+        // the accumulator of group g was last used by group g-2: it must be folded away
+        if (group_start && g >= 2 && !mbar_wait(&bar_fold[g & 1], (uint32_t)(((g - 2) >> 1) & 1))) {
+          *vfailed = 1;
+          break;
+        }
+        if (!mbar_wait(&bar_split[s], (uint32_t)((kb / kLinStages) & 1))) {
+          *vfailed = 1;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t acc = tmem_d + ((g & 1) ? kAcc1 : 0u);
+        const uint32_t st = tiles + (uint32_t)s * kLinStageBytes;
+#pragma unroll
+        for (int ks = 0; ks < kLinBK / 8; ++ks) {
+          const uint32_t ao = A_MN ? ks * 1024u : ks * 32u, bo = B_MN ? ks * 1024u : ks * 32u;
+          const uint32_t a_lbo = A_MN ? 4096u : 16u, b_lbo = B_MN ? 4096u : 16u;
+          const uint32_t a_sbo = A_MN ? 512u : 1024u, b_sbo = B_MN ? 512u : 1024u;
+          const uint32_t a_lt = A_MN ? 1u : 2u, b_lt = B_MN ? 1u : 2u;
+          const uint64_t dah = smem_desc_sw128(st + ao, a_lbo, a_sbo, a_lt);
+          const uint64_t dbh = smem_desc_sw128(st + kLinOpBytes + bo, b_lbo, b_sbo, b_lt);
+          const uint64_t dal = smem_desc_sw128(st + 2 * kLinOpBytes + ao, a_lbo, a_sbo, a_lt);
+          const uint64_t dbl = smem_desc_sw128(st + 3 * kLinOpBytes + bo, b_lbo, b_sbo, b_lt);
+          mma_tf32(acc, dah, dbh, idesc, (!group_start || ks > 0) ? 1u : 0u);
+          mma_tf32(acc, dah, dbl, idesc, 1u);
+          mma_tf32(acc, dal, dbh, idesc, 1u);
+        }
+        mma_commit(&bar_empty[s]);
+        if (kb % kLinGroup == kLinGroup - 1 || kb == KB - 1) mma_commit(&bar_grp[g & 1]);
+      }
+    }
+  } else {
+    // ---- split pass, folding one group behind ------------------------------------------------
+    const int st_tid = tid - 64;  // 0..255
+    const int quarter = warp & 3;          // tensor-memory lanes 32*quarter..
+    const int ch_lo = ((warp - 2) >> 2) * (kLinTile / 32), ch_hi = ch_lo + kLinTile / 32;  // column half
+    const uint32_t lane_base = (uint32_t)(32 * quarter) << 16;
+    // running sum (+)= accumulator of group g (this warp's 32 lanes and column half)
+    auto fold_group = [&](int g) -> bool {
+      if (!mbar_wait(&bar_grp[g & 1], (uint32_t)((g >> 1) & 1))) return false;
+      tc_fence_after_sync();
+      const uint32_t acc = tmem_d + lane_base + ((g & 1) ? kAcc1 : 0u), run = tmem_d + lane_base + kRun;
+      for (int ch = ch_lo; ch < ch_hi; ++ch) {
+        float pv[16], rv[16];
+        tmem_ld16(acc + ch * 16, pv);
+        if (g > 0) {
+          tmem_ld16(run + ch * 16, rv);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) pv[i] = rv[i] + pv[i];
+        }
+        tmem_st16(run + ch * 16, pv);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar_fold[g & 1]);
+      return true;
+    };
+    bool ok = true;
+    for (int kb = 0; kb < KB && ok && !*vfailed; ++kb) {
+      const int s = kb % kLinStages;
+      if (!mbar_wait(&bar_full[s], (uint32_t)((kb / kLinStages) & 1))) {
+        ok = false;
+        break;
+      }
+      float4 *raw = reinterpret_cast<float4 *>(tiles_ptr + (size_t)s * kLinStageBytes);
+      float4 *lo = raw + (2 * kLinOpBytes) / 16;
+#pragma unroll 4
+      for (int c = st_tid; c < (int)(2 * kLinOpBytes / 16); c += 32 * kLinWorkers) {
+        const float4 x = raw[c];
+        float4 h, l;
+        split_tf32(x, h, l);
+        raw[c] = h;
+        lo[c] = l;
+      }
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar_split[s]);
+      // the previous group was fully issued before this slice: fold it while the MMAs go on
+      if (kb % kLinGroup == 0 && kb >= kLinGroup)
+        ok = __all_sync(0xffffffffu, fold_group(kb / kLinGroup - 1));
+    }
+    // ---- epilogue ---------------------------------------------------------------------------
+    ok = ok && !*vfailed;
+    if (ok && NG >= 1) ok = fold_group(NG - 1);
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) *vfailed = 1;
+    tc_fence_after_sync();
+    const int m = m0 + 32 * quarter + lane;
+    float *out = p.out + (size_t)blockIdx.z * p.M * p.N;
+    const bool vec = (p.N % 4) == 0;
+    for (int ch = ch_lo; ch < ch_hi; ++ch) {
+      float v[16];
+      if (ok && KB > 0) {
+        tmem_ld16(tmem_d + lane_base + kRun + (uint32_t)(ch * 16), v);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = ok ? 0.f : NAN;
+      }
+      const int n = n0 + ch * 16;
+      if (m < p.M && n < p.N) {
+        if (p.bias != nullptr) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            if (n + i < p.N) v[i] += p.bias[n + i];
+        }
+        float *dst = out + (size_t)m * p.N + n;
+        if (vec && n + 16 <= p.N) {
+#pragma unroll
+          for (int i = 0; i < 16; i += 4)
+            *reinterpret_cast<float4 *>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            if (n + i < p.N) dst[i] = v[i];
+        }
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_d, kCols);
+}
+
+// out[i] = sum over splits of partial[z][i], z in order
+__global__ void splitk_reduce_kernel(const float *__restrict__ partial, float *__restrict__ out,
+                                     long long n, int splits) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float acc = 0;
+  for (int z = 0; z < splits; ++z) acc += partial[(size_t)z * n + i];
+  out[i] = acc;
+}
+
+// ---- host -----------------------------------------------------------------------------------
+static PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  if (fn == nullptr) {
+    void *ptr = nullptr;
+    cudaDriverEntryPointQueryResult res;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res) == cudaSuccess &&
+        res == cudaDriverEntryPointSuccess)
+      fn = (PFN_cuTensorMapEncodeTiled_v12000)ptr;
+  }
+  return fn;
+}
+
+// map of a row-major float matrix [rows][cols]; box = box_cols x box_rows
+static int make_map(CUtensorMap *map, const float *base, int rows, int cols, int box_cols,
+                    int box_rows, bool atom32) {
+  auto enc = tensor_map_encoder();
+  FRNNT_REQUIRE(enc != nullptr, FRNNT_ECUDA, "cuTensorMapEncodeTiled is not available");
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)cols * sizeof(float)};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void *)base, dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  FRNNT_REQUIRE(r == CUDA_SUCCESS, FRNNT_ECUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
+  return FRNNT_OK;
+}
+
+static int check_matrix(const void *p, int cols, const char *what) {
+  FRNNT_REQUIRE(p != nullptr, FRNNT_EINVAL, "%s is NULL", what);
+  FRNNT_REQUIRE((uintptr_t)p % 16 == 0 && cols % 4 == 0, FRNNT_EUNSUPPORTED,
+                "%s: TMA needs a 16-byte aligned base and a row length that is a multiple of 4 floats",
+                what);
+  return FRNNT_OK;
+}
+
+}  // namespace frnnt
+
+using namespace frnnt;
+
+extern "C" int frnnt_matmul_nt(const float *a, const float *b, const float *bias, float *d, int M,
+                               int N, int K, void *stream) {
+  FRNNT_REQUIRE(M >= 0 && N >= 0 && K >= 0, FRNNT_EINVAL, "negative size");
+  if (M == 0 || N == 0) return FRNNT_OK;
+  FRNNT_REQUIRE(K > 0, FRNNT_EINVAL, "K must be positive");
+  int rc = check_matrix(a, K, "a");
+  if (rc == FRNNT_OK) rc = check_matrix(b, K, "b");
+  if (rc != FRNNT_OK) return rc;
+  FRNNT_REQUIRE(d != nullptr && (uintptr_t)d % 16 == 0, FRNNT_EINVAL, "d is NULL or misaligned");
+  CUtensorMap ma, mb;
+  rc = make_map(&ma, a, M, K, kLinBK, kLinTile, false);
+  if (rc == FRNNT_OK) rc = make_map(&mb, b, N, K, kLinBK, kLinTile, false);
+  if (rc != FRNNT_OK) return rc;
+  auto kern = linear_umma_kernel<false, false>;
+  FRNNT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLinSmemBytes));
+  const int mt = (M + kLinTile - 1) / kLinTile, nt = (N + kLinTile - 1) / kLinTile;
+  FRNNT_REQUIRE(mt <= 65535, FRNNT_EUNSUPPORTED, "M too large for the grid");
+  LinParams p{d, bias, M, N, K, ((K + kLinBK - 1) / kLinBK) * kLinBK};
+  FRNNT_KERNEL(kern<<<dim3(nt, mt, 1), kLinThreads, kLinSmemBytes, (cudaStream_t)stream>>>(ma, mb, p));
+  FRNNT_CUDA(cudaGetLastError());
+  return FRNNT_OK;
+}
+
+extern "C" int frnnt_matmul_tn_splits(int M, int N, int R) {
+  if (M <= 0 || N <= 0 || R <= 0) return 1;
+  const int tiles = ((M + kLinTile - 1) / kLinTile) * ((N + kLinTile - 1) / kLinTile);
+  int splits = (2 * 148 + tiles - 1) / tiles;                 // about two CTAs' worth per SM
+  const int max_splits = (R + 8 * kLinBK - 1) / (8 * kLinBK);  // at least 8 K slices per CTA
+  if (splits > max_splits) splits = max_splits;
+  if (splits < 1) splits = 1;
+  return splits;
+}
+
+extern "C" int frnnt_matmul_tn(const float *a, const float *b, float *d, float *partials, int M,
+                               int N, int R, void *stream) {
+  FRNNT_REQUIRE(M >= 0 && N >= 0 && R >= 0, FRNNT_EINVAL, "negative size");
+  if (M == 0 || N == 0) return FRNNT_OK;
+  FRNNT_REQUIRE(R > 0, FRNNT_EINVAL, "R must be positive");
+  int rc = check_matrix(a, M, "a");
+  if (rc == FRNNT_OK) rc = check_matrix(b, N, "b");
+  if (rc != FRNNT_OK) return rc;
+  FRNNT_REQUIRE(d != nullptr && (uintptr_t)d % 16 == 0, FRNNT_EINVAL, "d is NULL or misaligned");
+  const int splits = frnnt_matmul_tn_splits(M, N, R);
+  FRNNT_REQUIRE(splits == 1 || (partials != nullptr && (uintptr_t)partials % 16 == 0), FRNNT_EINVAL,
+                "partials scratch of splits*M*N floats is required");
+  CUtensorMap ma, mb;
+  // operands contiguous along M / N: boxes of 32 values x 32 reduction rows, 32-byte swizzle atoms
+  rc = make_map(&ma, a, R, M, 32, kLinBK, true);
+  if (rc == FRNNT_OK) rc = make_map(&mb, b, R, N, 32, kLinBK, true);
+  if (rc != FRNNT_OK) return rc;
+  auto kern = linear_umma_kernel<true, true>;
+  FRNNT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLinSmemBytes));
+  const int mt = (M + kLinTile - 1) / kLinTile, nt = (N + kLinTile - 1) / kLinTile;
+  const int kblocks = (R + kLinBK - 1) / kLinBK;
+  const int k_per_split = ((kblocks + splits - 1) / splits) * kLinBK;
+  LinParams p{splits == 1 ? d : partials, nullptr, M, N, R, k_per_split};
+  cudaStream_t st = (cudaStream_t)stream;
+  FRNNT_KERNEL(kern<<<dim3(nt, mt, splits), kLinThreads, kLinSmemBytes, st>>>(ma, mb, p));
+  FRNNT_CUDA(cudaGetLastError());
+  if (splits > 1) {
+    const long long n = (long long)M * N;
+    FRNNT_KERNEL(splitk_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(partials, d, n, splits));
+    FRNNT_CUDA(cudaGetLastError());
+  }
+  return FRNNT_OK;
+}

@@ -156,11 +156,17 @@ __device__ __forceinline__ void mma_commit(uint64_t *bar) {
 }
 
 // ---- 3xTF32 split ---------------------------------------------------------------------------------
-// x = hi + lo with hi exactly representable in tf32 (low 13 mantissa bits zero);
-// hi*hi + hi*lo + lo*hi recovers fp32-level products on the tf32 pipe.
+// x ~= hi + lo, both rounded to nearest tf32 (cvt.rna; low 13 mantissa bits
+// zero, so the tensor core's own conversion changes nothing); hi*hi + hi*lo +
+// lo*hi then carries ~2^-22 relative error per product, unbiased.
+__device__ __forceinline__ float round_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
 __device__ __forceinline__ void split_tf32(float x, float &hi, float &lo) {
-  hi = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
-  lo = x - hi;
+  hi = round_tf32(x);
+  lo = round_tf32(x - hi);
 }
 __device__ __forceinline__ void split_tf32(const float4 &x, float4 &hi, float4 &lo) {
   split_tf32(x.x, hi.x, lo.x);

@@ -204,6 +204,28 @@ int frnnt_prune_gather(int dtype, const void *lm, const int64_t *ranges, void *o
 int frnnt_prune_gather_backward(int dtype, const void *out_grad, const int64_t *ranges,
                                 void *lm_grad, int B, int S1, int T, int R, int D, void *stream);
 
+/* ----------------------------------------------------------------------------
+ * fp32-accurate matrix products for the caller's joiner (next to the hot path)
+ * ------------------------------------------------------------------------- */
+
+/* The reference leaves the joiner between do_rnnt_pruning and rnnt_loss_pruned
+ * to the caller (README.md:180-190: a Linear over tanh(am_pruned + lm_pruned));
+ * it has no counterpart of these two functions.  They run the three products
+ * of a linear layer on the tensor cores with 3xTF32 splitting (fp32-level
+ * accuracy), fed by TMA.  All matrices are row-major float32 with 16-byte
+ * aligned bases and row lengths that are multiples of 4.
+ *
+ * D[M][N] = A[M][K] * B[N][K]^T (+ bias[N] if not NULL). */
+int frnnt_matmul_nt(const float *a, const float *b, const float *bias, float *d, int M, int N,
+                    int K, void *stream);
+
+/* D[M][N] = A[R][M]^T * B[R][N].  The reduction over R is split over
+ * frnnt_matmul_tn_splits(M, N, R) CTAs per output tile; `partials` is scratch of
+ * splits*M*N floats (may be NULL when splits == 1). */
+int frnnt_matmul_tn_splits(int M, int N, int R);
+int frnnt_matmul_tn(const float *a, const float *b, float *d, float *partials, int M, int N, int R,
+                    void *stream);
+
 #ifdef __cplusplus
 }
 #endif
