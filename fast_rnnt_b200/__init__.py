@@ -18,6 +18,10 @@ from .rnnt_loss import rnnt_loss_simple  # noqa: F401
 from .rnnt_loss import rnnt_loss_smoothed  # noqa: F401
 
 
+# additions that have no counterpart in the reference (the caller's joiner on the tensor cores)
+from .linear import linear, pruned_joiner  # noqa: F401,E402
+
+
 def with_cuda() -> bool:
     """Counterpart of ``_fast_rnnt.with_cuda`` (always True here; raises if the
     CUDA library has not been built)."""

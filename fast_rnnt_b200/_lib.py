@@ -16,6 +16,7 @@ F32, F64 = 0, 1
 _lib = None
 
 _c_int, _c_vp, _c_sz, _c_f64 = ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_double
+_c_longlong = ctypes.c_longlong
 
 
 class FrnntError(RuntimeError):

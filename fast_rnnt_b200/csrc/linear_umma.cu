@@ -64,6 +64,7 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap
 struct LinParams {
   float *out;          // [splits][M][N] (splits == 1: the result itself)
   const float *bias;   // [N] or nullptr
+  const float *tanh_out;  // [M][N] or nullptr: the result is multiplied by 1 - tanh_out^2
   int M, N, K;         // K = reduction length
   int k_per_split;     // multiple of kLinBK
 };
@@ -248,6 +249,12 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
           for (int i = 0; i < 16; ++i)
             if (n + i < p.N) v[i] += p.bias[n + i];
         }
+        if (p.tanh_out != nullptr) {
+          const float *a = p.tanh_out + (size_t)m * p.N + n;
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            if (n + i < p.N) v[i] *= 1.f - a[i] * a[i];
+        }
         float *dst = out + (size_t)m * p.N + n;
         if (vec && n + 16 <= p.N) {
 #pragma unroll
@@ -318,8 +325,8 @@ static int check_matrix(const void *p, int cols, const char *what) {
 
 using namespace frnnt;
 
-extern "C" int frnnt_matmul_nt(const float *a, const float *b, const float *bias, float *d, int M,
-                               int N, int K, void *stream) {
+extern "C" int frnnt_matmul_nt(const float *a, const float *b, const float *bias,
+                               const float *tanh_out, float *d, int M, int N, int K, void *stream) {
   FRNNT_REQUIRE(M >= 0 && N >= 0 && K >= 0, FRNNT_EINVAL, "negative size");
   if (M == 0 || N == 0) return FRNNT_OK;
   FRNNT_REQUIRE(K > 0, FRNNT_EINVAL, "K must be positive");
@@ -335,7 +342,7 @@ extern "C" int frnnt_matmul_nt(const float *a, const float *b, const float *bias
   FRNNT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLinSmemBytes));
   const int mt = (M + kLinTile - 1) / kLinTile, nt = (N + kLinTile - 1) / kLinTile;
   FRNNT_REQUIRE(mt <= 65535, FRNNT_EUNSUPPORTED, "M too large for the grid");
-  LinParams p{d, bias, M, N, K, ((K + kLinBK - 1) / kLinBK) * kLinBK};
+  LinParams p{d, bias, tanh_out, M, N, K, ((K + kLinBK - 1) / kLinBK) * kLinBK};
   FRNNT_KERNEL(kern<<<dim3(nt, mt, 1), kLinThreads, kLinSmemBytes, (cudaStream_t)stream>>>(ma, mb, p));
   FRNNT_CUDA(cudaGetLastError());
   return FRNNT_OK;
@@ -373,7 +380,7 @@ extern "C" int frnnt_matmul_tn(const float *a, const float *b, float *d, float *
   const int mt = (M + kLinTile - 1) / kLinTile, nt = (N + kLinTile - 1) / kLinTile;
   const int kblocks = (R + kLinBK - 1) / kLinBK;
   const int k_per_split = ((kblocks + splits - 1) / splits) * kLinBK;
-  LinParams p{splits == 1 ? d : partials, nullptr, M, N, R, k_per_split};
+  LinParams p{splits == 1 ? d : partials, nullptr, nullptr, M, N, R, k_per_split};
   cudaStream_t st = (cudaStream_t)stream;
   FRNNT_KERNEL(kern<<<dim3(nt, mt, splits), kLinThreads, kLinSmemBytes, st>>>(ma, mb, p));
   FRNNT_CUDA(cudaGetLastError());

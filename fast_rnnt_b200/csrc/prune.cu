@@ -212,6 +212,65 @@ prune_gather_backward_kernel(const real *__restrict__ g, const int64_t *__restri
   }
 }
 
+// act[b][t][k][:] = tanh(enc[b][t][:] + dec[b][ranges[b][t][k]][:]): the joiner's input
+// without materialising am_pruned / lm_pruned (one warp per output row)
+template <typename real, typename vec, int VW>
+__global__ void pruned_tanh_kernel(const real *__restrict__ enc, const real *__restrict__ dec,
+                                   const int64_t *__restrict__ ranges, real *__restrict__ act,
+                                   long long rows, int R, int TR, int S1, int D) {
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  const int dvec = D / VW;
+  for (long long row = warp0; row < rows; row += nwarps) {
+    const long long b = row / TR, bt = row / R;
+    long long s = ranges[row];
+    s = s < 0 ? 0 : (s >= S1 ? S1 - 1 : s);
+    const vec *e = reinterpret_cast<const vec *>(enc + (size_t)bt * D);
+    const vec *d = reinterpret_cast<const vec *>(dec + ((size_t)b * S1 + s) * D);
+    vec *o = reinterpret_cast<vec *>(act + (size_t)row * D);
+    for (int v = lane; v < dvec; v += 32) {
+      const vec x = e[v], y = d[v];
+      vec r;
+      const real *xe = reinterpret_cast<const real *>(&x), *ye = reinterpret_cast<const real *>(&y);
+      real *re = reinterpret_cast<real *>(&r);
+#pragma unroll
+      for (int c = 0; c < VW; ++c) re[c] = tanh(xe[c] + ye[c]);
+      o[v] = r;
+    }
+  }
+}
+
+// enc_grad[b][t][:] = sum_k gz[b][t][k][:]  (one warp per frame, k in order)
+template <typename real, typename vec, int VW>
+__global__ void sum_over_range_kernel(const real *__restrict__ gz, real *__restrict__ out,
+                                      long long frames, int R, int D) {
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  const int dvec = D / VW;
+  for (long long f = warp0; f < frames; f += nwarps) {
+    const vec *src = reinterpret_cast<const vec *>(gz + (size_t)f * R * D);
+    vec *dst = reinterpret_cast<vec *>(out + (size_t)f * D);
+    for (int v = lane; v < dvec; v += 32) {
+      real acc[VW];
+#pragma unroll
+      for (int c = 0; c < VW; ++c) acc[c] = 0;
+      for (int k = 0; k < R; ++k) {
+        const vec x = src[(size_t)k * dvec + v];
+        const real *xe = reinterpret_cast<const real *>(&x);
+#pragma unroll
+        for (int c = 0; c < VW; ++c) acc[c] += xe[c];
+      }
+      vec r;
+      real *re = reinterpret_cast<real *>(&r);
+#pragma unroll
+      for (int c = 0; c < VW; ++c) re[c] = acc[c];
+      dst[v] = r;
+    }
+  }
+}
+
 }  // namespace frnnt
 
 using namespace frnnt;
@@ -312,6 +371,65 @@ extern "C" int frnnt_prune_gather_backward(int dtype, const void *out_grad, cons
     else
       FRNNT_KERNEL(prune_gather_backward_kernel<double, double, 1><<<grid, kGbThreads, 0, st>>>(
           (const double *)out_grad, ranges, (double *)lm_grad, T * R, S1, D));
+  }
+  FRNNT_CUDA(cudaGetLastError());
+  return FRNNT_OK;
+}
+
+extern "C" int frnnt_pruned_tanh(int dtype, const void *enc, const void *dec, const int64_t *ranges,
+                                 void *act, int B, int S1, int T, int R, int D, void *stream) {
+  FRNNT_REQUIRE(check_dtype(dtype), FRNNT_EINVAL, "dtype must be FRNNT_F32 or FRNNT_F64");
+  FRNNT_REQUIRE(B >= 0 && S1 >= 1 && T >= 0 && R >= 1 && D >= 1, FRNNT_EINVAL, "bad sizes");
+  const long long rows = (long long)B * T * R;
+  if (rows == 0) return FRNNT_OK;
+  FRNNT_REQUIRE(enc && dec && ranges && act, FRNNT_EINVAL, "NULL argument");
+  cudaStream_t st = (cudaStream_t)stream;
+  long long want = (rows + 7) / 8;
+  const int grid = (int)(want < 148LL * 32 ? want : 148LL * 32);
+  const bool al = (uintptr_t)enc % 16 == 0 && (uintptr_t)dec % 16 == 0 && (uintptr_t)act % 16 == 0;
+  if (dtype == FRNNT_F32) {
+    if (al && D % 4 == 0)
+      FRNNT_KERNEL(pruned_tanh_kernel<float, float4, 4><<<grid, 256, 0, st>>>(
+          (const float *)enc, (const float *)dec, ranges, (float *)act, rows, R, T * R, S1, D));
+    else
+      FRNNT_KERNEL(pruned_tanh_kernel<float, float, 1><<<grid, 256, 0, st>>>(
+          (const float *)enc, (const float *)dec, ranges, (float *)act, rows, R, T * R, S1, D));
+  } else {
+    if (al && D % 2 == 0)
+      FRNNT_KERNEL(pruned_tanh_kernel<double, double2, 2><<<grid, 256, 0, st>>>(
+          (const double *)enc, (const double *)dec, ranges, (double *)act, rows, R, T * R, S1, D));
+    else
+      FRNNT_KERNEL(pruned_tanh_kernel<double, double, 1><<<grid, 256, 0, st>>>(
+          (const double *)enc, (const double *)dec, ranges, (double *)act, rows, R, T * R, S1, D));
+  }
+  FRNNT_CUDA(cudaGetLastError());
+  return FRNNT_OK;
+}
+
+extern "C" int frnnt_sum_over_range(int dtype, const void *gz, void *out, long long frames, int R,
+                                    int D, void *stream) {
+  FRNNT_REQUIRE(check_dtype(dtype), FRNNT_EINVAL, "dtype must be FRNNT_F32 or FRNNT_F64");
+  FRNNT_REQUIRE(frames >= 0 && R >= 1 && D >= 1, FRNNT_EINVAL, "bad sizes");
+  if (frames == 0) return FRNNT_OK;
+  FRNNT_REQUIRE(gz && out, FRNNT_EINVAL, "NULL argument");
+  cudaStream_t st = (cudaStream_t)stream;
+  long long want = (frames + 7) / 8;
+  const int grid = (int)(want < 148LL * 32 ? want : 148LL * 32);
+  const bool al = (uintptr_t)gz % 16 == 0 && (uintptr_t)out % 16 == 0;
+  if (dtype == FRNNT_F32) {
+    if (al && D % 4 == 0)
+      FRNNT_KERNEL(sum_over_range_kernel<float, float4, 4><<<grid, 256, 0, st>>>(
+          (const float *)gz, (float *)out, frames, R, D));
+    else
+      FRNNT_KERNEL(sum_over_range_kernel<float, float, 1><<<grid, 256, 0, st>>>(
+          (const float *)gz, (float *)out, frames, R, D));
+  } else {
+    if (al && D % 2 == 0)
+      FRNNT_KERNEL(sum_over_range_kernel<double, double2, 2><<<grid, 256, 0, st>>>(
+          (const double *)gz, (double *)out, frames, R, D));
+    else
+      FRNNT_KERNEL(sum_over_range_kernel<double, double, 1><<<grid, 256, 0, st>>>(
+          (const double *)gz, (double *)out, frames, R, D));
   }
   FRNNT_CUDA(cudaGetLastError());
   return FRNNT_OK;

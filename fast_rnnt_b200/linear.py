@@ -7,10 +7,20 @@ import torch
 from . import _lib
 
 
-def _matmul_nt(a, b, bias, M, N, K):
+def _matmul_nt(a, b, bias, M, N, K, tanh_out=None):
     out = torch.empty(M, N, dtype=torch.float32, device=a.device)
-    _lib.call("frnnt_matmul_nt", _lib.ptr(a), _lib.ptr(b), _lib.ptr(bias), _lib.ptr(out), M, N, K,
-              _lib.stream_ptr(a.device))
+    _lib.call("frnnt_matmul_nt", _lib.ptr(a), _lib.ptr(b), _lib.ptr(bias), _lib.ptr(tanh_out),
+              _lib.ptr(out), M, N, K, _lib.stream_ptr(a.device))
+    return out
+
+
+def _matmul_tn(a, b, M, N, R):
+    splits = _lib.lib().frnnt_matmul_tn_splits(M, N, R)
+    out = torch.empty(M, N, dtype=torch.float32, device=a.device)
+    partials = (torch.empty(splits, M, N, dtype=torch.float32, device=a.device)
+                if splits > 1 else None)
+    _lib.call("frnnt_matmul_tn", _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.ptr(partials),
+              M, N, R, _lib.stream_ptr(a.device))
     return out
 
 
@@ -40,12 +50,7 @@ class _Linear3xTF32(torch.autograd.Function):
                 wt = weight.t().contiguous()                      # [K][N]
                 gx = _matmul_nt(g2, wt, None, M, K, N).reshape(ctx.x_shape)
             if ctx.needs_input_grad[1]:
-                splits = _lib.lib().frnnt_matmul_tn_splits(N, K, M)
-                gw = torch.empty(N, K, dtype=torch.float32, device=g.device)
-                partials = (torch.empty(splits, N, K, dtype=torch.float32, device=g.device)
-                            if splits > 1 else None)
-                _lib.call("frnnt_matmul_tn", _lib.ptr(g2), _lib.ptr(x2), _lib.ptr(gw),
-                          _lib.ptr(partials), N, K, M, _lib.stream_ptr(g.device))
+                gw = _matmul_tn(g2, x2, N, K, M)
             if ctx.has_bias and ctx.needs_input_grad[2]:
                 gb = g2.sum(dim=0)
         return gx, gw, gb
@@ -57,3 +62,66 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor = None) -> 
     multiples of 4."""
     assert x.is_cuda and x.dtype == torch.float32 and weight.dtype == torch.float32
     return _Linear3xTF32.apply(x, weight, bias)
+
+
+class _PrunedJoiner(torch.autograd.Function):
+    """logits = Linear(tanh(enc[b,t] + dec[b, ranges[b,t,k]])) as one autograd node:
+    gather + add + tanh in one kernel, the three products on the tensor cores, the
+    tanh derivative in the epilogue of the grad-input product."""
+
+    @staticmethod
+    def forward(ctx, enc, dec, ranges, weight, bias):
+        B, T, D = enc.shape
+        S1 = dec.shape[1]
+        R = ranges.shape[2]
+        N = weight.shape[0]
+        enc, dec, ranges, weight = (enc.contiguous(), dec.contiguous(), ranges.contiguous(),
+                                    weight.contiguous())
+        dev = enc.device
+        with torch.cuda.device(dev):
+            act = torch.empty(B, T, R, D, dtype=torch.float32, device=dev)
+            _lib.call("frnnt_pruned_tanh", 0, _lib.ptr(enc), _lib.ptr(dec), _lib.ptr(ranges),
+                      _lib.ptr(act), B, S1, T, R, D, _lib.stream_ptr(dev))
+            out = _matmul_nt(act, weight, None if bias is None else bias.contiguous(),
+                             B * T * R, N, D)
+        ctx.save_for_backward(act, weight, ranges)
+        ctx.dims = (B, T, R, D, S1, N)
+        ctx.has_bias = bias is not None
+        return out.reshape(B, T, R, N)
+
+    @staticmethod
+    def backward(ctx, g):
+        act, weight, ranges = ctx.saved_tensors
+        B, T, R, D, S1, N = ctx.dims
+        M = B * T * R
+        dev = g.device
+        g2 = g.reshape(M, N).contiguous()
+        enc_grad = dec_grad = gw = gb = None
+        with torch.cuda.device(dev):
+            if ctx.needs_input_grad[0] or ctx.needs_input_grad[1]:
+                wt = weight.t().contiguous()
+                gz = _matmul_nt(g2, wt, None, M, D, N, tanh_out=act)   # d loss / d (enc + dec)
+                if ctx.needs_input_grad[0]:
+                    enc_grad = torch.empty(B, T, D, dtype=torch.float32, device=dev)
+                    _lib.call("frnnt_sum_over_range", 0, _lib.ptr(gz), _lib.ptr(enc_grad),
+                              _lib._c_longlong(B * T), R, D, _lib.stream_ptr(dev))
+                if ctx.needs_input_grad[1]:
+                    dec_grad = torch.empty(B, S1, D, dtype=torch.float32, device=dev)
+                    _lib.call("frnnt_prune_gather_backward", 0, _lib.ptr(gz), _lib.ptr(ranges),
+                              _lib.ptr(dec_grad), B, S1, T, R, D, _lib.stream_ptr(dev))
+            if ctx.needs_input_grad[3]:
+                gw = _matmul_tn(g2, act.reshape(M, D), N, D, M)
+            if ctx.has_bias and ctx.needs_input_grad[4]:
+                gb = g2.sum(dim=0)
+        return enc_grad, dec_grad, None, gw, gb
+
+
+def pruned_joiner(enc: torch.Tensor, dec: torch.Tensor, ranges: torch.Tensor,
+                  weight: torch.Tensor, bias: torch.Tensor = None) -> torch.Tensor:
+    """``linear(tanh(am_pruned + lm_pruned), weight, bias)`` for
+    ``am_pruned, lm_pruned = do_rnnt_pruning(enc, dec, ranges)`` -- the joiner of
+    the reference's documented usage (README.md:180-190) -- without materialising
+    the pruned tensors.  float32 CUDA tensors; enc [B][T][D], dec [B][S+1][D],
+    ranges int64 [B][T][R], weight [C][D]; returns logits [B][T][R][C]."""
+    assert enc.dtype == torch.float32 and dec.dtype == torch.float32
+    return _PrunedJoiner.apply(enc, dec, ranges, weight, bias)

@@ -215,9 +215,11 @@ int frnnt_prune_gather_backward(int dtype, const void *out_grad, const int64_t *
  * accuracy), fed by TMA.  All matrices are row-major float32 with 16-byte
  * aligned bases and row lengths that are multiples of 4.
  *
- * D[M][N] = A[M][K] * B[N][K]^T (+ bias[N] if not NULL). */
-int frnnt_matmul_nt(const float *a, const float *b, const float *bias, float *d, int M, int N,
-                    int K, void *stream);
+ * D[M][N] = A[M][K] * B[N][K]^T (+ bias[N] if not NULL); if tanh_out [M][N] is not
+ * NULL every result is multiplied by 1 - tanh_out^2 (the derivative of a tanh whose
+ * output is tanh_out: the backward of the joiner's activation, fused). */
+int frnnt_matmul_nt(const float *a, const float *b, const float *bias, const float *tanh_out,
+                    float *d, int M, int N, int K, void *stream);
 
 /* D[M][N] = A[R][M]^T * B[R][N].  The reduction over R is split over
  * frnnt_matmul_tn_splits(M, N, R) CTAs per output tile; `partials` is scratch of
@@ -225,6 +227,16 @@ int frnnt_matmul_nt(const float *a, const float *b, const float *bias, float *d,
 int frnnt_matmul_tn_splits(int M, int N, int R);
 int frnnt_matmul_tn(const float *a, const float *b, float *d, float *partials, int M, int N, int R,
                     void *stream);
+
+/* act[B][T][R][D] = tanh(enc[B][T][D] + dec[B][S1][D] gathered at ranges[B][T][R]): the
+ * joiner's input, i.e. tanh(am_pruned + lm_pruned) of the reference's usage
+ * (README.md:180-186) without materialising the two pruned tensors. */
+int frnnt_pruned_tanh(int dtype, const void *enc, const void *dec, const int64_t *ranges,
+                      void *act, int B, int S1, int T, int R, int D, void *stream);
+
+/* out[frames][D] = sum over k of gz[frames][R][D] (gradient of the stride-0 am_pruned view). */
+int frnnt_sum_over_range(int dtype, const void *gz, void *out, long long frames, int R, int D,
+                         void *stream);
 
 #ifdef __cplusplus
 }

@@ -54,3 +54,29 @@ def test_linear_rejects_unaligned_rows():
     from fast_rnnt_b200.linear import linear
     with pytest.raises(FrnntError):
         linear(torch.randn(8, 6, device="cuda"), torch.randn(4, 6, device="cuda"))
+
+
+def test_pruned_joiner_matches_the_torch_composition():
+    """pruned_joiner == linear(tanh(am_pruned + lm_pruned)) of the reference's usage,
+    values and all five gradients."""
+    import fast_rnnt_b200 as fr
+    torch.manual_seed(5)
+    B, T, S1, R, D, C = 3, 19, 9, 4, 64, 36
+    enc = torch.randn(B, T, D, device="cuda", requires_grad=True)
+    dec = torch.randn(B, S1, D, device="cuda", requires_grad=True)
+    w = (torch.randn(C, D, device="cuda") / 8).requires_grad_(True)
+    b = torch.randn(C, device="cuda", requires_grad=True)
+    start = torch.sort(torch.randint(0, S1 - R + 1, (B, T), device="cuda"), dim=1)[0]
+    ranges = start.unsqueeze(-1) + torch.arange(R, device="cuda")
+    y = fr.pruned_joiner(enc, dec, ranges, w, b)
+    g = torch.randn_like(y)
+    y.backward(g)
+    ours = [y.detach(), enc.grad, dec.grad, w.grad, b.grad]
+    e2, d2, w2, b2 = (t.detach().double().requires_grad_(True) for t in (enc, dec, w, b))
+    a_p = e2.unsqueeze(2).expand(B, T, R, D)
+    l_p = torch.gather(d2, 1, ranges.reshape(B, T * R, 1).expand(B, T * R, D)).reshape(B, T, R, D)
+    y_ref = torch.nn.functional.linear(torch.tanh(a_p + l_p), w2, b2)
+    y_ref.backward(g.double())
+    ref = [y_ref.detach(), e2.grad, d2.grad, w2.grad, b2.grad]
+    for o, r, what in zip(ours, ref, ("logits", "enc", "dec", "weight", "bias")):
+        torch.testing.assert_close(o.double(), r, rtol=1e-5, atol=2e-5, msg=lambda m: what + m)
