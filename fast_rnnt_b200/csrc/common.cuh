@@ -58,15 +58,12 @@ __device__ __forceinline__ double log_r(double x) { return log(x); }
 // finite (an operand is -inf) the larger operand is returned unchanged.
 template <typename real>
 __device__ __forceinline__ real log_add(real x, real y) {
-  real diff;
-  if (x < y) {
-    diff = x - y;
-    x = y;
-  } else {
-    diff = y - x;
-  }
-  if (diff - diff != 0) return x;
-  return x + log1p_r(exp_r(diff));
+  // same arithmetic as the reference (larger + log1p(exp(smaller - larger))), written
+  // without divergent branches: the guard is a select on the finished result
+  const real hi = x < y ? y : x;
+  const real diff = x < y ? x - y : y - x;
+  const real r = hi + log1p_r(exp_r(diff));
+  return (diff - diff != 0) ? hi : r;
 }
 
 template <typename T>

@@ -38,7 +38,10 @@ namespace frnnt {
 
 constexpr int kChunk = 32;      // anti-diagonals staged per chunk
 constexpr int kPitch = 33;      // ring row pitch in elements
-constexpr int kIoWarps = 4;     // loader / storer warps per CTA
+constexpr int kIoWarps = 4;     // loader warps per CTA of the forward sweep
+// helper warps per CTA of the backward sweep (they do the exp()): as many as the register
+// file allows next to NCW compute warps
+__host__ __device__ constexpr int bwd_io_warps(int ncw) { return ncw <= 4 ? 16 : 8; }
 constexpr int kHandRing = 64;   // hand-off slots per warp (two chunks deep)
 constexpr int kSpinLimit = 1 << 22;
 
@@ -104,7 +107,9 @@ template <> struct Hand<float> {
     q[warp * kHandRing + (step & (kHandRing - 1))] =
         ((unsigned long long)(unsigned)step << 32) | (unsigned long long)__float_as_uint(v);
   }
-  // value the neighbour published at `step`; gives up after kSpinLimit polls
+  // value the neighbour published at `step`; gives up after kSpinLimit polls.
+  // Called by ALL lanes of the consumer warp (one broadcast read, no divergence);
+  // the neighbour normally runs a step ahead, so the first read succeeds.
   __device__ static float get(volatile slot_t *q, int warp, int step, volatile int *failed) {
     volatile slot_t *slot = q + warp * kHandRing + (step & (kHandRing - 1));
     unsigned long long v = *slot;
@@ -143,7 +148,7 @@ __host__ __device__ constexpr size_t hand_bytes() {
 // -----------------------------------------------------------------------------
 // forward
 // -----------------------------------------------------------------------------
-template <typename real, int NCW, bool MODIFIED>
+template <typename real, int NCW, bool MODIFIED, bool WRITE_P>
 __global__ void __launch_bounds__((NCW + kIoWarps) * 32)
 mi_forward_kernel(const real *__restrict__ px, const real *__restrict__ py,
                   const int64_t *__restrict__ boundary, real *__restrict__ p,
@@ -166,7 +171,7 @@ mi_forward_kernel(const real *__restrict__ px, const real *__restrict__ py,
   const int nchunks = (nd + kChunk - 1) / kChunk;
   const real *X = px + (size_t)b * S * T1;
   const real *Y = py + (size_t)b * (S + 1) * T;
-  real *P = p ? p + (size_t)b * (S + 1) * (T + 1) : nullptr;
+  real *P = WRITE_P ? p + (size_t)b * (S + 1) * (T + 1) : nullptr;
   const int lpitch = lattice_pitch(S);
   const bool is_io = warp >= NCW;
   const real ninf = neg_inf<real>();
@@ -198,7 +203,11 @@ mi_forward_kernel(const real *__restrict__ px, const real *__restrict__ py,
   const int i = threadIdx.x;          // lattice row (compute threads only)
   const bool row_ok = i <= box.sb;
   const int k_first = i, k_last = i + box.tb;  // this row is active for k in [k_first, k_last]
-  real p_cur = ninf, p_old = ninf;    // this row's cells at t'-1 and t'-2
+  // this row's cells at t'-1 and t'-2.  Regular recursion: row 0 starts from 0 instead
+  // of -inf, so its first cell comes out as LogAdd(-inf, 0 + 0) = 0, the origin, without
+  // a special case in the loop (the modified recursion also reads the value of two steps
+  // back, where the fake start would leak into row 1, so it keeps the special case).
+  real p_cur = (!MODIFIED && i == 0) ? (real)0 : ninf, p_old = ninf;
   real p_last = ninf;                 // the last active value (the answer for row sb)
   real *L = lattice ? lattice + (size_t)b * lattice_elems_per_utt(S, T) + i : nullptr;
 
@@ -222,21 +231,23 @@ mi_forward_kernel(const real *__restrict__ px, const real *__restrict__ py,
           // p of the row above: one step back (regular) or two (modified)
           const real hist = MODIFIED ? p_old : p_cur;
           real up = __shfl_up_sync(0xffffffffu, hist, 1);
-          if (NCW > 1 && lane == 0 && warp > 0) {
+          if (NCW > 1 && warp > 0) {  // warp-uniform: every lane reads the neighbour's slot
             const int src = k - 1 + off;
-            up = src >= 0 ? H::get(hand, warp - 1, src, &failed) : ninf;
+            const real nb = src >= 0 ? H::get(hand, warp - 1, src, &failed) : ninf;
+            if (lane == 0) up = nb;
           }
           const bool active = row_ok && k >= k_first && k <= k_last;
           const real a = (i > 0) ? up + xv[u] : ninf;
           const real bb = p_cur + yv[u];
           real pn = log_add(a, bb);
-          if (k == 0 && i == 0) pn = 0;
+          if (MODIFIED && k == 0 && i == 0) pn = 0;
           if (!active) pn = ninf;
           if (active) {
             p_last = pn;
-            if (L != nullptr) L[(size_t)k * lpitch] = pn;
-            if (P != nullptr) P[(size_t)(box.s0 + i) * (T + 1) + box.t0 + (k - i)] = pn;
+            if (L != nullptr) *L = pn;
+            if (WRITE_P) P[(size_t)(box.s0 + i) * (T + 1) + box.t0 + (k - i)] = pn;
           }
+          if (L != nullptr) L += lpitch;
           p_old = p_cur;
           p_cur = pn;
           if (NCW > 1) {
@@ -255,12 +266,13 @@ mi_forward_kernel(const real *__restrict__ px, const real *__restrict__ py,
 // backward (from the diagonal-major lattice)
 // -----------------------------------------------------------------------------
 template <typename real, int NCW, bool MODIFIED>
-__global__ void __launch_bounds__((NCW + kIoWarps) * 32)
+__global__ void __launch_bounds__((NCW + bwd_io_warps(NCW)) * 32)
 mi_backward_kernel(const real *__restrict__ px, const real *__restrict__ lattice,
                    const int64_t *__restrict__ boundary, const real *__restrict__ ans_grad,
                    real *__restrict__ px_grad, real *__restrict__ py_grad,
                    real *__restrict__ origin_grad, int S, int T) {
   constexpr int ROWS = NCW * 32;
+  constexpr int NIO = bwd_io_warps(NCW);
   using H = Hand<real>;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   real *ringd = reinterpret_cast<real *>(smem_raw);  // [2][ROWS][kPitch]  px, then d1
@@ -296,7 +308,7 @@ mi_backward_kernel(const real *__restrict__ px, const real *__restrict__ lattice
     const int iw = warp - NCW;
     {
       const int k = c * kChunk + lane;
-      for (int i = 1 + iw; i <= box.sb; i += kIoWarps) {
+      for (int i = 1 + iw; i <= box.sb; i += NIO) {
         const int tp = k - i;
         const bool v = tp >= 1 && tp <= box.tb;
         async_copy_or_zero(&ringd[(slot * ROWS + i) * kPitch + lane],
@@ -304,14 +316,14 @@ mi_backward_kernel(const real *__restrict__ px, const real *__restrict__ lattice
       }
       async_copy_wait_all();
     }
-    bar_sync_named(2, kIoWarps * 32);
+    bar_sync_named(2, NIO * 32);
     // all lattice loads of this warp's diagonals are issued before the first exp
-    constexpr int NJ = kChunk / kIoWarps;   // diagonals per helper warp
+    constexpr int NJ = kChunk / NIO;   // diagonals per helper warp
     constexpr int NM = NCW;                 // 32-row blocks
     real up[NJ][NM], tot[NJ][NM];
 #pragma unroll
     for (int jj = 0; jj < NJ; ++jj) {
-      const int k = c * kChunk + iw + jj * kIoWarps;
+      const int k = c * kChunk + iw + jj * NIO;
 #pragma unroll
       for (int m = 0; m < NM; ++m) {
         const int i = lane + 32 * m;
@@ -321,20 +333,36 @@ mi_backward_kernel(const real *__restrict__ px, const real *__restrict__ lattice
         tot[jj][m] = v ? LT[(size_t)k * lpitch + i] : (real)0;
       }
     }
+    // weights of every cell of the chunk, special cases resolved here so that the
+    // compute warps only multiply: d1 (share of the x-predecessor) into ringd,
+    // d2 (share of the y-predecessor) into the slot of ringx they will overwrite
 #pragma unroll
     for (int jj = 0; jj < NJ; ++jj) {
-      const int j = iw + jj * kIoWarps;
+      const int j = iw + jj * NIO;
       const int k = c * kChunk + j;
 #pragma unroll
       for (int m = 0; m < NM; ++m) {
         const int i = lane + 32 * m;
+        if (i > box.sb) continue;
         const int tp = k - i;
-        if (i >= 1 && i <= box.sb && tp >= 1 && tp <= box.tb) {
-          real t = tot[jj][m];
-          if (t - t != 0) t = 0;
-          real *cell = ringd + (slot * ROWS + i) * kPitch + j;
-          *cell = exp_r(up[jj][m] + *cell - t);
+        real d1 = 0, d2 = 0;
+        if (tp >= 0 && tp <= box.tb) {
+          if (i == 0) {            // first row: only a y-predecessor
+            d2 = 1;
+          } else if (tp == 0) {    // first column: only an x-predecessor (regular) or none
+            d1 = MODIFIED ? 0 : 1;
+          } else {
+            real t = tot[jj][m];
+            if (t - t != 0) t = 0;
+            const real w = exp_r(up[jj][m] + ringd[(slot * ROWS + i) * kPitch + j] - t);
+            if (w - w == 0) {
+              d1 = w;
+              d2 = (real)1 - w;
+            }
+          }
         }
+        ringd[(slot * ROWS + i) * kPitch + j] = d1;
+        ringx[(slot * ROWS + i) * kPitch + j] = d2;
       }
     }
   };
@@ -344,7 +372,7 @@ mi_backward_kernel(const real *__restrict__ px, const real *__restrict__ lattice
     const int slot = c & 1;
     const int k = c * kChunk + lane;
 #pragma unroll 4
-    for (int i = warp - NCW; i <= box.sb; i += kIoWarps) {
+    for (int i = warp - NCW; i <= box.sb; i += NIO) {
       const int tp = k - i;
       if (tp <= box.tb) {
         if (i >= 1 && tp >= tp_min_x)
@@ -365,13 +393,13 @@ mi_backward_kernel(const real *__restrict__ px, const real *__restrict__ lattice
     // overlaps with the compute warps' first chunk
     const int lw = warp - NCW;
     const int cx_lo = box.t0, cx_hi = box.t0 + box.tb + off;  // inclusive, in-box columns of px_grad
-    for (int r = lw; r < S; r += kIoWarps) {
+    for (int r = lw; r < S; r += NIO) {
       const bool in_rows = r >= box.s0 && r < box.s0 + box.sb;
       for (int col = lane; col < T1; col += 32)
         if (!in_rows || col < cx_lo || col > cx_hi) GX[(size_t)r * T1 + col] = 0;
     }
     const int cy_lo = box.t0, cy_hi = box.t0 + box.tb - 1;
-    for (int r = lw; r <= S; r += kIoWarps) {
+    for (int r = lw; r <= S; r += NIO) {
       const bool in_rows = r >= box.s0 && r <= box.s0 + box.sb;
       for (int col = lane; col < T; col += 32)
         if (!in_rows || col < cy_lo || col > cy_hi) GY[(size_t)r * T + col] = 0;
@@ -380,12 +408,14 @@ mi_backward_kernel(const real *__restrict__ px, const real *__restrict__ lattice
 
   const int i = threadIdx.x;
   const bool row_ok = i <= box.sb;
-  const int k_first = i, k_last = i + box.tb;
   real g1_cur = 0, g1_old = 0;  // x-gradients this row sent up at the last two steps
   real g2_cur = 0;              // y-gradient this row sent left at the last step
+  real g_last = 0;              // gradient of the cell handled last (the origin for row 0)
   const real g_end = ans_grad[b];
   const int k_end = box.sb + box.tb;
-  const int k_top = nchunks * kChunk - 1;  // first diagonal the sweep visits
+  const int k_inject = i == box.sb ? k_end : -1;  // where the incoming gradient enters
+  const int k_top = nchunks * kChunk - 1;          // first diagonal the sweep visits
+  const bool has_below = NCW > 1 && warp + 1 < NCW;
 
   for (int c = nchunks - 1; c >= 0; --c) {
     if (is_io) {
@@ -397,47 +427,30 @@ mi_backward_kernel(const real *__restrict__ px, const real *__restrict__ lattice
       real *ry = ringy + ((c & 1) * ROWS + i) * kPitch;
 #pragma unroll 1
       for (int j0 = kChunk - 8; j0 >= 0; j0 -= 8) {
-        real dv[8];
+        real d1v[8], d2v[8];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) dv[u] = rd[j0 + u];
+        for (int u = 0; u < 8; ++u) {
+          d1v[u] = row_ok ? rd[j0 + u] : (real)0;
+          d2v[u] = row_ok ? rx[j0 + u] : (real)0;
+        }
 #pragma unroll
         for (int u = 7; u >= 0; --u) {
           const int k = c * kChunk + j0 + u;
           const real hist = MODIFIED ? g1_old : g1_cur;
           real below = __shfl_down_sync(0xffffffffu, hist, 1);
-          if (lane == 31) {
+          if (has_below) {  // warp-uniform: every lane reads the neighbour's slot
             const int src = k + 1 - off;
-            below = (NCW > 1 && warp + 1 < NCW && src <= k_top)
-                        ? H::get(hand, warp + 1, src, &failed)
-                        : (real)0;
+            const real nb = src <= k_top ? H::get(hand, warp + 1, src, &failed) : (real)0;
+            if (lane == 31) below = nb;
+          } else if (lane == 31) {
+            below = 0;
           }
-          const bool active = row_ok && k >= k_first && k <= k_last;
           real g = below + g2_cur;
-          if (i == box.sb && k == k_end) g = g_end;
-          real d1, d2;
-          if (i == 0) {  // first row: only a y-predecessor
-            d1 = 0;
-            d2 = 1;
-          } else if (k == k_first) {  // first column: only an x-predecessor (regular) or none
-            d1 = MODIFIED ? 0 : 1;
-            d2 = 0;
-          } else {
-            d1 = dv[u];
-            if (d1 - d1 == 0) {
-              d2 = (real)1 - d1;
-            } else {
-              d1 = 0;
-              d2 = 0;
-            }
-          }
-          real g1 = d1 * g, g2 = d2 * g;
-          if (!active) {
-            g1 = 0;
-            g2 = 0;
-          }
-          if (i == 0 && k == 0 && origin_grad != nullptr) origin_grad[b] = g;
+          if (k == k_inject) g = g_end;
+          const real g1 = d1v[u] * g, g2 = d2v[u] * g;
           rx[j0 + u] = g1;
           ry[j0 + u] = g2;
+          g_last = g;
           g1_old = g1_cur;
           g1_cur = g1;
           g2_cur = g2;
@@ -450,6 +463,7 @@ mi_backward_kernel(const real *__restrict__ px, const real *__restrict__ lattice
     }
     __syncthreads();
   }
+  if (!is_io && i == 0 && origin_grad != nullptr) origin_grad[b] = g_last;
   if (is_io && nchunks > 0) drain_chunk(0);
   if (failed && threadIdx.x == 0 && origin_grad != nullptr) origin_grad[b] = (real)NAN;
 }
@@ -480,10 +494,10 @@ static size_t mi_smem_bytes(int rings) {
   return (size_t)rings * 2 * NCW * 32 * kPitch * sizeof(real) + hand_bytes<real, NCW>();
 }
 
-template <typename real, int NCW, bool MODIFIED>
-static int launch_forward(const void *px, const void *py, const int64_t *boundary, void *p,
-                          void *ans, void *lattice, int B, int S, int T, cudaStream_t st) {
-  auto kern = mi_forward_kernel<real, NCW, MODIFIED>;
+template <typename real, int NCW, bool MODIFIED, bool WRITE_P>
+static int launch_forward_p(const void *px, const void *py, const int64_t *boundary, void *p,
+                            void *ans, void *lattice, int B, int S, int T, cudaStream_t st) {
+  auto kern = mi_forward_kernel<real, NCW, MODIFIED, WRITE_P>;
   const size_t smem = mi_smem_bytes<real, NCW>(2);
   FRNNT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   FRNNT_KERNEL(kern<<<B, (NCW + kIoWarps) * 32, smem, st>>>((const real *)px, (const real *)py,
@@ -494,13 +508,21 @@ static int launch_forward(const void *px, const void *py, const int64_t *boundar
 }
 
 template <typename real, int NCW, bool MODIFIED>
+static int launch_forward(const void *px, const void *py, const int64_t *boundary, void *p,
+                          void *ans, void *lattice, int B, int S, int T, cudaStream_t st) {
+  if (p != nullptr)
+    return launch_forward_p<real, NCW, MODIFIED, true>(px, py, boundary, p, ans, lattice, B, S, T, st);
+  return launch_forward_p<real, NCW, MODIFIED, false>(px, py, boundary, p, ans, lattice, B, S, T, st);
+}
+
+template <typename real, int NCW, bool MODIFIED>
 static int launch_backward(const void *px, const void *lattice, const int64_t *boundary,
                            const void *ans_grad, void *px_grad, void *py_grad, void *origin_grad,
                            int B, int S, int T, cudaStream_t st) {
   auto kern = mi_backward_kernel<real, NCW, MODIFIED>;
   const size_t smem = mi_smem_bytes<real, NCW>(3);
   FRNNT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  FRNNT_KERNEL(kern<<<B, (NCW + kIoWarps) * 32, smem, st>>>(
+  FRNNT_KERNEL(kern<<<B, (NCW + bwd_io_warps(NCW)) * 32, smem, st>>>(
       (const real *)px, (const real *)lattice, boundary, (const real *)ans_grad, (real *)px_grad,
       (real *)py_grad, (real *)origin_grad, S, T));
   FRNNT_CUDA(cudaGetLastError());

@@ -323,3 +323,53 @@ def test_c4_unpruned_against_reference_summary():
     flat = logits.grad.reshape(-1)
     assert_close(flat[:: max(1, flat.numel() // 4096)], g["logits_grad_sample"], 0, GRAD_ATOL,
                  "logits grad")
+
+
+def test_c5_shape_stagewise_vs_oracle():
+    """BASELINE config 5's shape (T=400, S=60, C=5000, s_range=5) on a batch of 2:
+    large-vocabulary rows take the multi-warp log-softmax path.  Stage-wise
+    against the CPU oracle with the oracle's occupancies, ranges and logits
+    injected; gradients that reach 1e2 in magnitude are compared relatively."""
+    wl = workloads.pipeline_workload("c5", batch=2, seed=2)
+    f = fr()
+    sym, bnd = wl["symbols"], wl["boundary"]
+    ls, as_ = wl["lm_only_scale"], wl["am_only_scale"]
+    am = wl["am"].clone().requires_grad_(True)
+    lm = wl["lm"].clone().requires_grad_(True)
+    ref_simple, (ox, oy) = orc.loss_smoothed(lm, am, sym, 0, ls, as_, bnd, reduction="sum",
+                                             return_grad=True)
+    ox, oy = ox.clone(), oy.clone()
+    ref_simple.backward()
+    cam = wl["am"].cuda().requires_grad_(True)
+    clm = wl["lm"].cuda().requires_grad_(True)
+    simple, (gx, gy) = f.rnnt_loss_smoothed(lm=clm, am=cam, symbols=sym.cuda(),
+                                            termination_symbol=0, lm_only_scale=ls,
+                                            am_only_scale=as_, boundary=bnd.cuda(),
+                                            reduction="sum", return_grad=True)
+    assert_close(simple, ref_simple.detach(), LOSS_RTOL, 0, "simple loss")
+    assert_close(gx, ox, 0, GRAD_ATOL, "occ_x")
+    assert_close(gy, oy, 0, GRAD_ATOL, "occ_y")
+    simple.backward()
+    assert_close(cam.grad, am.grad, 1e-4, GRAD_ATOL, "am grad")
+    assert_close(clm.grad, lm.grad, 1e-4, GRAD_ATOL, "lm grad")
+    # ranges on the oracle's occupancies: bit-exact
+    ranges = orc.prune_ranges(ox, oy, bnd, wl["s_range"])
+    r = f.get_rnnt_prune_ranges(px_grad=ox.cuda(), py_grad=oy.cuda(), boundary=bnd.cuda(),
+                                s_range=wl["s_range"])
+    assert torch.equal(r.cpu(), ranges)
+    # pruned stage on the oracle's ranges and logits
+    torch.manual_seed(9)
+    logits = torch.randn(2, 400, 5, 5000).requires_grad_(True)
+    ref_pruned = orc.loss_pruned(logits, sym, ranges, 0, bnd, reduction="sum")
+    ref_pruned.backward()
+    cl = logits.detach().cuda().requires_grad_(True)
+    ppx, ppy = f.get_rnnt_logprobs_pruned(logits=cl.detach(), symbols=sym.cuda(), ranges=r,
+                                          termination_symbol=0, boundary=bnd.cuda())
+    rpx, rpy = orc.pruned_logprobs(logits.detach(), sym, ranges, 0, bnd)
+    assert_close(ppx, rpx, 0, LATTICE_ATOL, "pruned px")
+    assert_close(ppy, rpy, 0, LATTICE_ATOL, "pruned py")
+    pruned = f.rnnt_loss_pruned(logits=cl, symbols=sym.cuda(), ranges=r, termination_symbol=0,
+                                boundary=bnd.cuda(), reduction="sum")
+    assert_close(pruned, ref_pruned.detach(), LOSS_RTOL, 0, "pruned loss")
+    pruned.backward()
+    assert_close(cl.grad, logits.grad, 0, GRAD_ATOL, "logits grad")
