@@ -210,13 +210,18 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       }
       float4 *raw = reinterpret_cast<float4 *>(tiles_ptr + (size_t)s * kLinStageBytes);
       float4 *lo = raw + (2 * kLinOpBytes) / 16;
-#pragma unroll 4
-      for (int c = st_tid; c < (int)(2 * kLinOpBytes / 16); c += 32 * kLinWorkers) {
-        const float4 x = raw[c];
-        float4 h, l;
-        split_tf32(x, h, l);
-        raw[c] = h;
-        lo[c] = l;
+      {
+        constexpr int kChunksPerThread = (int)(2 * kLinOpBytes / 16) / (32 * kLinWorkers);
+        float4 x[kChunksPerThread];
+#pragma unroll
+        for (int q = 0; q < kChunksPerThread; ++q) x[q] = raw[st_tid + q * 32 * kLinWorkers];
+#pragma unroll
+        for (int q = 0; q < kChunksPerThread; ++q) {
+          float4 h, l;
+          split_tf32(x[q], h, l);
+          raw[st_tid + q * 32 * kLinWorkers] = h;
+          lo[st_tid + q * 32 * kLinWorkers] = l;
+        }
       }
       fence_async_smem();
       __syncwarp();

@@ -156,13 +156,13 @@ __device__ __forceinline__ void mma_commit(uint64_t *bar) {
 }
 
 // ---- 3xTF32 split ---------------------------------------------------------------------------------
-// x ~= hi + lo, both rounded to nearest tf32 (cvt.rna; low 13 mantissa bits
+// x ~= hi + lo, both rounded to nearest tf32 (low 13 mantissa bits
 // zero, so the tensor core's own conversion changes nothing); hi*hi + hi*lo +
 // lo*hi then carries ~2^-22 relative error per product, unbiased.
 __device__ __forceinline__ float round_tf32(float x) {
-  uint32_t r;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-  return __uint_as_float(r);
+  // round to nearest, ties away from zero, on the 13 dropped mantissa bits -- what
+  // cvt.rna.tf32.f32 does -- with two full-rate integer instructions
+  return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
 }
 __device__ __forceinline__ void split_tf32(float x, float &hi, float &lo) {
   hi = round_tf32(x);
