@@ -66,8 +66,12 @@ __device__ __forceinline__ MiBox load_box(const int64_t *boundary, int b, int S,
 
 // lattice scratch: p by anti-diagonal, [B][S+T+1][pitch]
 __host__ __device__ inline int lattice_pitch(int S) { return (S + 1 + 31) & ~31; }
+// followed, per utterance, by two vectors of edge_elems() values: when the lattice has
+// more rows than one CTA holds it is swept in row blocks (one launch per block), and
+// the backward sweep passes the x-gradients that cross a block edge through them
+__host__ __device__ inline size_t edge_elems(int S, int T) { return (size_t)(S + T + 1 + 2 * kChunk); }
 __host__ __device__ inline size_t lattice_elems_per_utt(int S, int T) {
-  return (size_t)(S + T + 1) * lattice_pitch(S);
+  return (size_t)(S + T + 1) * lattice_pitch(S) + 2 * edge_elems(S, T);
 }
 
 __device__ __forceinline__ void bar_sync_named(int id, int nthreads) {
@@ -148,26 +152,33 @@ __host__ __device__ constexpr size_t hand_bytes() {
 // -----------------------------------------------------------------------------
 // forward
 // -----------------------------------------------------------------------------
-template <typename real, int NCW, bool MODIFIED, bool WRITE_P>
+// BLOCKED: the launch covers lattice rows [row0, row0 + ROWS) only; the row above the
+// block is read back from the lattice scratch, where the previous launch left it.
+template <typename real, int NCW, bool MODIFIED, bool WRITE_P, bool BLOCKED>
 __global__ void __launch_bounds__((NCW + kIoWarps) * 32)
 mi_forward_kernel(const real *__restrict__ px, const real *__restrict__ py,
                   const int64_t *__restrict__ boundary, real *__restrict__ p,
-                  real *__restrict__ ans, real *__restrict__ lattice, int S, int T) {
+                  real *__restrict__ ans, real *__restrict__ lattice, int S, int T, int row0_arg) {
   constexpr int ROWS = NCW * 32;
   using H = Hand<real>;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   real *ringx = reinterpret_cast<real *>(smem_raw);  // [2][ROWS][kPitch]
   real *ringy = ringx + 2 * ROWS * kPitch;           // [2][ROWS][kPitch]
+  real *ringu = ringy + 2 * ROWS * kPitch;           // [2][kPitch]  p of the row above the block
   volatile typename H::slot_t *hand =
-      reinterpret_cast<volatile typename H::slot_t *>(ringy + 2 * ROWS * kPitch);
+      reinterpret_cast<volatile typename H::slot_t *>(ringu + 2 * kPitch);
   __shared__ int failed;
+  const int row0 = BLOCKED ? row0_arg : 0;
 
   const int b = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int T1 = MODIFIED ? T : T + 1;
   constexpr int off = MODIFIED ? -1 : 0;
   const MiBox box = load_box(boundary, b, S, T);
-  const int nd = box.sb + box.tb + 1;  // anti-diagonals of this utterance
+  // rows of this launch: local row i <-> lattice row row0 + i, i <= ib; local diagonal
+  // k = i + t', lattice diagonal row0 + k
+  const int ib = min(ROWS - 1, box.sb - row0);
+  const int nd = ib >= 0 ? ib + box.tb + 1 : 0;  // anti-diagonals of this launch
   const int nchunks = (nd + kChunk - 1) / kChunk;
   const real *X = px + (size_t)b * S * T1;
   const real *Y = py + (size_t)b * (S + 1) * T;
@@ -184,15 +195,22 @@ mi_forward_kernel(const real *__restrict__ px, const real *__restrict__ py,
   auto load_chunk = [&](int c) {
     const int slot = c & 1;
     const int k = c * kChunk + lane;
-    for (int i = warp - NCW; i <= box.sb; i += kIoWarps) {
+    for (int i = warp - NCW; i <= ib; i += kIoWarps) {
       const int tp = k - i;
       const bool in_box = tp >= 0 && tp <= box.tb;
-      const bool vx = in_box && i >= 1 && tp + off >= 0;
+      const bool vx = in_box && row0 + i >= 1 && tp + off >= 0;
       const bool vy = in_box && tp >= 1;
       async_copy_or_zero(&ringx[(slot * ROWS + i) * kPitch + lane],
-                         vx ? X + (size_t)(box.s0 + i - 1) * T1 + (box.t0 + tp + off) : X, vx);
+                         vx ? X + (size_t)(box.s0 + row0 + i - 1) * T1 + (box.t0 + tp + off) : X, vx);
       async_copy_or_zero(&ringy[(slot * ROWS + i) * kPitch + lane],
-                         vy ? Y + (size_t)(box.s0 + i) * T + box.t0 + tp - 1 : Y, vy);
+                         vy ? Y + (size_t)(box.s0 + row0 + i) * T + box.t0 + tp - 1 : Y, vy);
+    }
+    if (BLOCKED && row0 > 0 && warp == NCW) {
+      // cell (row0 - 1, k + o) of the block above, as the previous launch stored it
+      const real *LB = lattice + (size_t)b * lattice_elems_per_utt(S, T);
+      const bool v = k + off >= 0 && k + off <= box.tb;
+      async_copy_or_zero(&ringu[slot * kPitch + lane],
+                         v ? LB + (size_t)(row0 + k - 1 + off) * lpitch + row0 - 1 : LB, v);
     }
     async_copy_wait_all();
   };
@@ -200,16 +218,19 @@ mi_forward_kernel(const real *__restrict__ px, const real *__restrict__ py,
   if (is_io) load_chunk(0);
   __syncthreads();
 
-  const int i = threadIdx.x;          // lattice row (compute threads only)
-  const bool row_ok = i <= box.sb;
+  const int i = threadIdx.x;          // local lattice row (compute threads only)
+  const bool row_ok = i <= ib;
+  const bool top_row = row0 + i == 0;
   const int k_first = i, k_last = i + box.tb;  // this row is active for k in [k_first, k_last]
   // this row's cells at t'-1 and t'-2.  Regular recursion: row 0 starts from 0 instead
   // of -inf, so its first cell comes out as LogAdd(-inf, 0 + 0) = 0, the origin, without
   // a special case in the loop (the modified recursion also reads the value of two steps
   // back, where the fake start would leak into row 1, so it keeps the special case).
-  real p_cur = (!MODIFIED && i == 0) ? (real)0 : ninf, p_old = ninf;
+  real p_cur = (!MODIFIED && top_row) ? (real)0 : ninf, p_old = ninf;
   real p_last = ninf;                 // the last active value (the answer for row sb)
-  real *L = lattice ? lattice + (size_t)b * lattice_elems_per_utt(S, T) + i : nullptr;
+  real *L = lattice ? lattice + (size_t)b * lattice_elems_per_utt(S, T) + (size_t)row0 * lpitch +
+                          row0 + i
+                    : nullptr;
 
   for (int c = 0; c < nchunks; ++c) {
     if (is_io) {
@@ -217,6 +238,7 @@ mi_forward_kernel(const real *__restrict__ px, const real *__restrict__ py,
     } else {
       const real *rx = ringx + ((c & 1) * ROWS + i) * kPitch;
       const real *ry = ringy + ((c & 1) * ROWS + i) * kPitch;
+      const real *ru = ringu + (c & 1) * kPitch;
 #pragma unroll 1
       for (int j0 = 0; j0 < kChunk; j0 += 8) {
         real xv[8], yv[8];
@@ -236,16 +258,17 @@ mi_forward_kernel(const real *__restrict__ px, const real *__restrict__ py,
             const real nb = src >= 0 ? H::get(hand, warp - 1, src, &failed) : ninf;
             if (lane == 0) up = nb;
           }
+          if (BLOCKED && row0 > 0 && i == 0) up = k + off >= 0 ? ru[j0 + u] : ninf;
           const bool active = row_ok && k >= k_first && k <= k_last;
-          const real a = (i > 0) ? up + xv[u] : ninf;
+          const real a = top_row ? ninf : up + xv[u];
           const real bb = p_cur + yv[u];
           real pn = log_add(a, bb);
-          if (MODIFIED && k == 0 && i == 0) pn = 0;
+          if (MODIFIED && k == 0 && top_row) pn = 0;
           if (!active) pn = ninf;
           if (active) {
             p_last = pn;
             if (L != nullptr) *L = pn;
-            if (WRITE_P) P[(size_t)(box.s0 + i) * (T + 1) + box.t0 + (k - i)] = pn;
+            if (WRITE_P) P[(size_t)(box.s0 + row0 + i) * (T + 1) + box.t0 + (k - i)] = pn;
           }
           if (L != nullptr) L += lpitch;
           p_old = p_cur;
@@ -259,18 +282,22 @@ mi_forward_kernel(const real *__restrict__ px, const real *__restrict__ py,
     }
     __syncthreads();
   }
-  if (!is_io && i == box.sb) ans[b] = failed ? (real)NAN : p_last;
+  if (!is_io && row0 + i == box.sb) ans[b] = failed ? (real)NAN : p_last;
 }
 
 // -----------------------------------------------------------------------------
 // backward (from the diagonal-major lattice)
 // -----------------------------------------------------------------------------
-template <typename real, int NCW, bool MODIFIED>
+// BLOCKED: the launch covers lattice rows [row0, row0 + ROWS) only, blocks run from the
+// last to the first.  The x-gradients that the first row of a block sends to the row
+// above are left, by lattice diagonal, in one of the two edge vectors behind the
+// lattice (alternating from block to block); the next launch stages them for its last row.
+template <typename real, int NCW, bool MODIFIED, bool BLOCKED>
 __global__ void __launch_bounds__((NCW + bwd_io_warps(NCW)) * 32)
-mi_backward_kernel(const real *__restrict__ px, const real *__restrict__ lattice,
+mi_backward_kernel(const real *__restrict__ px, real *__restrict__ lattice,
                    const int64_t *__restrict__ boundary, const real *__restrict__ ans_grad,
                    real *__restrict__ px_grad, real *__restrict__ py_grad,
-                   real *__restrict__ origin_grad, int S, int T) {
+                   real *__restrict__ origin_grad, int S, int T, int row0_arg) {
   constexpr int ROWS = NCW * 32;
   constexpr int NIO = bwd_io_warps(NCW);
   using H = Hand<real>;
@@ -278,9 +305,11 @@ mi_backward_kernel(const real *__restrict__ px, const real *__restrict__ lattice
   real *ringd = reinterpret_cast<real *>(smem_raw);  // [2][ROWS][kPitch]  px, then d1
   real *ringx = ringd + 2 * ROWS * kPitch;           // [2][ROWS][kPitch]  d/dpx
   real *ringy = ringx + 2 * ROWS * kPitch;           // [2][ROWS][kPitch]  d/dpy
+  real *ringb = ringy + 2 * ROWS * kPitch;           // [2][kPitch]  x-gradients from the block below
   volatile typename H::slot_t *hand =
-      reinterpret_cast<volatile typename H::slot_t *>(ringy + 2 * ROWS * kPitch);
+      reinterpret_cast<volatile typename H::slot_t *>(ringb + 2 * kPitch);
   __shared__ int failed;
+  const int row0 = BLOCKED ? row0_arg : 0;
 
   const int b = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -288,13 +317,20 @@ mi_backward_kernel(const real *__restrict__ px, const real *__restrict__ lattice
   constexpr int off = MODIFIED ? -1 : 0;
   constexpr int tp_min_x = MODIFIED ? 1 : 0;  // first t' whose cell has an x-predecessor
   const MiBox box = load_box(boundary, b, S, T);
-  const int nd = box.sb + box.tb + 1;
+  const int ib = min(ROWS - 1, box.sb - row0);  // last local row of this launch
+  const int nd = ib >= 0 ? ib + box.tb + 1 : 0;
   const int nchunks = (nd + kChunk - 1) / kChunk;
   const real *X = px + (size_t)b * S * T1;
   real *GX = px_grad + (size_t)b * S * T1;
   real *GY = py_grad + (size_t)b * (S + 1) * T;
   const int lpitch = lattice_pitch(S);
   const real *LT = lattice + (size_t)b * lattice_elems_per_utt(S, T);
+  // edge vectors, indexed by lattice diagonal: this block writes one, reads the other
+  real *edge = lattice + (size_t)b * lattice_elems_per_utt(S, T) + (size_t)(S + T + 1) * lpitch;
+  const int blk = row0 / ROWS;
+  real *edge_out = edge + (size_t)(blk & 1) * edge_elems(S, T);
+  const real *edge_in = edge + (size_t)((blk + 1) & 1) * edge_elems(S, T);
+  const bool block_below = BLOCKED && row0 + ROWS <= box.sb;
   const bool is_io = warp >= NCW;
 
   H::init(hand, NCW * H::kSlotsPerWarp, (real)0);
@@ -308,11 +344,18 @@ mi_backward_kernel(const real *__restrict__ px, const real *__restrict__ lattice
     const int iw = warp - NCW;
     {
       const int k = c * kChunk + lane;
-      for (int i = 1 + iw; i <= box.sb; i += NIO) {
+      for (int i = iw; i <= ib; i += NIO) {
         const int tp = k - i;
-        const bool v = tp >= 1 && tp <= box.tb;
+        const bool v = row0 + i >= 1 && tp >= 1 && tp <= box.tb;
         async_copy_or_zero(&ringd[(slot * ROWS + i) * kPitch + lane],
-                           v ? X + (size_t)(box.s0 + i - 1) * T1 + (box.t0 + tp + off) : X, v);
+                           v ? X + (size_t)(box.s0 + row0 + i - 1) * T1 + (box.t0 + tp + off) : X, v);
+      }
+      if (BLOCKED && iw == 0) {
+        // what cell (row0 + ROWS, t' - o) of the block below sent up to the last row's
+        // cell (row0 + ROWS - 1, t'), t' = k - (ROWS - 1)
+        const int ts = k - (ROWS - 1) - off;
+        const bool v = block_below && ts >= 0 && ts <= box.tb;
+        async_copy_or_zero(&ringb[slot * kPitch + lane], v ? edge_in + (row0 + k + 1 - off) : edge_in, v);
       }
       async_copy_wait_all();
     }
@@ -328,9 +371,9 @@ mi_backward_kernel(const real *__restrict__ px, const real *__restrict__ lattice
       for (int m = 0; m < NM; ++m) {
         const int i = lane + 32 * m;
         const int tp = k - i;
-        const bool v = i >= 1 && i <= box.sb && tp >= 1 && tp <= box.tb;
-        up[jj][m] = v ? LT[(size_t)(k - 1 + off) * lpitch + i - 1] : (real)0;
-        tot[jj][m] = v ? LT[(size_t)k * lpitch + i] : (real)0;
+        const bool v = row0 + i >= 1 && i <= ib && tp >= 1 && tp <= box.tb;
+        up[jj][m] = v ? LT[(size_t)(row0 + k - 1 + off) * lpitch + row0 + i - 1] : (real)0;
+        tot[jj][m] = v ? LT[(size_t)(row0 + k) * lpitch + row0 + i] : (real)0;
       }
     }
     // weights of every cell of the chunk, special cases resolved here so that the
@@ -343,11 +386,11 @@ mi_backward_kernel(const real *__restrict__ px, const real *__restrict__ lattice
 #pragma unroll
       for (int m = 0; m < NM; ++m) {
         const int i = lane + 32 * m;
-        if (i > box.sb) continue;
+        if (i > ib) continue;
         const int tp = k - i;
         real d1 = 0, d2 = 0;
         if (tp >= 0 && tp <= box.tb) {
-          if (i == 0) {            // first row: only a y-predecessor
+          if (row0 + i == 0) {     // first row: only a y-predecessor
             d2 = 1;
           } else if (tp == 0) {    // first column: only an x-predecessor (regular) or none
             d1 = MODIFIED ? 0 : 1;
@@ -372,14 +415,14 @@ mi_backward_kernel(const real *__restrict__ px, const real *__restrict__ lattice
     const int slot = c & 1;
     const int k = c * kChunk + lane;
 #pragma unroll 4
-    for (int i = warp - NCW; i <= box.sb; i += NIO) {
+    for (int i = warp - NCW; i <= ib; i += NIO) {
       const int tp = k - i;
       if (tp <= box.tb) {
-        if (i >= 1 && tp >= tp_min_x)
-          GX[(size_t)(box.s0 + i - 1) * T1 + (box.t0 + tp + off)] =
+        if (row0 + i >= 1 && tp >= tp_min_x)
+          GX[(size_t)(box.s0 + row0 + i - 1) * T1 + (box.t0 + tp + off)] =
               ringx[(slot * ROWS + i) * kPitch + lane];
         if (tp >= 1)
-          GY[(size_t)(box.s0 + i) * T + box.t0 + tp - 1] =
+          GY[(size_t)(box.s0 + row0 + i) * T + box.t0 + tp - 1] =
               ringy[(slot * ROWS + i) * kPitch + lane];
       }
     }
@@ -388,7 +431,7 @@ mi_backward_kernel(const real *__restrict__ px, const real *__restrict__ lattice
   if (is_io && nchunks > 0) weights_chunk(nchunks - 1);
   __syncthreads();
 
-  if (is_io) {
+  if (is_io && row0 == 0) {
     // exact zeros outside the boundary box (mutual_information_cpu.cu:161-166);
     // overlaps with the compute warps' first chunk
     const int lw = warp - NCW;
@@ -407,13 +450,13 @@ mi_backward_kernel(const real *__restrict__ px, const real *__restrict__ lattice
   }
 
   const int i = threadIdx.x;
-  const bool row_ok = i <= box.sb;
+  const bool row_ok = i <= ib;
   real g1_cur = 0, g1_old = 0;  // x-gradients this row sent up at the last two steps
   real g2_cur = 0;              // y-gradient this row sent left at the last step
   real g_last = 0;              // gradient of the cell handled last (the origin for row 0)
   const real g_end = ans_grad[b];
-  const int k_end = box.sb + box.tb;
-  const int k_inject = i == box.sb ? k_end : -1;  // where the incoming gradient enters
+  // local diagonal where the incoming gradient enters (cell (sb, tb))
+  const int k_inject = row0 + i == box.sb ? i + box.tb : -1;
   const int k_top = nchunks * kChunk - 1;          // first diagonal the sweep visits
   const bool has_below = NCW > 1 && warp + 1 < NCW;
 
@@ -425,6 +468,7 @@ mi_backward_kernel(const real *__restrict__ px, const real *__restrict__ lattice
       const real *rd = ringd + ((c & 1) * ROWS + i) * kPitch;
       real *rx = ringx + ((c & 1) * ROWS + i) * kPitch;
       real *ry = ringy + ((c & 1) * ROWS + i) * kPitch;
+      const real *rb = ringb + (c & 1) * kPitch;
 #pragma unroll 1
       for (int j0 = kChunk - 8; j0 >= 0; j0 -= 8) {
         real d1v[8], d2v[8];
@@ -443,7 +487,7 @@ mi_backward_kernel(const real *__restrict__ px, const real *__restrict__ lattice
             const real nb = src <= k_top ? H::get(hand, warp + 1, src, &failed) : (real)0;
             if (lane == 31) below = nb;
           } else if (lane == 31) {
-            below = 0;
+            below = BLOCKED ? rb[j0 + u] : (real)0;
           }
           real g = below + g2_cur;
           if (k == k_inject) g = g_end;
@@ -454,6 +498,7 @@ mi_backward_kernel(const real *__restrict__ px, const real *__restrict__ lattice
           g1_old = g1_cur;
           g1_cur = g1;
           g2_cur = g2;
+          if (BLOCKED && row0 > 0 && i == 0 && k < nd) edge_out[row0 + k] = g1;
           if (NCW > 1) {
             if (lane == 0 && warp > 0) H::put(hand, warp, k, g1);
             if (H::kBarrier) bar_sync_named(1, NCW * 32);
@@ -463,7 +508,7 @@ mi_backward_kernel(const real *__restrict__ px, const real *__restrict__ lattice
     }
     __syncthreads();
   }
-  if (!is_io && i == 0 && origin_grad != nullptr) origin_grad[b] = g_last;
+  if (!is_io && row0 + i == 0 && origin_grad != nullptr) origin_grad[b] = g_last;
   if (is_io && nchunks > 0) drain_chunk(0);
   if (failed && threadIdx.x == 0 && origin_grad != nullptr) origin_grad[b] = (real)NAN;
 }
@@ -491,18 +536,23 @@ __global__ void mi_lattice_from_p_kernel(const real *__restrict__ p,
 // -----------------------------------------------------------------------------
 template <typename real, int NCW>
 static size_t mi_smem_bytes(int rings) {
-  return (size_t)rings * 2 * NCW * 32 * kPitch * sizeof(real) + hand_bytes<real, NCW>();
+  return (size_t)(rings * 2 * NCW * 32 + 2) * kPitch * sizeof(real) + hand_bytes<real, NCW>();
 }
 
-template <typename real, int NCW, bool MODIFIED, bool WRITE_P>
+// lattice rows one CTA holds: 8 warps of float rows, 4 of double (the three rings of
+// the backward sweep fill shared memory beyond that)
+static int mi_rows_per_block(int dtype) { return (dtype == FRNNT_F64 ? 4 : 8) * 32; }
+
+template <typename real, int NCW, bool MODIFIED, bool WRITE_P, bool BLOCKED>
 static int launch_forward_p(const void *px, const void *py, const int64_t *boundary, void *p,
-                            void *ans, void *lattice, int B, int S, int T, cudaStream_t st) {
-  auto kern = mi_forward_kernel<real, NCW, MODIFIED, WRITE_P>;
+                            void *ans, void *lattice, int B, int S, int T, int row0,
+                            cudaStream_t st) {
+  auto kern = mi_forward_kernel<real, NCW, MODIFIED, WRITE_P, BLOCKED>;
   const size_t smem = mi_smem_bytes<real, NCW>(2);
   FRNNT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   FRNNT_KERNEL(kern<<<B, (NCW + kIoWarps) * 32, smem, st>>>((const real *)px, (const real *)py,
                                                             boundary, (real *)p, (real *)ans,
-                                                            (real *)lattice, S, T));
+                                                            (real *)lattice, S, T, row0));
   FRNNT_CUDA(cudaGetLastError());
   return FRNNT_OK;
 }
@@ -511,21 +561,62 @@ template <typename real, int NCW, bool MODIFIED>
 static int launch_forward(const void *px, const void *py, const int64_t *boundary, void *p,
                           void *ans, void *lattice, int B, int S, int T, cudaStream_t st) {
   if (p != nullptr)
-    return launch_forward_p<real, NCW, MODIFIED, true>(px, py, boundary, p, ans, lattice, B, S, T, st);
-  return launch_forward_p<real, NCW, MODIFIED, false>(px, py, boundary, p, ans, lattice, B, S, T, st);
+    return launch_forward_p<real, NCW, MODIFIED, true, false>(px, py, boundary, p, ans, lattice, B,
+                                                              S, T, 0, st);
+  return launch_forward_p<real, NCW, MODIFIED, false, false>(px, py, boundary, p, ans, lattice, B,
+                                                             S, T, 0, st);
 }
 
-template <typename real, int NCW, bool MODIFIED>
-static int launch_backward(const void *px, const void *lattice, const int64_t *boundary,
-                           const void *ans_grad, void *px_grad, void *py_grad, void *origin_grad,
-                           int B, int S, int T, cudaStream_t st) {
-  auto kern = mi_backward_kernel<real, NCW, MODIFIED>;
+// more rows than one CTA holds: one launch per block of rows, top to bottom
+template <typename real, bool MODIFIED>
+static int launch_forward_blocked(const void *px, const void *py, const int64_t *boundary, void *p,
+                                  void *ans, void *lattice, int B, int S, int T, cudaStream_t st) {
+  constexpr int NCW = sizeof(real) == 8 ? 4 : 8;
+  for (int row0 = 0; row0 <= S; row0 += NCW * 32) {
+    const int rc = p != nullptr
+                       ? launch_forward_p<real, NCW, MODIFIED, true, true>(
+                             px, py, boundary, p, ans, lattice, B, S, T, row0, st)
+                       : launch_forward_p<real, NCW, MODIFIED, false, true>(
+                             px, py, boundary, p, ans, lattice, B, S, T, row0, st);
+    if (rc != FRNNT_OK) return rc;
+  }
+  return FRNNT_OK;
+}
+
+template <typename real, int NCW, bool MODIFIED, bool BLOCKED>
+static int launch_backward_b(const void *px, void *lattice, const int64_t *boundary,
+                             const void *ans_grad, void *px_grad, void *py_grad,
+                             void *origin_grad, int B, int S, int T, int row0, cudaStream_t st) {
+  auto kern = mi_backward_kernel<real, NCW, MODIFIED, BLOCKED>;
   const size_t smem = mi_smem_bytes<real, NCW>(3);
   FRNNT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   FRNNT_KERNEL(kern<<<B, (NCW + bwd_io_warps(NCW)) * 32, smem, st>>>(
-      (const real *)px, (const real *)lattice, boundary, (const real *)ans_grad, (real *)px_grad,
-      (real *)py_grad, (real *)origin_grad, S, T));
+      (const real *)px, (real *)lattice, boundary, (const real *)ans_grad, (real *)px_grad,
+      (real *)py_grad, (real *)origin_grad, S, T, row0));
   FRNNT_CUDA(cudaGetLastError());
+  return FRNNT_OK;
+}
+
+template <typename real, int NCW, bool MODIFIED>
+static int launch_backward(const void *px, void *lattice, const int64_t *boundary,
+                           const void *ans_grad, void *px_grad, void *py_grad, void *origin_grad,
+                           int B, int S, int T, cudaStream_t st) {
+  return launch_backward_b<real, NCW, MODIFIED, false>(px, lattice, boundary, ans_grad, px_grad,
+                                                       py_grad, origin_grad, B, S, T, 0, st);
+}
+
+// one launch per block of rows, bottom to top
+template <typename real, bool MODIFIED>
+static int launch_backward_blocked(const void *px, void *lattice, const int64_t *boundary,
+                                   const void *ans_grad, void *px_grad, void *py_grad,
+                                   void *origin_grad, int B, int S, int T, cudaStream_t st) {
+  constexpr int NCW = sizeof(real) == 8 ? 4 : 8;
+  constexpr int ROWS = NCW * 32;
+  for (int row0 = (S / ROWS) * ROWS; row0 >= 0; row0 -= ROWS) {
+    const int rc = launch_backward_b<real, NCW, MODIFIED, true>(
+        px, lattice, boundary, ans_grad, px_grad, py_grad, origin_grad, B, S, T, row0, st);
+    if (rc != FRNNT_OK) return rc;
+  }
   return FRNNT_OK;
 }
 
@@ -538,17 +629,17 @@ static int launch_backward(const void *px, const void *lattice, const int64_t *b
     case 5: return FN<real, 5, MOD>(__VA_ARGS__);                         \
     case 6: return FN<real, 6, MOD>(__VA_ARGS__);                         \
     case 7: return FN<real, 7, MOD>(__VA_ARGS__);                         \
-    default: return FN<real, 8, MOD>(__VA_ARGS__);                        \
+    case 8: return FN<real, 8, MOD>(__VA_ARGS__);                         \
+    default: return FN##_blocked<real, MOD>(__VA_ARGS__);                 \
   }
 
-// double rows are capped at 4 warps (the three rings of the backward sweep fill
-// shared memory beyond that), so only those instantiations exist
 #define MI_DISPATCH_NCW_F64(FN, MOD, ncw, ...)                            \
   switch (ncw) {                                                          \
     case 1: return FN<double, 1, MOD>(__VA_ARGS__);                       \
     case 2: return FN<double, 2, MOD>(__VA_ARGS__);                       \
     case 3: return FN<double, 3, MOD>(__VA_ARGS__);                       \
-    default: return FN<double, 4, MOD>(__VA_ARGS__);                      \
+    case 4: return FN<double, 4, MOD>(__VA_ARGS__);                       \
+    default: return FN##_blocked<double, MOD>(__VA_ARGS__);               \
   }
 
 #define MI_DISPATCH(FN, dtype, modified, ncw, ...)                        \
@@ -562,16 +653,14 @@ static int launch_backward(const void *px, const void *lattice, const int64_t *b
     }                                                                     \
   } while (0)
 
+// *ncw = compute warps of the single launch that holds the whole lattice, or 0 when
+// the lattice has more rows than that and is swept in row blocks
 static int mi_check_sizes(int dtype, int B, int S, int T, int modified, int *ncw) {
   FRNNT_REQUIRE(check_dtype(dtype), FRNNT_EINVAL, "dtype must be FRNNT_F32 or FRNNT_F64, got %d",
                 dtype);
   FRNNT_REQUIRE(B >= 0 && S >= 0 && T >= 0, FRNNT_EINVAL, "negative size B=%d S=%d T=%d", B, S, T);
   FRNNT_REQUIRE(modified == 0 || modified == 1, FRNNT_EINVAL, "modified must be 0 or 1");
-  const int rows_max = (dtype == FRNNT_F64 ? 4 : 8) * 32;
-  FRNNT_REQUIRE(S + 1 <= rows_max, FRNNT_EUNSUPPORTED,
-                "S+1=%d exceeds the %d lattice rows one CTA holds for this dtype", S + 1,
-                rows_max);
-  *ncw = (S + 1 + 31) / 32;
+  *ncw = S + 1 <= mi_rows_per_block(dtype) ? (S + 1 + 31) / 32 : 0;
   return FRNNT_OK;
 }
 
@@ -609,6 +698,10 @@ static int static_scratch_address(void **out) {
 
 using namespace frnnt;
 
+extern "C" int frnnt_mi_rows_per_block(int dtype) {
+  return check_dtype(dtype) ? mi_rows_per_block(dtype) : 0;
+}
+
 extern "C" size_t frnnt_mi_lattice_bytes(int dtype, int B, int S, int T) {
   if (!check_dtype(dtype) || B < 0 || S < 0 || T < 0) return 0;
   return (size_t)B * lattice_elems_per_utt(S, T) * dtype_size(dtype);
@@ -624,12 +717,16 @@ extern "C" int frnnt_mi_forward(int dtype, const void *px, const void *py,
   FRNNT_REQUIRE(ans != nullptr, FRNNT_EINVAL, "ans is NULL");
   FRNNT_REQUIRE((px != nullptr || S == 0 || (modified && T == 0)) && (py != nullptr || T == 0),
                 FRNNT_EINVAL, "px or py is NULL");
+  FRNNT_REQUIRE(ncw != 0 || lattice != nullptr, FRNNT_EINVAL,
+                "S+1=%d exceeds frnnt_mi_rows_per_block(): the sweep runs in row blocks and needs "
+                "the lattice scratch",
+                S + 1);
   cudaStream_t st = (cudaStream_t)stream;
   MI_DISPATCH(launch_forward, dtype, modified, ncw, px, py, boundary, p, ans, lattice, B, S, T, st);
   return FRNNT_OK;
 }
 
-extern "C" int frnnt_mi_backward_from_lattice(int dtype, const void *px, const void *lattice,
+extern "C" int frnnt_mi_backward_from_lattice(int dtype, const void *px, void *lattice,
                                               const int64_t *boundary, const void *ans_grad,
                                               void *px_grad, void *py_grad, void *origin_grad,
                                               int B, int S, int T, int modified, void *stream) {

@@ -42,7 +42,9 @@ def mi_forward(px: Tensor, py: Tensor, boundary: Optional[Tensor], want_p: bool 
         ans = torch.empty(B, dtype=px.dtype, device=dev)
         p = torch.empty(B, S + 1, T + 1, dtype=px.dtype, device=dev) if want_p else None
         lattice = None
-        if want_lattice:
+        # a lattice taller than one launch holds is swept in row blocks, which
+        # hand the row above each block over through the scratch
+        if want_lattice or S + 1 > _lib.lib().frnnt_mi_rows_per_block(dt):
             nbytes = _lib.lib().frnnt_mi_lattice_bytes(dt, B, S, T)
             lattice = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=dev)
         _lib.call("frnnt_mi_forward", _c_int(dt), _lib.ptr(px), _lib.ptr(py), _lib.ptr(boundary),

@@ -65,15 +65,26 @@ int frnnt_with_cuda(void);
 
 /* Bytes of the `lattice` scratch of the functions below: the forward sweep
  * stores p there by anti-diagonal ([B][S+T+1][round_up(S+1,32)]), so that it
- * writes it and the backward sweep reads it fully coalesced. */
+ * writes it and the backward sweep reads it fully coalesced; two vectors of
+ * S+T+65 values per utterance follow (see frnnt_mi_rows_per_block). */
 size_t frnnt_mi_lattice_bytes(int dtype, int B, int S, int T);
+
+/* Lattice rows (S+1) that one launch sweeps: 256 for FRNNT_F32, 128 for
+ * FRNNT_F64.  A taller lattice is swept in blocks of that many rows, one launch
+ * per block and direction (the reference tiles in 32x32 blocks and launches once
+ * per anti-diagonal of tiles, mutual_information_cuda.cu:680-731).  The row above
+ * a block is read back from `lattice`, which frnnt_mi_forward then requires, and
+ * the reverse sweep passes the gradients that cross a block edge through the two
+ * vectors at the end of `lattice`, which is why it takes it non-const. */
+int frnnt_mi_rows_per_block(int dtype);
 
 /* Forward recursion.  Replaces mutual_information_forward(px, py, boundary, p)
  * of the reference's extension module (fast_rnnt/python/csrc/mutual_information.cu:27-45,
  * MutualInformationCuda at fast_rnnt/csrc/mutual_information_cuda.cu:676-728).
  *   p       ([B][S+1][T+1], the reference's layout) may be NULL when the caller
  *           does not need the lattice;
- *   lattice (scratch, see above) may be NULL when no backward sweep will follow;
+ *   lattice (scratch, see above) may be NULL when no backward sweep will follow
+ *           and S+1 <= frnnt_mi_rows_per_block(dtype);
  *   ans     [B] receives p[b][s_end][t_end]. */
 int frnnt_mi_forward(int dtype, const void *px, const void *py, const int64_t *boundary,
                      void *p, void *ans, void *lattice, int B, int S, int T, int modified,
@@ -85,7 +96,7 @@ int frnnt_mi_forward(int dtype, const void *px, const void *py, const int64_t *b
  * gradient that reaches p[s_begin][t_begin], which equals ans_grad[b] up to
  * rounding when the sweep is right (the reference overwrites ans_grad with it,
  * mutual_information_cuda.cu:667-669). */
-int frnnt_mi_backward_from_lattice(int dtype, const void *px, const void *lattice,
+int frnnt_mi_backward_from_lattice(int dtype, const void *px, void *lattice,
                                    const int64_t *boundary, const void *ans_grad, void *px_grad,
                                    void *py_grad, void *origin_grad, int B, int S, int T,
                                    int modified, void *stream);

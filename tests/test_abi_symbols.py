@@ -33,14 +33,15 @@ def test_host_side_checks(lib):
     lib.frnnt_mi_lattice_bytes.restype = ctypes.c_size_t
     assert lib.frnnt_version() >= 100
     assert lib.frnnt_with_cuda() == 1
-    # (S+T+1) diagonals of round_up(S+1, 32) floats per utterance
-    assert lib.frnnt_mi_lattice_bytes(0, 2, 100, 500) == 2 * 601 * 128 * 4
+    # (S+T+1) diagonals of round_up(S+1, 32) floats per utterance + two edge vectors
+    assert lib.frnnt_mi_lattice_bytes(0, 2, 100, 500) == 2 * (601 * 128 + 2 * (601 + 64)) * 4
+    assert lib.frnnt_mi_rows_per_block(0) == 256 and lib.frnnt_mi_rows_per_block(1) == 128
     assert lib.frnnt_mi_lattice_bytes(7, 2, 100, 500) == 0          # bad dtype
     # argument errors are found before any CUDA call
     rc = lib.frnnt_mi_forward(ctypes.c_int(5), None, None, None, None, None, None, 1, 1, 1, 0, None)
     assert rc == -1 and b"dtype" in lib.frnnt_last_error()
     rc = lib.frnnt_mi_forward(ctypes.c_int(0), None, None, None, None, None, None, 1, 5000, 10, 0, None)
-    assert rc == -2 and b"lattice rows" in lib.frnnt_last_error()
+    assert rc == -1 and b"ans is NULL" in lib.frnnt_last_error()
     rc = lib.frnnt_prune_ranges(ctypes.c_int(0), None, None, None, None, 1, 4, 4, 5, 9, None)
     assert rc == -1
 

@@ -66,7 +66,9 @@ def test_mi_golden(name):
 
 SIZES = [(1, 1, 1), (2, 1, 7), (3, 5, 1), (2, 31, 40), (2, 32, 33), (3, 33, 31), (2, 63, 70),
          (2, 64, 64), (2, 65, 100), (1, 100, 37), (2, 127, 130), (1, 128, 20), (2, 200, 210),
-         (1, 255, 256), (4, 17, 300), (2, 0, 9)]
+         (1, 255, 256), (4, 17, 300), (2, 0, 9),
+         # taller than one launch holds (256 float rows, 128 double rows): row blocks
+         (2, 256, 40), (3, 300, 310), (1, 600, 100), (2, 513, 64)]
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
@@ -76,8 +78,6 @@ def test_mi_random_vs_oracle(dtype, modified):
     torch.manual_seed(5)
     rtol, atol = tol(dtype)
     for (B, S, T) in SIZES:
-        if dtype == torch.float64 and S + 1 > 128:
-            continue
         if modified and T < S:
             T = S + rng.randint(0, 5)
         for kind in ("none", "random", "full"):
@@ -143,9 +143,16 @@ def test_mi_c2_full_size():
 
 def test_errors_are_reported():
     from fast_rnnt_b200 import FrnntError, mutual_information as mi
+    from fast_rnnt_b200 import _lib
     px = torch.zeros(1, 300, 5, device="cuda")
     py = torch.zeros(1, 301, 4, device="cuda")
-    with pytest.raises(FrnntError):
-        mi.mi_forward(px, py, None)
+    ans = torch.zeros(1, device="cuda")
+    # a lattice taller than one launch holds needs the scratch
+    with pytest.raises(FrnntError, match="lattice scratch"):
+        _lib.call("frnnt_mi_forward", 0, _lib.ptr(px), _lib.ptr(py), None, None, _lib.ptr(ans),
+                  None, 1, 300, 4, 0, None)
+    with pytest.raises(FrnntError, match="ans is NULL"):
+        _lib.call("frnnt_mi_forward", 0, _lib.ptr(px), _lib.ptr(py), None, None, None,
+                  None, 1, 300, 4, 0, None)
     with pytest.raises(TypeError):
         mi.mi_forward(px.half(), py.half(), None)
