@@ -43,15 +43,6 @@ struct Raw4 {
 
 constexpr size_t kGemmSmemBytes = (size_t)kGemmStages * 4 * kGemmTile * 128 + 1024;
 
-// byte offset inside an MN-major [32 k][128 mn] tile of the 16-byte chunk
-// (k row kr, values 4*c4 .. 4*c4+3): atoms of 4 k x 32 mn (512 bytes) ordered
-// (mn block, k group); inside an atom the 32-byte chunks are XOR-ed with the row
-__device__ __forceinline__ uint32_t mn_tile_offset(int kr, int c4) {
-  const int c16 = c4 & 7;
-  return (uint32_t)((((c4 >> 3) * 8 + (kr >> 2)) << 9) + ((kr & 3) << 7) +
-                    ((((c16 >> 1) ^ (kr & 3)) << 5) | ((c16 & 1) << 4)));
-}
-
 template <class Pol>
 __global__ void __launch_bounds__(kGemmThreads, 1) umma_gemm_kernel(Pol pol) {
   extern __shared__ uint8_t smem_dyn[];
