@@ -27,7 +27,7 @@
 // Every mbarrier wait is bounded; on a timeout the tile is poisoned with NaN.
 #include "common.cuh"
 #include "umma.cuh"
-#include "umma_gemm.cuh"
+#include "umma_linear.cuh"
 
 namespace frnnt {
 
@@ -273,113 +273,66 @@ int launch_norm_umma(const float *lm, const float *am, const float *lmmax, const
 }
 
 // ---- gradient contractions -------------------------------------------------------------
+// Both run on the engine in umma_linear.cuh, batched over the utterances (3-D tensor
+// maps: rows / columns outside an utterance's matrix arrive as zeros), with the
+// exponentiated operand produced in the engine's split pass and the remaining
+// factors applied in its epilogue; no exponentiated copy of am / lm exists in HBM.
+//
 // dlm[s][c] = -L[s][c] * sum_t Rw[s][t] A[t][c]  (+ lm-only / unigram terms)
-//   tile: M = c (lanes, so the stores along c are contiguous), N = s, K = t
-//   A operand = e^{am[t][c]-ammax[t]}: contiguous along c -> MN-major
-//   B operand = Rw[s][t]:               contiguous along t -> K-major
-struct LmGradUmma {
-  static constexpr bool A_MN = true, B_MN = false;
-  const float *am, *ammax, *rw, *lm, *lmmax, *lmsum, *gl, *dp, *rowdot;
+//   tile: M = s, N = c, K = t
+//   A operand = Rw[s][t]:                contiguous along t -> K-major
+//   B operand = e^{am[t][c]-ammax[t]}:   contiguous along c -> MN-major, shift = ammax
+struct LmGradExt {
+  static constexpr bool kBatched = true, kExpB = true;
+  const float *ammax, *lm, *lmmax, *lmsum, *gl, *dp, *rowdot;
   float *lm_grad;
-  int S1, T, C, Tp;
-  __device__ void init(int b) {
-    am += (size_t)b * T * C;
-    ammax += (size_t)b * T;
-    rw += (size_t)b * S1 * Tp;
-    lm += (size_t)b * S1 * C;
-    lmmax += (size_t)b * S1;
-    lmsum += (size_t)b * S1;
-    if (gl) gl += (size_t)b * S1;
-    if (rowdot) rowdot += (size_t)b * S1;
-    lm_grad += (size_t)b * S1 * C;
-  }
-  __device__ int K() const { return T; }
-  // exp(-inf - 0) = 0 outside the matrix
-  __device__ Raw4 a_raw(int c, int t) const {
-    if (c >= C || t >= T) return Raw4{make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY), 0.f};
-    return Raw4{*reinterpret_cast<const float4 *>(am + (size_t)t * C + c), ammax[t]};
-  }
-  __device__ float4 a_fix(const Raw4 &r) const {
-    return make_float4(expf(r.v.x - r.aux), expf(r.v.y - r.aux), expf(r.v.z - r.aux),
-                       expf(r.v.w - r.aux));
-  }
-  __device__ Raw4 b_raw(int s, int t) const {
-    if (s >= S1 || t >= Tp) return Raw4{make_float4(0.f, 0.f, 0.f, 0.f), 0.f};
-    return Raw4{*reinterpret_cast<const float4 *>(rw + (size_t)s * Tp + t), 0.f};
-  }
-  __device__ float4 b_fix(const Raw4 &r) const { return r.v; }
-  __device__ void store(int c, int s0, const float (&acc)[16]) const {
-    if (c >= C) return;
+  int S1, T, C;
+  __device__ const float *b_shift(int b) const { return ammax + (size_t)b * T; }
+  __device__ const float *pre_row(int b, int s) const { return lm + ((size_t)b * S1 + s) * C; }
+  __device__ float *out_row(int b, int s) const { return lm_grad + ((size_t)b * S1 + s) * C; }
+  __device__ void finish(int b, int s, int c0, float (&v)[16], const float (&x)[16]) const {
+    const size_t row = (size_t)b * S1 + s;
+    const float mx = lmmax[row];
+    const float inv_sum = gl != nullptr ? 1.f / lmsum[row] : 0.f;
+    const float g = gl != nullptr ? gl[row] : 0.f;
+    const float rd = (gl != nullptr && dp != nullptr) ? rowdot[row] : 0.f;
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-      const int s = s0 + i;
-      if (s >= S1) break;
-      const float L = expf(lm[(size_t)s * C + c] - lmmax[s]);
-      float v = -(L * acc[i]);
+      const float L = expf(x[i] - mx);
+      float r = -(L * v[i]);
       if (gl != nullptr) {
-        const float P = L / lmsum[s];
-        v -= gl[s] * P;
-        if (dp != nullptr) v += P * (dp[c] - rowdot[s]);
+        const float P = L * inv_sum;
+        r -= g * P;
+        if (dp != nullptr && c0 + i < C) r += P * (dp[c0 + i] - rd);
       }
-      lm_grad[(size_t)s * C + c] = v;
+      v[i] = r;
     }
-  }
-  __device__ void poison(int c, int s0) const {
-    if (c >= C) return;
-    for (int i = 0; i < 16 && s0 + i < S1; ++i) lm_grad[(size_t)(s0 + i) * C + c] = NAN;
   }
 };
 
 // dam[t][c] = -A[t][c] * sum_s Rw[s][t] L[s][c]  (+ am-only term)
-//   tile: M = c, N = t, K = s;  A operand = e^{lm[s][c]-lmmax[s]} (MN-major),
-//   B operand = Rw[s][t] (contiguous along t = N -> MN-major)
-struct AmGradUmma {
-  static constexpr bool A_MN = true, B_MN = true;
-  const float *lm, *lmmax, *rw, *am, *ammax, *h, *uni, *amonly;
+//   tile: M = t, N = c, K = s
+//   A operand = Rw[s][t]:                contiguous along t = M -> MN-major
+//   B operand = e^{lm[s][c]-lmmax[s]}:   contiguous along c -> MN-major, shift = lmmax
+struct AmGradExt {
+  static constexpr bool kBatched = true, kExpB = true;
+  const float *lmmax, *am, *ammax, *h, *uni, *amonly;
   float *am_grad;
-  int S1, T, C, Tp;
-  __device__ void init(int b) {
-    lm += (size_t)b * S1 * C;
-    lmmax += (size_t)b * S1;
-    rw += (size_t)b * S1 * Tp;
-    am += (size_t)b * T * C;
-    ammax += (size_t)b * T;
-    if (h) {
-      h += (size_t)b * T;
-      amonly += (size_t)b * T;
-    }
-    am_grad += (size_t)b * T * C;
-  }
-  __device__ int K() const { return S1; }
-  __device__ Raw4 a_raw(int c, int s) const {
-    if (c >= C || s >= S1) return Raw4{make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY), 0.f};
-    return Raw4{*reinterpret_cast<const float4 *>(lm + (size_t)s * C + c), lmmax[s]};
-  }
-  __device__ float4 a_fix(const Raw4 &r) const {
-    return make_float4(expf(r.v.x - r.aux), expf(r.v.y - r.aux), expf(r.v.z - r.aux),
-                       expf(r.v.w - r.aux));
-  }
-  __device__ Raw4 b_raw(int t, int s) const {
-    if (t >= Tp || s >= S1) return Raw4{make_float4(0.f, 0.f, 0.f, 0.f), 0.f};
-    return Raw4{*reinterpret_cast<const float4 *>(rw + (size_t)s * Tp + t), 0.f};
-  }
-  __device__ float4 b_fix(const Raw4 &r) const { return r.v; }
-  __device__ void store(int c, int t0, const float (&acc)[16]) const {
-    if (c >= C) return;
-    const float u = h != nullptr ? uni[c] : 0.f;
+  int S1, T, C;
+  __device__ const float *b_shift(int b) const { return lmmax + (size_t)b * S1; }
+  __device__ const float *pre_row(int b, int t) const { return am + ((size_t)b * T + t) * C; }
+  __device__ float *out_row(int b, int t) const { return am_grad + ((size_t)b * T + t) * C; }
+  __device__ void finish(int b, int t, int c0, float (&v)[16], const float (&x)[16]) const {
+    const size_t row = (size_t)b * T + t;
+    const float mx = ammax[row];
+    const float w = h != nullptr ? h[row] * expf(mx - amonly[row]) : 0.f;
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-      const int t = t0 + i;
-      if (t >= T) break;
-      const float A = expf(am[(size_t)t * C + c] - ammax[t]);
-      float v = -(A * acc[i]);
-      if (h != nullptr) v -= h[t] * A * u * expf(ammax[t] - amonly[t]);
-      am_grad[(size_t)t * C + c] = v;
+      const float A = expf(x[i] - mx);
+      float r = -(A * v[i]);
+      if (h != nullptr && c0 + i < C) r -= w * A * uni[c0 + i];
+      v[i] = r;
     }
-  }
-  __device__ void poison(int c, int t0) const {
-    if (c >= C) return;
-    for (int i = 0; i < 16 && t0 + i < T; ++i) am_grad[(size_t)(t0 + i) * C + c] = NAN;
   }
 };
 
@@ -388,24 +341,29 @@ int launch_simple_grads_umma(const float *lm, const float *am, const float *lmma
                              const float *uni, const float *rw, const float *gl, const float *h,
                              const float *dp, const float *rowdot, float *lm_grad, float *am_grad,
                              int B, int S1, int T, int C, int Tp, cudaStream_t st) {
-  const int ctiles = (C + kGemmTile - 1) / kGemmTile;
+  if (B == 0 || C == 0) return FRNNT_OK;
+  const int ctiles = (C + kLinTile - 1) / kLinTile;
+  CUtensorMap ma, mb;
+  int rc;
   {
-    LmGradUmma pol{am, ammax, rw, lm, lmmax, lmsum, gl, dp, rowdot, lm_grad, S1, T, C, Tp};
-    auto kern = umma_gemm_kernel<LmGradUmma>;
-    FRNNT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    (int)kGemmSmemBytes));
-    dim3 grid((unsigned)ctiles, (unsigned)B, (unsigned)((S1 + kGemmTile - 1) / kGemmTile));
-    FRNNT_KERNEL(kern<<<grid, kGemmThreads, kGemmSmemBytes, st>>>(pol));
-    FRNNT_CUDA(cudaGetLastError());
+    rc = make_operand_map(&ma, rw, S1, T, Tp, (long long)S1 * Tp, B, false);
+    if (rc == FRNNT_OK) rc = make_operand_map(&mb, am, T, C, C, (long long)T * C, B, true);
+    if (rc != FRNNT_OK) return rc;
+    const LinShape shape{S1, C, T, ((T + kLinBK - 1) / kLinBK) * kLinBK, (S1 + kLinTile - 1) / kLinTile,
+                         ctiles, B};
+    const LmGradExt ext{ammax, lm, lmmax, lmsum, gl, dp, rowdot, lm_grad, S1, T, C};
+    rc = launch_linear_umma<false, true>(ma, mb, shape, ext, st);
+    if (rc != FRNNT_OK) return rc;
   }
   if (T > 0) {
-    AmGradUmma pol{lm, lmmax, rw, am, ammax, h, uni, amonly, am_grad, S1, T, C, Tp};
-    auto kern = umma_gemm_kernel<AmGradUmma>;
-    FRNNT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    (int)kGemmSmemBytes));
-    dim3 grid((unsigned)ctiles, (unsigned)B, (unsigned)((T + kGemmTile - 1) / kGemmTile));
-    FRNNT_KERNEL(kern<<<grid, kGemmThreads, kGemmSmemBytes, st>>>(pol));
-    FRNNT_CUDA(cudaGetLastError());
+    rc = make_operand_map(&ma, rw, S1, T, Tp, (long long)S1 * Tp, B, true);
+    if (rc == FRNNT_OK) rc = make_operand_map(&mb, lm, S1, C, C, (long long)S1 * C, B, true);
+    if (rc != FRNNT_OK) return rc;
+    const LinShape shape{T, C, S1, ((S1 + kLinBK - 1) / kLinBK) * kLinBK, (T + kLinTile - 1) / kLinTile,
+                         ctiles, B};
+    const AmGradExt ext{lmmax, am, ammax, h, uni, amonly, am_grad, S1, T, C};
+    rc = launch_linear_umma<true, true>(ma, mb, shape, ext, st);
+    if (rc != FRNNT_OK) return rc;
   }
   return FRNNT_OK;
 }
