@@ -33,7 +33,8 @@ def lib():
         _lib = ctypes.CDLL(LIB_PATH)
         _lib.frnnt_last_error.restype = ctypes.c_char_p
         for name in ("frnnt_mi_lattice_bytes", "frnnt_simple_saved_bytes",
-                     "frnnt_simple_scratch_bytes"):
+                     "frnnt_simple_scratch_bytes", "frnnt_matmul_tn_scratch_floats",
+                     "frnnt_joiner_input_grads_scratch_bytes"):
             if hasattr(_lib, name):
                 getattr(_lib, name).restype = _c_sz
     return _lib

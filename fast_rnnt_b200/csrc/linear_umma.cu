@@ -15,12 +15,17 @@
 namespace frnnt {
 
 // (+ bias[n]) and, for the gradient that flows back through tanh, * (1 - tanh_out^2)
+template <bool COLSUM>
 struct PlainLinearExt {
-  static constexpr bool kBatched = false, kExpB = false;
+  static constexpr bool kBatched = false, kExpB = false, kColSumA = COLSUM;
   float *out;             // [splits][M][N] (splits == 1: the result itself)
   const float *bias;      // [N] or nullptr
   const float *tanh_out;  // [M][N] or nullptr
+  float *colsum;          // [splits][2][M] partial sums of A over its rows, or nullptr
   int M, N;
+  __device__ float *a_colsum(int z, int half) const {
+    return colsum != nullptr ? colsum + ((size_t)z * 2 + half) * M : nullptr;
+  }
   __device__ const float *b_shift(int) const { return nullptr; }
   __device__ const float *pre_row(int, int m) const {
     return tanh_out != nullptr ? tanh_out + (size_t)m * N : nullptr;
@@ -76,7 +81,7 @@ extern "C" int frnnt_matmul_nt(const float *a, const float *b, const float *bias
   if (rc != FRNNT_OK) return rc;
   const int mt = (M + kLinTile - 1) / kLinTile, nt = (N + kLinTile - 1) / kLinTile;
   const LinShape shape{M, N, K, ((K + kLinBK - 1) / kLinBK) * kLinBK, mt, nt, 1};
-  const PlainLinearExt ext{d, bias, tanh_out, M, N};
+  const PlainLinearExt<false> ext{d, bias, tanh_out, nullptr, M, N};
   return launch_linear_umma<false, false>(ma, mb, shape, ext, (cudaStream_t)stream);
 }
 
@@ -90,8 +95,14 @@ extern "C" int frnnt_matmul_tn_splits(int M, int N, int R) {
   return splits;
 }
 
-extern "C" int frnnt_matmul_tn(const float *a, const float *b, float *d, float *partials, int M,
-                               int N, int R, void *stream) {
+extern "C" size_t frnnt_matmul_tn_scratch_floats(int M, int N, int R) {
+  if (M <= 0 || N <= 0 || R <= 0) return 0;
+  const size_t splits = (size_t)frnnt_matmul_tn_splits(M, N, R);
+  return (splits > 1 ? splits * M * N : 0) + 2 * splits * M;
+}
+
+extern "C" int frnnt_matmul_tn_colsum(const float *a, const float *b, float *d, float *a_colsum,
+                                      float *scratch, int M, int N, int R, void *stream) {
   FRNNT_REQUIRE(M >= 0 && N >= 0 && R >= 0, FRNNT_EINVAL, "negative size");
   if (M == 0 || N == 0) return FRNNT_OK;
   FRNNT_REQUIRE(R > 0, FRNNT_EINVAL, "R must be positive");
@@ -100,8 +111,10 @@ extern "C" int frnnt_matmul_tn(const float *a, const float *b, float *d, float *
   if (rc != FRNNT_OK) return rc;
   FRNNT_REQUIRE(d != nullptr && (uintptr_t)d % 16 == 0, FRNNT_EINVAL, "d is NULL or misaligned");
   const int splits = frnnt_matmul_tn_splits(M, N, R);
-  FRNNT_REQUIRE(splits == 1 || (partials != nullptr && (uintptr_t)partials % 16 == 0), FRNNT_EINVAL,
-                "partials scratch of splits*M*N floats is required");
+  FRNNT_REQUIRE((splits == 1 && a_colsum == nullptr) || (scratch != nullptr && (uintptr_t)scratch % 16 == 0),
+                FRNNT_EINVAL, "a scratch of frnnt_matmul_tn_scratch_floats() floats is required");
+  float *partials = splits > 1 ? scratch : nullptr;
+  float *cs_partials = a_colsum != nullptr ? scratch + (splits > 1 ? (size_t)splits * M * N : 0) : nullptr;
   CUtensorMap ma, mb;
   // operands contiguous along M / N: boxes of 32 values x 32 reduction rows, 32-byte swizzle atoms
   rc = make_operand_map(&ma, a, R, M, M, 0, 0, true);
@@ -111,14 +124,27 @@ extern "C" int frnnt_matmul_tn(const float *a, const float *b, float *d, float *
   const int kblocks = (R + kLinBK - 1) / kLinBK;
   const int k_per_split = ((kblocks + splits - 1) / splits) * kLinBK;
   const LinShape shape{M, N, R, k_per_split, mt, nt, splits};
-  const PlainLinearExt ext{splits == 1 ? d : partials, nullptr, nullptr, M, N};
   cudaStream_t st = (cudaStream_t)stream;
-  rc = launch_linear_umma<true, true>(ma, mb, shape, ext, st);
+  float *out = splits == 1 ? d : partials;
+  if (a_colsum != nullptr)
+    rc = launch_linear_umma<true, true>(ma, mb, shape, PlainLinearExt<true>{out, nullptr, nullptr, cs_partials, M, N}, st);
+  else
+    rc = launch_linear_umma<true, true>(ma, mb, shape, PlainLinearExt<false>{out, nullptr, nullptr, nullptr, M, N}, st);
   if (rc != FRNNT_OK) return rc;
   if (splits > 1) {
     const long long n = (long long)M * N;
     FRNNT_KERNEL(splitk_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(partials, d, n, splits));
     FRNNT_CUDA(cudaGetLastError());
   }
+  if (a_colsum != nullptr) {
+    FRNNT_KERNEL(splitk_reduce_kernel<<<(unsigned)((M + 255) / 256), 256, 0, st>>>(cs_partials, a_colsum, M,
+                                                                              2 * splits));
+    FRNNT_CUDA(cudaGetLastError());
+  }
   return FRNNT_OK;
+}
+
+extern "C" int frnnt_matmul_tn(const float *a, const float *b, float *d, float *partials, int M,
+                               int N, int R, void *stream) {
+  return frnnt_matmul_tn_colsum(a, b, d, nullptr, partials, M, N, R, stream);
 }

@@ -17,6 +17,8 @@
 // prune_gather: a row copy lm[b][ranges[b][t][k]][:] -> out[b][t][k][:] with
 //   16-byte accesses; its backward sums, for every (b, s), the gradient rows
 //   whose range entry equals s, in frame order (deterministic, no atomics).
+#include <climits>
+
 #include "common.cuh"
 
 namespace frnnt {
@@ -271,6 +273,118 @@ __global__ void sum_over_range_kernel(const real *__restrict__ gz, real *__restr
   }
 }
 
+// ---- both input gradients of the pruned joiner from ONE pass over gz -----------------------
+// enc_grad[b][t][:] = sum_k gz[b][t][k][:]
+// dec_grad[b][s][:] = sum over (t,k) with ranges[b][t][k] == s of gz[b][t][k][:]
+// One CTA per (utterance, chunk of kJgFrames frames); thread <-> 4 columns of D.  The
+// rows of a chunk land on a few neighbouring s (get_rnnt_prune_ranges moves the window
+// by less than one row per frame), so the CTA keeps a window of kJgWindow rows of partial
+// sums in shared memory, each thread adding into its own columns in (t, k) order, and
+// writes the used rows to a scratch; joiner_dec_reduce_kernel then adds the chunks'
+// partial rows per (b, s) in chunk order.  Rows that fall outside the window (possible
+// only for ranges that are not the monotone ones this library produces) go to dec_grad
+// with atomicAdd, which is why dec_grad is cleared first.
+constexpr int kJgFrames = 16;
+constexpr int kJgWindow = 16;
+constexpr int kJgThreads = 128;
+
+__global__ void __launch_bounds__(kJgThreads)
+joiner_input_grads_kernel(const float *__restrict__ gz, const int64_t *__restrict__ ranges,
+                          float *__restrict__ enc_grad, float *__restrict__ dec_grad,
+                          float *__restrict__ partial, int *__restrict__ window, int T, int R, int S1,
+                          int D) {
+  extern __shared__ float4 jg_smem[];  // [kJgWindow][D / 4]
+  __shared__ int s_lo_sh, s_hi_sh;
+  const int b = blockIdx.y, ch = blockIdx.x, nch = gridDim.x;
+  const int t0 = ch * kJgFrames, t1 = min(T, t0 + kJgFrames);
+  const int dvec = D / 4;
+  const int64_t *rg = ranges + ((size_t)b * T + t0) * R;
+  const int n_entries = (t1 - t0) * R;
+  if (threadIdx.x == 0) {
+    s_lo_sh = INT_MAX;
+    s_hi_sh = -1;
+  }
+  __syncthreads();
+  {
+    int lo = INT_MAX, hi = -1;
+    for (int e = threadIdx.x; e < n_entries; e += kJgThreads) {
+      const long long s = rg[e];
+      if (s >= 0 && s < S1) {
+        lo = min(lo, (int)s);
+        hi = max(hi, (int)s);
+      }
+    }
+    if (hi >= 0) {
+      atomicMin(&s_lo_sh, lo);
+      atomicMax(&s_hi_sh, hi);
+    }
+  }
+  for (int i = threadIdx.x; i < kJgWindow * dvec; i += kJgThreads) jg_smem[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  __syncthreads();
+  const int s_lo = s_lo_sh, s_hi = s_hi_sh;
+  const int rows_used = s_hi >= 0 ? min(kJgWindow, s_hi - s_lo + 1) : 0;
+  if (threadIdx.x == 0) {
+    window[((size_t)b * nch + ch) * 2] = s_lo;
+    window[((size_t)b * nch + ch) * 2 + 1] = rows_used;
+  }
+  const float4 *G = reinterpret_cast<const float4 *>(gz) + ((size_t)b * T + t0) * R * dvec;
+  float4 *E = reinterpret_cast<float4 *>(enc_grad) + ((size_t)b * T + t0) * dvec;
+  for (int v = threadIdx.x; v < dvec; v += kJgThreads) {
+    for (int t = 0; t < t1 - t0; ++t) {
+      float4 e = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int k0 = 0; k0 < R; k0 += 8) {
+        float4 x[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          if (k0 + u < R) x[u] = G[((size_t)t * R + k0 + u) * dvec + v];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          if (k0 + u >= R) break;
+          e.x += x[u].x, e.y += x[u].y, e.z += x[u].z, e.w += x[u].w;
+          const long long s = rg[t * R + k0 + u];
+          if (s < 0 || s >= S1) continue;
+          const int sl = (int)s - s_lo;
+          if (sl < kJgWindow) {
+            float4 a = jg_smem[sl * dvec + v];
+            a.x += x[u].x, a.y += x[u].y, a.z += x[u].z, a.w += x[u].w;
+            jg_smem[sl * dvec + v] = a;
+          } else {
+            float *dst = dec_grad + ((size_t)b * S1 + s) * D + 4 * v;
+            atomicAdd(dst, x[u].x), atomicAdd(dst + 1, x[u].y);
+            atomicAdd(dst + 2, x[u].z), atomicAdd(dst + 3, x[u].w);
+          }
+        }
+      }
+      E[(size_t)t * dvec + v] = e;
+    }
+    float4 *P = reinterpret_cast<float4 *>(partial) + ((size_t)b * nch + ch) * kJgWindow * dvec;
+    for (int r = 0; r < rows_used; ++r) P[(size_t)r * dvec + v] = jg_smem[r * dvec + v];
+  }
+}
+
+// dec_grad[b][s][:] += the chunks' partial rows for s, in chunk order
+__global__ void __launch_bounds__(kJgThreads)
+joiner_dec_reduce_kernel(const float *__restrict__ partial, const int *__restrict__ window,
+                         float *__restrict__ dec_grad, int nch, int S1, int D) {
+  const int b = blockIdx.y, s = blockIdx.x;
+  const int dvec = D / 4;
+  const int *win = window + (size_t)b * nch * 2;
+  float4 *out = reinterpret_cast<float4 *>(dec_grad) + ((size_t)b * S1 + s) * dvec;
+  for (int v = threadIdx.x; v < dvec; v += kJgThreads) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int ch = 0; ch < nch; ++ch) {
+      const int lo = win[2 * ch], n = win[2 * ch + 1];
+      if (s >= lo && s < lo + n) {
+        const float4 x = reinterpret_cast<const float4 *>(partial)[(((size_t)b * nch + ch) * kJgWindow + (s - lo)) * dvec + v];
+        acc.x += x.x, acc.y += x.y, acc.z += x.z, acc.w += x.w;
+      }
+    }
+    float4 o = out[v];
+    o.x += acc.x, o.y += acc.y, o.z += acc.z, o.w += acc.w;
+    out[v] = o;
+  }
+}
+
 }  // namespace frnnt
 
 using namespace frnnt;
@@ -431,6 +545,42 @@ extern "C" int frnnt_sum_over_range(int dtype, const void *gz, void *out, long l
       FRNNT_KERNEL(sum_over_range_kernel<double, double, 1><<<grid, 256, 0, st>>>(
           (const double *)gz, (double *)out, frames, R, D));
   }
+  FRNNT_CUDA(cudaGetLastError());
+  return FRNNT_OK;
+}
+
+extern "C" size_t frnnt_joiner_input_grads_scratch_bytes(int B, int T, int D) {
+  if (B <= 0 || T <= 0 || D <= 0) return 0;
+  const size_t nch = (size_t)(T + kJgFrames - 1) / kJgFrames;
+  return (size_t)B * nch * ((size_t)kJgWindow * D * sizeof(float) + 2 * sizeof(int));
+}
+
+extern "C" int frnnt_joiner_input_grads(const float *gz, const int64_t *ranges, float *enc_grad,
+                                        float *dec_grad, void *scratch, int B, int S1, int T, int R,
+                                        int D, void *stream) {
+  FRNNT_REQUIRE(B >= 0 && S1 >= 1 && T >= 0 && R >= 1 && D >= 1, FRNNT_EINVAL, "bad sizes");
+  FRNNT_REQUIRE(B <= 65535, FRNNT_EUNSUPPORTED, "B too large for the grid");
+  FRNNT_REQUIRE(D % 4 == 0 && (size_t)kJgWindow * D * sizeof(float) <= 200 * 1024, FRNNT_EUNSUPPORTED,
+                "D must be a multiple of 4 and at most %d", 200 * 1024 / (kJgWindow * 4));
+  if (B == 0) return FRNNT_OK;
+  FRNNT_REQUIRE(dec_grad != nullptr, FRNNT_EINVAL, "dec_grad is NULL");
+  cudaStream_t st = (cudaStream_t)stream;
+  FRNNT_CUDA(cudaMemsetAsync(dec_grad, 0, (size_t)B * S1 * D * sizeof(float), st));
+  if (T == 0) return FRNNT_OK;
+  FRNNT_REQUIRE(gz && ranges && enc_grad && scratch, FRNNT_EINVAL, "NULL argument");
+  FRNNT_REQUIRE((uintptr_t)gz % 16 == 0 && (uintptr_t)enc_grad % 16 == 0 && (uintptr_t)dec_grad % 16 == 0 &&
+                    (uintptr_t)scratch % 16 == 0,
+                FRNNT_EUNSUPPORTED, "pointers must be 16-byte aligned");
+  const int nch = (T + kJgFrames - 1) / kJgFrames;
+  float *partial = (float *)scratch;
+  int *window = (int *)(partial + (size_t)B * nch * kJgWindow * D);
+  const size_t smem = (size_t)kJgWindow * D * sizeof(float);
+  FRNNT_CUDA(cudaFuncSetAttribute(joiner_input_grads_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  (int)smem));
+  FRNNT_KERNEL(joiner_input_grads_kernel<<<dim3((unsigned)nch, (unsigned)B), kJgThreads, smem, st>>>(
+      gz, ranges, enc_grad, dec_grad, partial, window, T, R, S1, D));
+  FRNNT_KERNEL(joiner_dec_reduce_kernel<<<dim3((unsigned)S1, (unsigned)B), kJgThreads, 0, st>>>(
+      partial, window, dec_grad, nch, S1, D));
   FRNNT_CUDA(cudaGetLastError());
   return FRNNT_OK;
 }

@@ -283,7 +283,8 @@ int launch_norm_umma(const float *lm, const float *am, const float *lmmax, const
 //   A operand = Rw[s][t]:                contiguous along t -> K-major
 //   B operand = e^{am[t][c]-ammax[t]}:   contiguous along c -> MN-major, shift = ammax
 struct LmGradExt {
-  static constexpr bool kBatched = true, kExpB = true;
+  static constexpr bool kBatched = true, kExpB = true, kColSumA = false;
+  __device__ float *a_colsum(int, int) const { return nullptr; }
   const float *ammax, *lm, *lmmax, *lmsum, *gl, *dp, *rowdot;
   float *lm_grad;
   int S1, T, C;
@@ -315,7 +316,8 @@ struct LmGradExt {
 //   A operand = Rw[s][t]:                contiguous along t = M -> MN-major
 //   B operand = e^{lm[s][c]-lmmax[s]}:   contiguous along c -> MN-major, shift = lmmax
 struct AmGradExt {
-  static constexpr bool kBatched = true, kExpB = true;
+  static constexpr bool kBatched = true, kExpB = true, kColSumA = false;
+  __device__ float *a_colsum(int, int) const { return nullptr; }
   const float *lmmax, *am, *ammax, *h, *uni, *amonly;
   float *am_grad;
   int S1, T, C;

@@ -43,6 +43,9 @@
 //   void finish(int z, int m, int n, float (&v)[16], const float (&x)[16]) const;
 //                                     columns n..n+15 of row m, in place
 //   float *out_row(int z, int m) const;         where row m of the result goes
+//   static constexpr bool kColSumA;   also sum the A operand over k (per row m of the tile):
+//   float *a_colsum(int z, int half) const;     [M] partial sums of work-item slice z, one per
+//                                     half of the split warps (they share a K slice 16 / 16)
 #pragma once
 #include <cuda.h>
 #include <cudaTypedefs.h>
@@ -250,6 +253,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     for (int w = blockIdx.x; w < n_items && !*vfailed; w += gridDim.x) {
       const LinTile t = lin_tile<BATCHED>(p, w);
       const float *shift = Ext::kExpB ? ext.b_shift(t.z) : nullptr;
+      float asum = 0.f;
       for (int kb = 0; kb < t.KB && !*vfailed; ++kb, ++it) {
         const int s = it % kLinStages;
         float sh = 0.f;
@@ -302,6 +306,10 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         float hi[16], lo[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) split_tf32(av[i], hi[i], lo[i]);
+        if (Ext::kColSumA) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) asum += av[i];
+        }
         // the slot was last read by the MMAs of K slice it - kLinASlots
         if (it >= kLinASlots) {
           const int ip = it - kLinASlots;
@@ -319,6 +327,10 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bar_split[s]);
+      }
+      if (Ext::kColSumA && t.n0 == 0 && t.m0 + row < p.M) {
+        float *cs = ext.a_colsum(t.z, half);
+        if (cs != nullptr) cs[t.m0 + row] = asum;
       }
     }
   } else {

@@ -14,14 +14,16 @@ def _matmul_nt(a, b, bias, M, N, K, tanh_out=None):
     return out
 
 
-def _matmul_tn(a, b, M, N, R):
-    splits = _lib.lib().frnnt_matmul_tn_splits(M, N, R)
+def _matmul_tn(a, b, M, N, R, want_colsum=False):
+    """a[R][M]^T @ b[R][N]; with want_colsum also a.sum(0), taken from the operand
+    tiles as they pass through the product (the bias gradient of a linear layer)."""
     out = torch.empty(M, N, dtype=torch.float32, device=a.device)
-    partials = (torch.empty(splits, M, N, dtype=torch.float32, device=a.device)
-                if splits > 1 else None)
-    _lib.call("frnnt_matmul_tn", _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.ptr(partials),
-              M, N, R, _lib.stream_ptr(a.device))
-    return out
+    colsum = torch.empty(M, dtype=torch.float32, device=a.device) if want_colsum else None
+    nscratch = _lib.lib().frnnt_matmul_tn_scratch_floats(M, N, R)
+    scratch = torch.empty(max(nscratch, 1), dtype=torch.float32, device=a.device)
+    _lib.call("frnnt_matmul_tn_colsum", _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.ptr(colsum),
+              _lib.ptr(scratch), M, N, R, _lib.stream_ptr(a.device))
+    return (out, colsum) if want_colsum else out
 
 
 class _Linear3xTF32(torch.autograd.Function):
@@ -49,9 +51,12 @@ class _Linear3xTF32(torch.autograd.Function):
             if ctx.needs_input_grad[0]:
                 wt = weight.t().contiguous()                      # [K][N]
                 gx = _matmul_nt(g2, wt, None, M, K, N).reshape(ctx.x_shape)
+            want_gb = ctx.has_bias and ctx.needs_input_grad[2]
             if ctx.needs_input_grad[1]:
-                gw = _matmul_tn(g2, x2, N, K, M)
-            if ctx.has_bias and ctx.needs_input_grad[2]:
+                gw = _matmul_tn(g2, x2, N, K, M, want_colsum=want_gb)
+                if want_gb:
+                    gw, gb = gw
+            elif want_gb:
                 gb = g2.sum(dim=0)
         return gx, gw, gb
 
@@ -101,17 +106,26 @@ class _PrunedJoiner(torch.autograd.Function):
             if ctx.needs_input_grad[0] or ctx.needs_input_grad[1]:
                 wt = weight.t().contiguous()
                 gz = _matmul_nt(g2, wt, None, M, D, N, tanh_out=act)   # d loss / d (enc + dec)
-                if ctx.needs_input_grad[0]:
-                    enc_grad = torch.empty(B, T, D, dtype=torch.float32, device=dev)
+                enc_grad = torch.empty(B, T, D, dtype=torch.float32, device=dev)
+                dec_grad = torch.empty(B, S1, D, dtype=torch.float32, device=dev)
+                if D % 4 == 0 and D <= 3200:
+                    # both from one pass over gz
+                    nbytes = _lib.lib().frnnt_joiner_input_grads_scratch_bytes(B, T, D)
+                    scratch = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=dev)
+                    _lib.call("frnnt_joiner_input_grads", _lib.ptr(gz), _lib.ptr(ranges),
+                              _lib.ptr(enc_grad), _lib.ptr(dec_grad), _lib.ptr(scratch), B, S1, T, R,
+                              D, _lib.stream_ptr(dev))
+                else:
                     _lib.call("frnnt_sum_over_range", 0, _lib.ptr(gz), _lib.ptr(enc_grad),
                               _lib._c_longlong(B * T), R, D, _lib.stream_ptr(dev))
-                if ctx.needs_input_grad[1]:
-                    dec_grad = torch.empty(B, S1, D, dtype=torch.float32, device=dev)
                     _lib.call("frnnt_prune_gather_backward", 0, _lib.ptr(gz), _lib.ptr(ranges),
                               _lib.ptr(dec_grad), B, S1, T, R, D, _lib.stream_ptr(dev))
+            want_gb = ctx.has_bias and ctx.needs_input_grad[4]
             if ctx.needs_input_grad[3]:
-                gw = _matmul_tn(g2, act.reshape(M, D), N, D, M)
-            if ctx.has_bias and ctx.needs_input_grad[4]:
+                gw = _matmul_tn(g2, act.reshape(M, D), N, D, M, want_colsum=want_gb)
+                if want_gb:
+                    gw, gb = gw
+            elif want_gb:
                 gb = g2.sum(dim=0)
         return enc_grad, dec_grad, None, gw, gb
 

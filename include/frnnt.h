@@ -233,11 +233,19 @@ int frnnt_matmul_nt(const float *a, const float *b, const float *bias, const flo
                     float *d, int M, int N, int K, void *stream);
 
 /* D[M][N] = A[R][M]^T * B[R][N].  The reduction over R is split over
- * frnnt_matmul_tn_splits(M, N, R) CTAs per output tile; `partials` is scratch of
- * splits*M*N floats (may be NULL when splits == 1). */
+ * frnnt_matmul_tn_splits(M, N, R) work items per output tile; `partials` is scratch
+ * of splits*M*N floats (may be NULL when splits == 1). */
 int frnnt_matmul_tn_splits(int M, int N, int R);
 int frnnt_matmul_tn(const float *a, const float *b, float *d, float *partials, int M, int N, int R,
                     void *stream);
+
+/* The same product that, when a_colsum is not NULL, also returns a_colsum[m] =
+ * sum over r of A[r][m], taken from the operand tiles as they pass through the
+ * split pass (for a linear layer: grad_weight and grad_bias from one read of
+ * grad_out).  `scratch` holds frnnt_matmul_tn_scratch_floats(M, N, R) floats. */
+size_t frnnt_matmul_tn_scratch_floats(int M, int N, int R);
+int frnnt_matmul_tn_colsum(const float *a, const float *b, float *d, float *a_colsum, float *scratch,
+                           int M, int N, int R, void *stream);
 
 /* act[B][T][R][D] = tanh(enc[B][T][D] + dec[B][S1][D] gathered at ranges[B][T][R]): the
  * joiner's input, i.e. tanh(am_pruned + lm_pruned) of the reference's usage
@@ -248,6 +256,19 @@ int frnnt_pruned_tanh(int dtype, const void *enc, const void *dec, const int64_t
 /* out[frames][D] = sum over k of gz[frames][R][D] (gradient of the stride-0 am_pruned view). */
 int frnnt_sum_over_range(int dtype, const void *gz, void *out, long long frames, int R, int D,
                          void *stream);
+
+/* Both input gradients of the pruned joiner from one pass over gz [B][T][R][D], the
+ * gradient with respect to enc[b][t] + dec[b][ranges[b][t][k]] (no counterpart in the
+ * reference, which leaves them to autograd through do_rnnt_pruning's expand and gather):
+ *   enc_grad [B][T][D]  = sum over k           (what frnnt_sum_over_range gives),
+ *   dec_grad [B][S1][D] = the scatter-add over ranges (what frnnt_prune_gather_backward gives).
+ * float32, D a multiple of 4, 16-byte aligned pointers; `scratch` holds
+ * frnnt_joiner_input_grads_scratch_bytes(B, T, D) bytes.  Sums are taken in a fixed
+ * order for ranges whose rows move by less than a row per frame (the ones
+ * frnnt_prune_ranges writes); other ranges are handled with atomic adds. */
+size_t frnnt_joiner_input_grads_scratch_bytes(int B, int T, int D);
+int frnnt_joiner_input_grads(const float *gz, const int64_t *ranges, float *enc_grad, float *dec_grad,
+                             void *scratch, int B, int S1, int T, int R, int D, void *stream);
 
 #ifdef __cplusplus
 }
