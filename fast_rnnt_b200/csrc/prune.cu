@@ -43,36 +43,46 @@ __device__ void block_suffix_min(int *arr, int n, int *part) {
   __syncthreads();
 }
 
-// Stage 1: one thread per frame.  s_begin[b][t] (first maximum of the windowed
-// score) is parked in ranges[b][t][0] for stage 2.  RT > 0: the window width is
-// a compile-time constant and the window lives in registers.
+// Stage 1: kArgParts threads per frame, each scanning a contiguous share of the window
+// positions (lane <-> frame, so the loads of a warp are contiguous; warp <-> share);
+// the shares are combined in ascending order with a strict comparison, which keeps
+// the FIRST maximum exactly as a single scan would.  s_begin[b][t] is parked in
+// ranges[b][t][0] for stage 2.  RT > 0: the window width is a compile-time constant
+// and the window lives in registers.
+constexpr int kArgParts = 8;
+
 template <typename real, int RT>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(32 * kArgParts)
 prune_argmax_kernel(const real *__restrict__ px_grad, const real *__restrict__ py_grad,
                     const int64_t *__restrict__ boundary, int64_t *__restrict__ ranges, int S,
                     int T, int T1, int Rdyn) {
+  __shared__ real part_best[kArgParts][32];
+  __shared__ int part_s[kArgParts][32];
   const int b = blockIdx.y;
-  const int t = blockIdx.x * blockDim.x + threadIdx.x;
-  if (t >= T) return;
+  const int lane = threadIdx.x & 31, part = threadIdx.x >> 5;
+  const int t = blockIdx.x * 32 + lane;
   const int R = RT > 0 ? RT : Rdyn;
   const int S1 = S + 1;
   const int n_win = S1 - R + 1;
-  const real *GX = px_grad + (size_t)b * S * T1 + t;
-  const real *GY = py_grad + (size_t)b * S1 * T + t;
   const long long Sb = boundary[4 * b + 2], Tb = boundary[4 * b + 3];
-  int best_s = 0;
-  if ((long long)t < Tb - 1) {
-    real best = 0;
+  const bool scan = t < T && (long long)t < Tb - 1;
+  const int per = (n_win + kArgParts - 1) / kArgParts;
+  const int s_lo = part * per, s_hi = min(n_win, s_lo + per);
+  int best_s = -1;
+  real best = 0;
+  if (scan && s_lo < s_hi) {
+    const real *GX = px_grad + (size_t)b * S * T1 + t;
+    const real *GY = py_grad + (size_t)b * S1 * T + t;
     if (RT > 0) {
       real w[RT > 0 ? RT : 1];
 #pragma unroll
-      for (int k = 0; k < RT; ++k) w[k] = GY[(size_t)k * T];
-      for (int s = 0; s < n_win; ++s) {
+      for (int k = 0; k < RT; ++k) w[k] = GY[(size_t)(s_lo + k) * T];
+      for (int s = s_lo; s < s_hi; ++s) {
         real acc = w[0];
 #pragma unroll
         for (int k = 1; k < RT; ++k) acc = acc + w[k];
         const real score = acc - (s == 0 ? (real)0 : GX[(size_t)(s - 1) * T1]);
-        if (s == 0 || score > best) {
+        if (s == s_lo || score > best) {
           best = score;
           best_s = s;
         }
@@ -81,23 +91,38 @@ prune_argmax_kernel(const real *__restrict__ px_grad, const real *__restrict__ p
         if (s + RT < S1) w[RT - 1] = GY[(size_t)(s + RT) * T];
       }
     } else {
-      for (int s = 0; s < n_win; ++s) {
+      for (int s = s_lo; s < s_hi; ++s) {
         real acc = GY[(size_t)s * T];
         for (int k = 1; k < R; ++k) acc = acc + GY[(size_t)(s + k) * T];
         const real score = acc - (s == 0 ? (real)0 : GX[(size_t)(s - 1) * T1]);
-        if (s == 0 || score > best) {
+        if (s == s_lo || score > best) {
           best = score;
           best_s = s;
         }
+      }
+    }
+  }
+  part_best[part][lane] = best;
+  part_s[part][lane] = best_s;
+  __syncthreads();
+  if (part != 0 || t >= T) return;
+  int out_s;
+  if (scan) {
+    out_s = part_s[0][lane];
+    real top = part_best[0][lane];
+    for (int q = 1; q < kArgParts; ++q) {
+      if (part_s[q][lane] >= 0 && part_best[q][lane] > top) {
+        top = part_best[q][lane];
+        out_s = part_s[q][lane];
       }
     }
   } else {
     long long pad = Sb - R + 1;
     if (pad < 0) pad = 0;
     if (pad > n_win - 1) pad = n_win - 1;  // keeps ranges inside [0, S] for malformed rows
-    best_s = (int)pad;
+    out_s = (int)pad;
   }
-  ranges[((size_t)b * T + t) * R] = best_s;
+  ranges[((size_t)b * T + t) * R] = out_s;
 }
 
 // Stage 2: one CTA per utterance: monotone fix-up (integer scans) and expansion.
@@ -403,9 +428,9 @@ extern "C" int frnnt_prune_ranges(int dtype, const void *px_grad, const void *py
   if (B == 0) return FRNNT_OK;
   FRNNT_REQUIRE(B <= 65535, FRNNT_EUNSUPPORTED, "B too large for the grid");
   cudaStream_t st = (cudaStream_t)stream;
-  dim3 grid1((unsigned)((T + 127) / 128), (unsigned)B);
+  dim3 grid1((unsigned)((T + 31) / 32), (unsigned)B);
 #define PRUNE_ARGMAX(real, RT)                                                                  \
-  FRNNT_KERNEL(prune_argmax_kernel<real, RT><<<grid1, 128, 0, st>>>(                              \
+  FRNNT_KERNEL(prune_argmax_kernel<real, RT><<<grid1, 32 * kArgParts, 0, st>>>(                            \
       (const real *)px_grad, (const real *)py_grad, boundary, ranges, S, T, T1, s_range))
 #define PRUNE_ARGMAX_R(real)                                   \
   switch (s_range) {                                           \

@@ -449,20 +449,37 @@ __global__ void grad_row_sums_kernel(EffGrads<real> eg, real *__restrict__ sgx,
   }
 }
 
-// one thread per (b, t): sums over s
+// sums over s for 32 frames per CTA: lane <-> frame, the 8 warps take every 8th row
+// each (contiguous 128-byte loads, all of a warp's rows independent), then the eight
+// partial sums are added in warp order
+constexpr int kColSumWarps = 8;
 template <typename real>
-__global__ void grad_col_sums_kernel(EffGrads<real> eg, real *__restrict__ cgx,
-                                     real *__restrict__ cgy, int B) {
-  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= B * eg.T) return;
-  const int b = idx / eg.T, t = idx % eg.T;
+__global__ void __launch_bounds__(32 * kColSumWarps)
+grad_col_sums_kernel(EffGrads<real> eg, real *__restrict__ cgx, real *__restrict__ cgy, int B) {
+  __shared__ real px_part[kColSumWarps][32], py_part[kColSumWarps][32];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int b = blockIdx.y, t = blockIdx.x * 32 + lane;
   real ax = 0, ay = 0;
-  for (int s = 0; s <= eg.S; ++s) {
-    ax += eg.gx(b, s, t);
-    ay += eg.gy(b, s, t);
+  if (t < eg.T) {
+#pragma unroll 4
+    for (int s = w; s <= eg.S; s += kColSumWarps) {
+      ax += eg.gx(b, s, t);
+      ay += eg.gy(b, s, t);
+    }
   }
-  cgx[idx] = ax;
-  cgy[idx] = ay;
+  px_part[w][lane] = ax;
+  py_part[w][lane] = ay;
+  __syncthreads();
+  if (w == 0 && t < eg.T) {
+    ax = px_part[0][lane];
+    ay = py_part[0][lane];
+    for (int q = 1; q < kColSumWarps; ++q) {
+      ax += px_part[q][lane];
+      ay += py_part[q][lane];
+    }
+    cgx[(size_t)b * eg.T + t] = ax;
+    cgy[(size_t)b * eg.T + t] = ay;
+  }
 }
 
 // v[i] = alpha * (a[i] + b[i])
@@ -498,13 +515,21 @@ __global__ void am_onehot_kernel(EffGrads<real> eg, const int64_t *__restrict__ 
   if (idx >= B * eg.T) return;
   const int b = idx / eg.T, t = idx % eg.T;
   real *g = am_grad + (size_t)idx * C;
-  for (int s = 0; s < eg.S; ++s) {
-    int y = (int)symbols[(size_t)b * eg.S + s];
-    if (y < 0 || y >= C) y = blank;
-    // fire-and-forget adds: this thread owns row (b, t), and adds issued by one
-    // thread to one address are applied in program order, so the sum is deterministic
-    const real v = eg.gx(b, s, t);
-    if (v != 0) atomicAdd(&g[y], coef * v);
+  // fire-and-forget adds: this thread owns row (b, t), and adds issued by one
+  // thread to one address are applied in program order, so the sum is deterministic.
+  // Eight gradient loads are issued before their adds (the adds would otherwise keep
+  // the next load from starting).
+  for (int s0 = 0; s0 < eg.S; s0 += 8) {
+    real v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) v[u] = s0 + u < eg.S ? eg.gx(b, s0 + u, t) : (real)0;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      if (s0 + u >= eg.S || v[u] == 0) continue;
+      int y = (int)symbols[(size_t)b * eg.S + s0 + u];
+      if (y < 0 || y >= C) y = blank;
+      atomicAdd(&g[y], coef * v[u]);
+    }
   }
   atomicAdd(&g[blank], coef * cgy[idx]);
 }
@@ -678,7 +703,8 @@ static int simple_backward_impl(const void *lm_, const void *am_, const int64_t 
     FRNNT_KERNEL(grad_weight_kernel<real><<<g3, 128, 0, st>>>(eg, norm, lmmax, ammax, rw, (real)cfg.both, Tp));
   FRNNT_KERNEL(grad_row_sums_kernel<real><<<(int)((lm_rows * 32 + 255) / 256), 256, 0, st>>>(eg, sgx, sgy, B));
   if (T > 0)
-    FRNNT_KERNEL(grad_col_sums_kernel<real><<<(int)((am_rows + 127) / 128), 128, 0, st>>>(eg, cgx, cgy, B));
+    FRNNT_KERNEL(grad_col_sums_kernel<real><<<dim3((unsigned)((T + 31) / 32), (unsigned)B), 32 * kColSumWarps, 0,
+                                              st>>>(eg, cgx, cgy, B));
   FRNNT_CUDA(cudaGetLastError());
 
   const real *gl_p = nullptr, *h_p = nullptr, *dp_p = nullptr, *rowdot_p = nullptr;
