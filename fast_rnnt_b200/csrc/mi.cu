@@ -23,10 +23,12 @@
 //     ring (row i, diagonal k), 32 diagonals per chunk, double buffered: global
 //     reads are contiguous row segments, ring reads by the diagonal are
 //     bank-conflict free (pitch 33);
-//   * the forward sweep stores p by anti-diagonal in a scratch ("lattice"),
-//     fully coalesced.  In the backward sweep the helper warps turn it into the
-//     weights d1 (the only exp() of the backward) one chunk ahead of the compute
-//     warps, whose dependent chain per step is shuffle + add + multiply;
+//   * the forward sweep stores, by anti-diagonal in a scratch ("lattice", fully
+//     coalesced), the exponent of the backward weight of every cell,
+//     p[s-1][t+o] + px[s-1][t+o] - p[s][t], which it has in registers anyway.  In
+//     the backward sweep the helper warps turn it into the weights d1 (the only
+//     exp() of the backward) one chunk ahead of the compute warps, whose
+//     dependent chain per step is shuffle + add + multiply;
 //   * gradients leave through the same kind of skewed ring, written back as
 //     contiguous row segments by the helper warps, which also write the exact
 //     zeros outside the boundary box.
@@ -64,11 +66,12 @@ __device__ __forceinline__ MiBox load_box(const int64_t *boundary, int b, int S,
   return box;
 }
 
-// lattice scratch: p by anti-diagonal, [B][S+T+1][pitch]
+// lattice scratch: the weight exponents by anti-diagonal, [B][S+T+1][pitch]
 __host__ __device__ inline int lattice_pitch(int S) { return (S + 1 + 31) & ~31; }
 // followed, per utterance, by two vectors of edge_elems() values: when the lattice has
-// more rows than one CTA holds it is swept in row blocks (one launch per block), and
-// the backward sweep passes the x-gradients that cross a block edge through them
+// more rows than one CTA holds it is swept in row blocks (one launch per block); the
+// forward sweep passes p of a block's last row, the backward sweep the x-gradients of
+// a block's first row, to the next launch through them
 __host__ __device__ inline size_t edge_elems(int S, int T) { return (size_t)(S + T + 1 + 2 * kChunk); }
 __host__ __device__ inline size_t lattice_elems_per_utt(int S, int T) {
   return (size_t)(S + T + 1) * lattice_pitch(S) + 2 * edge_elems(S, T);
@@ -152,8 +155,8 @@ __host__ __device__ constexpr size_t hand_bytes() {
 // -----------------------------------------------------------------------------
 // forward
 // -----------------------------------------------------------------------------
-// BLOCKED: the launch covers lattice rows [row0, row0 + ROWS) only; the row above the
-// block is read back from the lattice scratch, where the previous launch left it.
+// BLOCKED: the launch covers lattice rows [row0, row0 + ROWS) only; p of the row above
+// the block is read back from the edge vector where the previous launch left it.
 template <typename real, int NCW, bool MODIFIED, bool WRITE_P, bool BLOCKED>
 __global__ void __launch_bounds__((NCW + kIoWarps) * 32)
 mi_forward_kernel(const real *__restrict__ px, const real *__restrict__ py,
@@ -186,6 +189,13 @@ mi_forward_kernel(const real *__restrict__ px, const real *__restrict__ py,
   const int lpitch = lattice_pitch(S);
   const bool is_io = warp >= NCW;
   const real ninf = neg_inf<real>();
+  // edge vectors behind the lattice, indexed by lattice diagonal: this block writes one
+  // (p of its last row), the next block reads it
+  real *edge = lattice ? lattice + (size_t)b * lattice_elems_per_utt(S, T) + (size_t)(S + T + 1) * lpitch
+                       : nullptr;
+  const int blk = row0 / ROWS;
+  real *edge_out = edge ? edge + (size_t)(blk & 1) * edge_elems(S, T) : nullptr;
+  const real *edge_in = edge ? edge + (size_t)((blk + 1) & 1) * edge_elems(S, T) : nullptr;
 
   H::init(hand, NCW * H::kSlotsPerWarp, ninf);
   if (threadIdx.x == 0) failed = 0;
@@ -206,11 +216,9 @@ mi_forward_kernel(const real *__restrict__ px, const real *__restrict__ py,
                          vy ? Y + (size_t)(box.s0 + row0 + i) * T + box.t0 + tp - 1 : Y, vy);
     }
     if (BLOCKED && row0 > 0 && warp == NCW) {
-      // cell (row0 - 1, k + o) of the block above, as the previous launch stored it
-      const real *LB = lattice + (size_t)b * lattice_elems_per_utt(S, T);
+      // p of cell (row0 - 1, k + o) of the block above, by lattice diagonal
       const bool v = k + off >= 0 && k + off <= box.tb;
-      async_copy_or_zero(&ringu[slot * kPitch + lane],
-                         v ? LB + (size_t)(row0 + k - 1 + off) * lpitch + row0 - 1 : LB, v);
+      async_copy_or_zero(&ringu[slot * kPitch + lane], v ? edge_in + (row0 + k - 1 + off) : edge_in, v);
     }
     async_copy_wait_all();
   };
@@ -267,7 +275,8 @@ mi_forward_kernel(const real *__restrict__ px, const real *__restrict__ py,
           if (!active) pn = ninf;
           if (active) {
             p_last = pn;
-            if (L != nullptr) *L = pn;
+            if (L != nullptr) *L = a - pn;   // exponent of this cell's backward weight
+            if (BLOCKED && i == ROWS - 1) edge_out[row0 + k] = pn;
             if (WRITE_P) P[(size_t)(box.s0 + row0 + i) * (T + 1) + box.t0 + (k - i)] = pn;
           }
           if (L != nullptr) L += lpitch;
@@ -288,6 +297,7 @@ mi_forward_kernel(const real *__restrict__ px, const real *__restrict__ py,
 // -----------------------------------------------------------------------------
 // backward (from the diagonal-major lattice)
 // -----------------------------------------------------------------------------
+// px is not read: the lattice holds everything the sweep needs.
 // BLOCKED: the launch covers lattice rows [row0, row0 + ROWS) only, blocks run from the
 // last to the first.  The x-gradients that the first row of a block sends to the row
 // above are left, by lattice diagonal, in one of the two edge vectors behind the
@@ -320,7 +330,7 @@ mi_backward_kernel(const real *__restrict__ px, real *__restrict__ lattice,
   const int ib = min(ROWS - 1, box.sb - row0);  // last local row of this launch
   const int nd = ib >= 0 ? ib + box.tb + 1 : 0;
   const int nchunks = (nd + kChunk - 1) / kChunk;
-  const real *X = px + (size_t)b * S * T1;
+  (void)px;
   real *GX = px_grad + (size_t)b * S * T1;
   real *GY = py_grad + (size_t)b * (S + 1) * T;
   const int lpitch = lattice_pitch(S);
@@ -336,34 +346,24 @@ mi_backward_kernel(const real *__restrict__ px, real *__restrict__ lattice,
   H::init(hand, NCW * H::kSlotsPerWarp, (real)0);
   if (threadIdx.x == 0) failed = 0;
 
-  // helper warps: weights d1 of chunk c into ringd[c&1].
-  //   step 1 (lane = diagonal): px row segments, contiguous in memory
-  //   step 2 (lane = row): d1 = exp(p[i-1][k-1+o] + px - p[i][k]), p read by diagonal
+  // helper warps: weights of chunk c.  lane = row, the weight exponents are read by
+  // diagonal (contiguous), all loads of this warp's diagonals in flight before the
+  // first exp
   auto weights_chunk = [&](int c) {
     const int slot = c & 1;
     const int iw = warp - NCW;
-    {
+    if (BLOCKED && iw == 0) {
+      // what cell (row0 + ROWS, t' - o) of the block below sent up to the last row's
+      // cell (row0 + ROWS - 1, t'), t' = k - (ROWS - 1)
       const int k = c * kChunk + lane;
-      for (int i = iw; i <= ib; i += NIO) {
-        const int tp = k - i;
-        const bool v = row0 + i >= 1 && tp >= 1 && tp <= box.tb;
-        async_copy_or_zero(&ringd[(slot * ROWS + i) * kPitch + lane],
-                           v ? X + (size_t)(box.s0 + row0 + i - 1) * T1 + (box.t0 + tp + off) : X, v);
-      }
-      if (BLOCKED && iw == 0) {
-        // what cell (row0 + ROWS, t' - o) of the block below sent up to the last row's
-        // cell (row0 + ROWS - 1, t'), t' = k - (ROWS - 1)
-        const int ts = k - (ROWS - 1) - off;
-        const bool v = block_below && ts >= 0 && ts <= box.tb;
-        async_copy_or_zero(&ringb[slot * kPitch + lane], v ? edge_in + (row0 + k + 1 - off) : edge_in, v);
-      }
+      const int ts = k - (ROWS - 1) - off;
+      const bool v = block_below && ts >= 0 && ts <= box.tb;
+      async_copy_or_zero(&ringb[slot * kPitch + lane], v ? edge_in + (row0 + k + 1 - off) : edge_in, v);
       async_copy_wait_all();
     }
-    bar_sync_named(2, NIO * 32);
-    // all lattice loads of this warp's diagonals are issued before the first exp
     constexpr int NJ = kChunk / NIO;   // diagonals per helper warp
     constexpr int NM = NCW;                 // 32-row blocks
-    real up[NJ][NM], tot[NJ][NM];
+    real dl[NJ][NM];
 #pragma unroll
     for (int jj = 0; jj < NJ; ++jj) {
       const int k = c * kChunk + iw + jj * NIO;
@@ -372,10 +372,12 @@ mi_backward_kernel(const real *__restrict__ px, real *__restrict__ lattice,
         const int i = lane + 32 * m;
         const int tp = k - i;
         const bool v = row0 + i >= 1 && i <= ib && tp >= 1 && tp <= box.tb;
-        up[jj][m] = v ? LT[(size_t)(row0 + k - 1 + off) * lpitch + row0 + i - 1] : (real)0;
-        tot[jj][m] = v ? LT[(size_t)(row0 + k) * lpitch + row0 + i] : (real)0;
+        dl[jj][m] = v ? LT[(size_t)(row0 + k) * lpitch + row0 + i] : (real)0;
       }
     }
+    // the slot still holds gradients that other helper warps are writing out
+    // (drain_chunk of two chunks back): wait for all of them, loads in flight
+    bar_sync_named(2, NIO * 32);
     // weights of every cell of the chunk, special cases resolved here so that the
     // compute warps only multiply: d1 (share of the x-predecessor) into ringd,
     // d2 (share of the y-predecessor) into the slot of ringx they will overwrite
@@ -395,9 +397,8 @@ mi_backward_kernel(const real *__restrict__ px, real *__restrict__ lattice,
           } else if (tp == 0) {    // first column: only an x-predecessor (regular) or none
             d1 = MODIFIED ? 0 : 1;
           } else {
-            real t = tot[jj][m];
-            if (t - t != 0) t = 0;
-            const real w = exp_r(up[jj][m] + ringd[(slot * ROWS + i) * kPitch + j] - t);
+            // an unreachable cell has a non-finite exponent; it gets no gradient
+            const real w = exp_r(dl[jj][m]);
             if (w - w == 0) {
               d1 = w;
               d2 = (real)1 - w;
@@ -513,21 +514,30 @@ mi_backward_kernel(const real *__restrict__ px, real *__restrict__ lattice,
   if (failed && threadIdx.x == 0 && origin_grad != nullptr) origin_grad[b] = (real)NAN;
 }
 
-// lattice in the reference's [B][S+1][T+1] layout -> diagonal-major scratch
+// p in the reference's [B][S+1][T+1] layout -> the weight exponents
+// p[s-1][t+o] + px[s-1][t+o] - p[s][t] in the diagonal-major scratch
 template <typename real>
-__global__ void mi_lattice_from_p_kernel(const real *__restrict__ p,
+__global__ void mi_lattice_from_p_kernel(const real *__restrict__ p, const real *__restrict__ px,
                                          const int64_t *__restrict__ boundary,
-                                         real *__restrict__ lattice, int S, int T) {
+                                         real *__restrict__ lattice, int S, int T, int modified) {
   const int b = blockIdx.y;
   const MiBox box = load_box(boundary, b, S, T);
+  const int T1 = modified ? T : T + 1, off = modified ? -1 : 0;
   const real *P = p + (size_t)b * (S + 1) * (T + 1);
+  const real *X = px + (size_t)b * S * T1;
   const int lpitch = lattice_pitch(S);
   real *LT = lattice + (size_t)b * lattice_elems_per_utt(S, T);
   const int ncell = (box.sb + 1) * (box.tb + 1);
   for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < ncell;
        idx += gridDim.x * blockDim.x) {
     const int i = idx / (box.tb + 1), tp = idx % (box.tb + 1);
-    LT[(size_t)(i + tp) * lpitch + i] = P[(size_t)(box.s0 + i) * (T + 1) + box.t0 + tp];
+    real d = 0;  // first row / first column: the weights are fixed by position
+    if (i >= 1 && tp >= 1) {
+      const size_t up = (size_t)(box.s0 + i - 1);
+      d = P[up * (T + 1) + box.t0 + tp + off] + X[up * T1 + box.t0 + tp + off] -
+          P[(size_t)(box.s0 + i) * (T + 1) + box.t0 + tp];
+    }
+    LT[(size_t)(i + tp) * lpitch + i] = d;
   }
 }
 
@@ -736,7 +746,6 @@ extern "C" int frnnt_mi_backward_from_lattice(int dtype, const void *px, void *l
   if (B == 0) return FRNNT_OK;
   FRNNT_REQUIRE(lattice != nullptr && ans_grad != nullptr, FRNNT_EINVAL,
                 "lattice or ans_grad is NULL");
-  FRNNT_REQUIRE((px != nullptr || S == 0 || (modified && T == 0)), FRNNT_EINVAL, "px is NULL");
   FRNNT_REQUIRE((px_grad != nullptr || S == 0 || (modified && T == 0)) &&
                     (py_grad != nullptr || T == 0),
                 FRNNT_EINVAL, "px_grad or py_grad is NULL");
@@ -756,14 +765,15 @@ extern "C" int frnnt_mi_backward(int dtype, const void *px, const void *py,
   if (rc != FRNNT_OK) return rc;
   if (B == 0) return FRNNT_OK;
   FRNNT_REQUIRE(p != nullptr && lattice != nullptr, FRNNT_EINVAL, "p or lattice is NULL");
+  FRNNT_REQUIRE(px != nullptr || S == 0 || (modified && T == 0), FRNNT_EINVAL, "px is NULL");
   cudaStream_t st = (cudaStream_t)stream;
   dim3 grid((unsigned)min(64, ((S + 1) * (T + 1) + 255) / 256), (unsigned)B);
   if (dtype == FRNNT_F32)
     FRNNT_KERNEL(mi_lattice_from_p_kernel<float><<<grid, 256, 0, st>>>(
-        (const float *)p, boundary, (float *)lattice, S, T));
+        (const float *)p, (const float *)px, boundary, (float *)lattice, S, T, modified));
   else
     FRNNT_KERNEL(mi_lattice_from_p_kernel<double><<<grid, 256, 0, st>>>(
-        (const double *)p, boundary, (double *)lattice, S, T));
+        (const double *)p, (const double *)px, boundary, (double *)lattice, S, T, modified));
   FRNNT_CUDA(cudaGetLastError());
   return frnnt_mi_backward_from_lattice(dtype, px, lattice, boundary, ans_grad, px_grad, py_grad,
                                         origin_grad, B, S, T, modified, stream);

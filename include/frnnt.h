@@ -64,7 +64,8 @@ int frnnt_with_cuda(void);
  * ------------------------------------------------------------------------- */
 
 /* Bytes of the `lattice` scratch of the functions below: the forward sweep
- * stores p there by anti-diagonal ([B][S+T+1][round_up(S+1,32)]), so that it
+ * stores there, by anti-diagonal ([B][S+T+1][round_up(S+1,32)]), the exponent of
+ * every cell's backward weight, p[s-1][t+o] + px[s-1][t+o] - p[s][t], so that it
  * writes it and the backward sweep reads it fully coalesced; two vectors of
  * S+T+65 values per utterance follow (see frnnt_mi_rows_per_block). */
 size_t frnnt_mi_lattice_bytes(int dtype, int B, int S, int T);
@@ -73,9 +74,9 @@ size_t frnnt_mi_lattice_bytes(int dtype, int B, int S, int T);
  * FRNNT_F64.  A taller lattice is swept in blocks of that many rows, one launch
  * per block and direction (the reference tiles in 32x32 blocks and launches once
  * per anti-diagonal of tiles, mutual_information_cuda.cu:680-731).  The row above
- * a block is read back from `lattice`, which frnnt_mi_forward then requires, and
- * the reverse sweep passes the gradients that cross a block edge through the two
- * vectors at the end of `lattice`, which is why it takes it non-const. */
+ * a block and the gradients that cross a block edge travel from launch to launch
+ * through the two vectors at the end of `lattice`, which frnnt_mi_forward then
+ * requires and which is why the reverse sweep takes it non-const. */
 int frnnt_mi_rows_per_block(int dtype);
 
 /* Forward recursion.  Replaces mutual_information_forward(px, py, boundary, p)
@@ -90,8 +91,8 @@ int frnnt_mi_forward(int dtype, const void *px, const void *py, const int64_t *b
                      void *p, void *ans, void *lattice, int B, int S, int T, int modified,
                      void *stream);
 
-/* Reverse sweep from the `lattice` written by frnnt_mi_forward (and the same
- * px): px_grad [B][S][T1] and py_grad [B][S+1][T] are fully written (exact
+/* Reverse sweep from the `lattice` written by frnnt_mi_forward (px is not read
+ * any more and may be NULL): px_grad [B][S][T1] and py_grad [B][S+1][T] are fully written (exact
  * zeros outside the boundary box).  origin_grad (may be NULL) receives the
  * gradient that reaches p[s_begin][t_begin], which equals ans_grad[b] up to
  * rounding when the sweep is right (the reference overwrites ans_grad with it,
