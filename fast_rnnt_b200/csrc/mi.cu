@@ -122,7 +122,8 @@ template <> struct Hand<float> {
     unsigned long long v = *slot;
     int spins = 0;
     while ((unsigned)(v >> 32) != (unsigned)step) {
-      if (++spins > kSpinLimit) {
+      // one wait that runs out ends all later ones at their first miss
+      if (*failed || ++spins > kSpinLimit) {
         *failed = 1;
         break;
       }
