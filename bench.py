@@ -40,7 +40,17 @@ NCU_TRAFFIC_C3 = {
     "lsm_gather_bwd": 600.2e6, "lsm_gather_fwd": 329.3e6, "prune_gather_fwd": 280.0e6,
     "prune_gather_bwd": 345.4e6, "mi_forward": 17.4e6, "mi_backward": 20.9e6,
     "mi_forward_pruned": 17.4e6, "mi_backward_pruned": 20.9e6,
+    "joiner_linear_fwd": 944.4e6, "joiner_linear_grad_input": 944.4e6,
+    "joiner_linear_grad_weight": 681.4e6, "joiner_tanh": 347.2e6, "joiner_input_grads": 403.9e6 + 39.2e6,
 }
+
+
+def measured_tensor_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["bf16_tflops"]), "measured"
+    return 1590.0, "fallback"
 
 
 def measured_peaks():
@@ -275,6 +285,42 @@ def stage_table(fr, wl, dev, flush, hbm_gbs):
                                                        retain_graph=True),
          2 * es * B * T * R * C, None),
     ]
+    # the joiner's kernels (harness around the loss path, but most of a step's time): the
+    # same calls fast_rnnt_b200.pruned_joiner makes, one at a time
+    import importlib
+    from fast_rnnt_b200 import _lib
+    flin = importlib.import_module("fast_rnnt_b200.linear")   # the package exports a function of that name
+    M = B * T * R
+    W = t["joiner_w"].contiguous()
+    Wt = W.t().contiguous()
+    act = torch.empty(B, T, R, D, device=dev)
+    gz = torch.randn(M, D, device=dev)
+    g_logits = torch.randn(M, C, device=dev)
+    enc_g, dec_g = torch.empty(B, T, D, device=dev), torch.empty(B, S + 1, D, device=dev)
+    jscratch = torch.empty(max(1, _lib.lib().frnnt_joiner_input_grads_scratch_bytes(B, T, D)),
+                           dtype=torch.uint8, device=dev)
+    sp = _lib.stream_ptr(dev)
+
+    def j_tanh():
+        _lib.call("frnnt_pruned_tanh", 0, _lib.ptr(t["enc"]), _lib.ptr(t["dec"]), _lib.ptr(ranges),
+                  _lib.ptr(act), B, S + 1, T, R, D, sp)
+
+    j_tanh()
+    act2 = act.reshape(M, D)
+    gemm_flops = 2.0 * M * C * D
+    stages += [
+        ("joiner_tanh", j_tanh, es * M * D + es * B * (T + S + 1) * D + 8 * M, None),
+        ("joiner_linear_fwd", lambda: flin._matmul_nt(act2, W, t["joiner_b"], M, C, D),
+         es * (M * D + M * C + C * D), gemm_flops),
+        ("joiner_linear_grad_input", lambda: flin._matmul_nt(g_logits, Wt, None, M, D, C, tanh_out=act2),
+         es * (M * C + 2 * M * D + C * D), gemm_flops),
+        ("joiner_linear_grad_weight", lambda: flin._matmul_tn(g_logits, act2, C, D, M, want_colsum=True),
+         es * (M * C + M * D + C * D), gemm_flops),
+        ("joiner_input_grads", lambda: _lib.call(
+            "frnnt_joiner_input_grads", _lib.ptr(gz), _lib.ptr(ranges), _lib.ptr(enc_g),
+            _lib.ptr(dec_g), _lib.ptr(jscratch), B, S + 1, T, R, D, sp),
+         es * (M * D + B * (T + S + 1) * D), None),
+    ]
     out = {}
     for name, fn, nbytes, flops in stages:
         ms = time_call(fn, flush)
@@ -489,19 +535,37 @@ def main():
 
     if rank == 0 and not args.no_stages:
         stages, cells = stage_table(fr, wl, dev, flush, hbm_gbs)
-        loss_path_ms = sum(v["ms"] for v in stages.values())
+        loss_path_ms = sum(v["ms"] for k, v in stages.items() if not k.startswith("joiner_"))
         line["stages"] = stages
         line["loss_path"] = {"ms_per_step": round(loss_path_ms, 4),
                              "value": round(batch / (loss_path_ms * 1e-3), 1), "unit": "utt/s",
                              "note": "sum of the library's stages timed alone (no joiner)"}
         mi_ms = stages["mi_forward"]["ms"] + stages["mi_backward"]["ms"]
         line["mi_cells_per_s"] = round(cells / (mi_ms * 1e-3), 1)
-        single = [k for k in stages if not k.startswith("simple_")]
-        top = max(single, key=lambda k: stages[k]["ms"])
-        line["roofline"] = {"kernel": top, "bound": "hbm", "achieved": stages[top]["gbs"],
-                            "peak": hbm_gbs, "unit": "GB/s", "frac": stages[top]["hbm_frac"],
-                            "peak_kind": f"of {peak_kind}",
+        # the dominant kernel of a step: the joiner's forward product on the tensor-core
+        # engine (one kernel; the largest share of the launch list)
+        tf_peak, tf_kind = measured_tensor_peak()
+        top = max((k for k in stages if "tflops" in stages[k] and k.startswith("joiner_")),
+                  key=lambda k: stages[k]["ms"])
+        line["roofline"] = {"kernel": top + " (linear_umma_kernel, 3xTF32 tcgen05)", "bound": "tensor",
+                            "achieved": stages[top]["tflops"], "peak": tf_peak, "unit": "TFLOP/s",
+                            "frac": round(stages[top]["tflops"] / tf_peak, 4),
+                            "peak_kind": f"dense bf16 burst, of {tf_kind}",
+                            "note": "achieved counts the useful 2*M*N*K flops of an fp32-accurate product; "
+                                    "the kernel issues 3x that as tf32 MMAs, and tf32 runs at half the bf16 "
+                                    "rate, so 1/6 of the bf16 peak is the ceiling of this formulation",
+                            "issued_tflops": round(3 * stages[top]["tflops"], 1),
                             "traffic": NCU_TRAFFIC_C3.get(top) if args.workload == "c3" else None}
+        # and the slowest kernel of the loss path proper
+        single = [k for k in stages if not k.startswith(("simple_", "joiner_"))]
+        lp = max(single, key=lambda k: stages[k]["ms"])
+        line["roofline_loss_path"] = {
+            "kernel": lp, "bound": "hbm", "achieved": stages[lp]["gbs"], "peak": hbm_gbs, "unit": "GB/s",
+            "frac": stages[lp]["hbm_frac"], "peak_kind": f"of {peak_kind}",
+            "traffic": NCU_TRAFFIC_C3.get(lp) if args.workload == "c3" else None,
+            "note": ("the mutual-information sweeps are bound by their (S_b+T_b+1)-step dependency "
+                     "chain, not by bytes: the fraction is low by construction"
+                     if lp.startswith("mi_") else "")}
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         torch.set_num_threads(os.cpu_count() or 1)
         sample = min(batch, 16)

@@ -313,6 +313,7 @@ constexpr int kJgFrames = 16;
 constexpr int kJgWindow = 16;
 constexpr int kJgThreads = 128;
 
+template <bool WITH_ENC>
 __global__ void __launch_bounds__(kJgThreads)
 joiner_input_grads_kernel(const float *__restrict__ gz, const int64_t *__restrict__ ranges,
                           float *__restrict__ enc_grad, float *__restrict__ dec_grad,
@@ -353,34 +354,61 @@ joiner_input_grads_kernel(const float *__restrict__ gz, const int64_t *__restric
     window[((size_t)b * nch + ch) * 2 + 1] = rows_used;
   }
   const float4 *G = reinterpret_cast<const float4 *>(gz) + ((size_t)b * T + t0) * R * dvec;
-  float4 *E = reinterpret_cast<float4 *>(enc_grad) + ((size_t)b * T + t0) * dvec;
+  float4 *E = WITH_ENC ? reinterpret_cast<float4 *>(enc_grad) + ((size_t)b * T + t0) * dvec : nullptr;
+  // this thread's columns of one gradient row: into the frame sum and the window row
+  auto consume = [&](const float4 &x, int entry, int v, float4 &e) {
+    e.x += x.x, e.y += x.y, e.z += x.z, e.w += x.w;
+    const long long s = rg[entry];
+    if (s < 0 || s >= S1) return;
+    const int sl = (int)s - s_lo;
+    if (sl < kJgWindow) {
+      float4 a = jg_smem[sl * dvec + v];
+      a.x += x.x, a.y += x.y, a.z += x.z, a.w += x.w;
+      jg_smem[sl * dvec + v] = a;
+    } else {
+      float *dst = dec_grad + ((size_t)b * S1 + s) * D + 4 * v;
+      atomicAdd(dst, x.x), atomicAdd(dst + 1, x.y);
+      atomicAdd(dst + 2, x.z), atomicAdd(dst + 3, x.w);
+    }
+  };
   for (int v = threadIdx.x; v < dvec; v += kJgThreads) {
-    for (int t = 0; t < t1 - t0; ++t) {
-      float4 e = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int k0 = 0; k0 < R; k0 += 8) {
-        float4 x[8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u)
-          if (k0 + u < R) x[u] = G[((size_t)t * R + k0 + u) * dvec + v];
+    const int nt = t1 - t0;
+    if (R <= 8) {
+      // two frames per round: up to 16 independent row loads in flight per thread
+      for (int t = 0; t < nt; t += 2) {
+        float4 x[2][8];
+        const bool two = t + 1 < nt;
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
-          if (k0 + u >= R) break;
-          e.x += x[u].x, e.y += x[u].y, e.z += x[u].z, e.w += x[u].w;
-          const long long s = rg[t * R + k0 + u];
-          if (s < 0 || s >= S1) continue;
-          const int sl = (int)s - s_lo;
-          if (sl < kJgWindow) {
-            float4 a = jg_smem[sl * dvec + v];
-            a.x += x[u].x, a.y += x[u].y, a.z += x[u].z, a.w += x[u].w;
-            jg_smem[sl * dvec + v] = a;
-          } else {
-            float *dst = dec_grad + ((size_t)b * S1 + s) * D + 4 * v;
-            atomicAdd(dst, x[u].x), atomicAdd(dst + 1, x[u].y);
-            atomicAdd(dst + 2, x[u].z), atomicAdd(dst + 3, x[u].w);
+          if (u < R) {
+            x[0][u] = G[((size_t)t * R + u) * dvec + v];
+            if (two) x[1][u] = G[((size_t)(t + 1) * R + u) * dvec + v];
           }
         }
+#pragma unroll
+        for (int f = 0; f < 2; ++f) {
+          if (f == 1 && !two) break;
+          float4 e = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            if (u < R) consume(x[f][u], (t + f) * R + u, v, e);
+          if (WITH_ENC) E[(size_t)(t + f) * dvec + v] = e;
+        }
       }
-      E[(size_t)t * dvec + v] = e;
+    } else {
+      for (int t = 0; t < nt; ++t) {
+        float4 e = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int k0 = 0; k0 < R; k0 += 8) {
+          float4 x[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            if (k0 + u < R) x[u] = G[((size_t)t * R + k0 + u) * dvec + v];
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            if (k0 + u < R) consume(x[u], t * R + k0 + u, v, e);
+        }
+        if (WITH_ENC) E[(size_t)t * dvec + v] = e;
+      }
     }
     float4 *P = reinterpret_cast<float4 *>(partial) + ((size_t)b * nch + ch) * kJgWindow * dvec;
     for (int r = 0; r < rows_used; ++r) P[(size_t)r * dvec + v] = jg_smem[r * dvec + v];
@@ -592,7 +620,7 @@ extern "C" int frnnt_joiner_input_grads(const float *gz, const int64_t *ranges, 
   cudaStream_t st = (cudaStream_t)stream;
   FRNNT_CUDA(cudaMemsetAsync(dec_grad, 0, (size_t)B * S1 * D * sizeof(float), st));
   if (T == 0) return FRNNT_OK;
-  FRNNT_REQUIRE(gz && ranges && enc_grad && scratch, FRNNT_EINVAL, "NULL argument");
+  FRNNT_REQUIRE(gz && ranges && scratch, FRNNT_EINVAL, "NULL argument");
   FRNNT_REQUIRE((uintptr_t)gz % 16 == 0 && (uintptr_t)enc_grad % 16 == 0 && (uintptr_t)dec_grad % 16 == 0 &&
                     (uintptr_t)scratch % 16 == 0,
                 FRNNT_EUNSUPPORTED, "pointers must be 16-byte aligned");
@@ -600,10 +628,17 @@ extern "C" int frnnt_joiner_input_grads(const float *gz, const int64_t *ranges, 
   float *partial = (float *)scratch;
   int *window = (int *)(partial + (size_t)B * nch * kJgWindow * D);
   const size_t smem = (size_t)kJgWindow * D * sizeof(float);
-  FRNNT_CUDA(cudaFuncSetAttribute(joiner_input_grads_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  (int)smem));
-  FRNNT_KERNEL(joiner_input_grads_kernel<<<dim3((unsigned)nch, (unsigned)B), kJgThreads, smem, st>>>(
-      gz, ranges, enc_grad, dec_grad, partial, window, T, R, S1, D));
+  if (enc_grad != nullptr) {
+    FRNNT_CUDA(cudaFuncSetAttribute(joiner_input_grads_kernel<true>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    FRNNT_KERNEL(joiner_input_grads_kernel<true><<<dim3((unsigned)nch, (unsigned)B), kJgThreads, smem, st>>>(
+        gz, ranges, enc_grad, dec_grad, partial, window, T, R, S1, D));
+  } else {
+    FRNNT_CUDA(cudaFuncSetAttribute(joiner_input_grads_kernel<false>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    FRNNT_KERNEL(joiner_input_grads_kernel<false><<<dim3((unsigned)nch, (unsigned)B), kJgThreads, smem, st>>>(
+        gz, ranges, nullptr, dec_grad, partial, window, T, R, S1, D));
+  }
   FRNNT_KERNEL(joiner_dec_reduce_kernel<<<dim3((unsigned)S1, (unsigned)B), kJgThreads, 0, st>>>(
       partial, window, dec_grad, nch, S1, D));
   FRNNT_CUDA(cudaGetLastError());

@@ -280,9 +280,17 @@ class _PruneGather(torch.autograd.Function):
         g = g.contiguous()
         with torch.cuda.device(dev):
             lm_grad = torch.empty(B, S1, D, dtype=g.dtype, device=dev)
-            _lib.call("frnnt_prune_gather_backward", _c_int(_lib.dtype_code(g.dtype)),
-                      _lib.ptr(g), _lib.ptr(ranges), _lib.ptr(lm_grad), B, S1, T, R, D,
-                      _lib.stream_ptr(dev))
+            if g.dtype == torch.float32 and D % 4 == 0 and D <= 3200:
+                # windowed partial sums per chunk of frames (one streaming pass)
+                nbytes = _lib.lib().frnnt_joiner_input_grads_scratch_bytes(B, T, D)
+                scratch = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=dev)
+                _lib.call("frnnt_joiner_input_grads", _lib.ptr(g), _lib.ptr(ranges), None,
+                          _lib.ptr(lm_grad), _lib.ptr(scratch), B, S1, T, R, D,
+                          _lib.stream_ptr(dev))
+            else:
+                _lib.call("frnnt_prune_gather_backward", _c_int(_lib.dtype_code(g.dtype)),
+                          _lib.ptr(g), _lib.ptr(ranges), _lib.ptr(lm_grad), B, S1, T, R, D,
+                          _lib.stream_ptr(dev))
         return lm_grad, None
 
 

@@ -264,7 +264,8 @@ int frnnt_sum_over_range(int dtype, const void *gz, void *out, long long frames,
  *   enc_grad [B][T][D]  = sum over k           (what frnnt_sum_over_range gives),
  *   dec_grad [B][S1][D] = the scatter-add over ranges (what frnnt_prune_gather_backward gives).
  * float32, D a multiple of 4, 16-byte aligned pointers; `scratch` holds
- * frnnt_joiner_input_grads_scratch_bytes(B, T, D) bytes.  Sums are taken in a fixed
+ * frnnt_joiner_input_grads_scratch_bytes(B, T, D) bytes.  enc_grad may be NULL: the
+ * call is then a faster frnnt_prune_gather_backward.  Sums are taken in a fixed
  * order for ranges whose rows move by less than a row per frame (the ones
  * frnnt_prune_ranges writes); other ranges are handled with atomic adds. */
 size_t frnnt_joiner_input_grads_scratch_bytes(int B, int T, int D);
