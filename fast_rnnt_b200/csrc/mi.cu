@@ -114,12 +114,19 @@ template <> struct Hand<float> {
     q[warp * kHandRing + (step & (kHandRing - 1))] =
         ((unsigned long long)(unsigned)step << 32) | (unsigned long long)__float_as_uint(v);
   }
-  // value the neighbour published at `step`; gives up after kSpinLimit polls.
+  // raw slot of `step`, read early: the consumer issues this one step before it needs
+  // the value, so that the shared-memory latency is off its dependent chain
+  __device__ static slot_t peek(volatile slot_t *q, int warp, int step) {
+    return q[warp * kHandRing + (step & (kHandRing - 1))];
+  }
+  // value the neighbour published at `step`, starting from an early read of the slot;
+  // polls (at most kSpinLimit times) only if that read came too early.
   // Called by ALL lanes of the consumer warp (one broadcast read, no divergence);
-  // the neighbour normally runs a step ahead, so the first read succeeds.
-  __device__ static float get(volatile slot_t *q, int warp, int step, volatile int *failed) {
+  // the neighbour normally runs a step ahead, so the early read succeeds.
+  __device__ static float get(volatile slot_t *q, int warp, int step, volatile int *failed,
+                              slot_t early) {
     volatile slot_t *slot = q + warp * kHandRing + (step & (kHandRing - 1));
-    unsigned long long v = *slot;
+    unsigned long long v = early;
     int spins = 0;
     while ((unsigned)(v >> 32) != (unsigned)step) {
       // one wait that runs out ends all later ones at their first miss
@@ -143,7 +150,8 @@ template <> struct Hand<double> {
   __device__ static void put(volatile slot_t *q, int warp, int step, double v) {
     q[warp * 4 + (step & 3)] = v;
   }
-  __device__ static double get(volatile slot_t *q, int warp, int step, volatile int *) {
+  __device__ static slot_t peek(volatile slot_t *, int, int) { return 0; }
+  __device__ static double get(volatile slot_t *q, int warp, int step, volatile int *, slot_t) {
     return q[warp * 4 + (step & 3)];
   }
 };
@@ -237,6 +245,7 @@ mi_forward_kernel(const real *__restrict__ px, const real *__restrict__ py,
   // back, where the fake start would leak into row 1, so it keeps the special case).
   real p_cur = (!MODIFIED && top_row) ? (real)0 : ninf, p_old = ninf;
   real p_last = ninf;                 // the last active value (the answer for row sb)
+  typename H::slot_t early = 0;       // the neighbour's slot for the next step, read ahead
   real *L = lattice ? lattice + (size_t)b * lattice_elems_per_utt(S, T) + (size_t)row0 * lpitch +
                           row0 + i
                     : nullptr;
@@ -264,7 +273,7 @@ mi_forward_kernel(const real *__restrict__ px, const real *__restrict__ py,
           real up = __shfl_up_sync(0xffffffffu, hist, 1);
           if (NCW > 1 && warp > 0) {  // warp-uniform: every lane reads the neighbour's slot
             const int src = k - 1 + off;
-            const real nb = src >= 0 ? H::get(hand, warp - 1, src, &failed) : ninf;
+            const real nb = src >= 0 ? H::get(hand, warp - 1, src, &failed, early) : ninf;
             if (lane == 0) up = nb;
           }
           if (BLOCKED && row0 > 0 && i == 0) up = k + off >= 0 ? ru[j0 + u] : ninf;
@@ -285,6 +294,7 @@ mi_forward_kernel(const real *__restrict__ px, const real *__restrict__ py,
           p_cur = pn;
           if (NCW > 1) {
             if (lane == 31 && warp + 1 < NCW) H::put(hand, warp, k, pn);
+            if (!H::kBarrier && warp > 0) early = H::peek(hand, warp - 1, k + off);  // for step k+1
             if (H::kBarrier) bar_sync_named(1, NCW * 32);
           }
         }
@@ -461,6 +471,7 @@ mi_backward_kernel(const real *__restrict__ px, real *__restrict__ lattice,
   const int k_inject = row0 + i == box.sb ? i + box.tb : -1;
   const int k_top = nchunks * kChunk - 1;          // first diagonal the sweep visits
   const bool has_below = NCW > 1 && warp + 1 < NCW;
+  typename H::slot_t early = 0;       // the neighbour's slot for the next step, read ahead
 
   for (int c = nchunks - 1; c >= 0; --c) {
     if (is_io) {
@@ -486,7 +497,7 @@ mi_backward_kernel(const real *__restrict__ px, real *__restrict__ lattice,
           real below = __shfl_down_sync(0xffffffffu, hist, 1);
           if (has_below) {  // warp-uniform: every lane reads the neighbour's slot
             const int src = k + 1 - off;
-            const real nb = src <= k_top ? H::get(hand, warp + 1, src, &failed) : (real)0;
+            const real nb = src <= k_top ? H::get(hand, warp + 1, src, &failed, early) : (real)0;
             if (lane == 31) below = nb;
           } else if (lane == 31) {
             below = BLOCKED ? rb[j0 + u] : (real)0;
@@ -503,6 +514,7 @@ mi_backward_kernel(const real *__restrict__ px, real *__restrict__ lattice,
           if (BLOCKED && row0 > 0 && i == 0 && k < nd) edge_out[row0 + k] = g1;
           if (NCW > 1) {
             if (lane == 0 && warp > 0) H::put(hand, warp, k, g1);
+            if (!H::kBarrier && has_below) early = H::peek(hand, warp + 1, k - off);  // for step k-1
             if (H::kBarrier) bar_sync_named(1, NCW * 32);
           }
         }
