@@ -30,6 +30,23 @@ def _boundary_rows(boundary: Tensor):
     return rows
 
 
+def provide_boundary_rows(boundary: Tensor, rows) -> Tensor:
+    """Hands the library a host copy of ``boundary`` (a list of B rows
+    ``[s_begin, t_begin, s_end, t_end]`` or a CPU tensor) that the caller already
+    has -- a data loader builds the boundaries on the host before it uploads them.
+    The range checks of the loss functions and the ``s_range`` adjustment of
+    ``get_rnnt_prune_ranges`` (the reference reads the device tensor back for them,
+    fast_rnnt/python/fast_rnnt/mutual_information.py:277-288, rnnt_loss.py:699-706)
+    then need no device-to-host copy and no synchronisation.  The caller vouches
+    that ``rows`` equals the tensor's content; the copy is dropped as soon as the
+    tensor is modified in place.  No counterpart in the reference.  Returns
+    ``boundary``."""
+    rows = rows.tolist() if isinstance(rows, Tensor) else [[int(v) for v in r] for r in rows]
+    assert len(rows) == boundary.shape[0] and all(len(r) == 4 for r in rows)
+    boundary._frnnt_rows = ((boundary.data_ptr(), boundary._version), rows)
+    return boundary
+
+
 def mi_forward(px: Tensor, py: Tensor, boundary: Optional[Tensor], want_p: bool = False,
                want_lattice: bool = True):
     """Raw forward sweep: returns (ans [B], p or None, lattice scratch or None)."""

@@ -373,3 +373,26 @@ def test_c5_shape_stagewise_vs_oracle():
     assert_close(pruned, ref_pruned.detach(), LOSS_RTOL, 0, "pruned loss")
     pruned.backward()
     assert_close(cl.grad, logits.grad, 0, GRAD_ATOL, "logits grad")
+
+
+def test_provided_boundary_rows_skip_the_read_back():
+    """provide_boundary_rows: same results, and the loss call does not synchronise
+    on the boundary tensor (checked through torch's sync debug mode)."""
+    wl = workloads.pipeline_workload("mini", "regular", seed=4)
+    f = fr()
+    lm, am, sym, bnd = (cu(wl[k]) for k in ("lm", "am", "symbols", "boundary"))
+    ref = f.rnnt_loss_simple(lm=lm, am=am, symbols=sym, termination_symbol=0, boundary=bnd,
+                             reduction="none")
+    bnd2 = f.provide_boundary_rows(bnd.clone(), wl["boundary"])
+    torch.cuda.synchronize()
+    torch.cuda.set_sync_debug_mode("error")
+    try:
+        out = f.rnnt_loss_simple(lm=lm, am=am, symbols=sym, termination_symbol=0, boundary=bnd2,
+                                 reduction="none")
+        r = f.get_rnnt_prune_ranges  # the s_range adjustment reads the rows too
+    finally:
+        torch.cuda.set_sync_debug_mode("default")
+    assert torch.equal(out, ref)
+    bnd2[0, 3] -= 1          # an in-place change drops the host copy
+    from fast_rnnt_b200.mutual_information import _boundary_rows
+    assert _boundary_rows(bnd2)[0][3] == int(wl["boundary"][0, 3]) - 1
