@@ -265,6 +265,10 @@ mi_forward_kernel(const real *__restrict__ px, const real *__restrict__ py,
           xv[u] = rx[j0 + u];
           yv[u] = ry[j0 + u];
         }
+        // the results of the eight steps leave for memory after the batch, so that no
+        // store sits between two steps of the dependent chain
+        real dlv[8], pv[8];
+        unsigned act_mask = 0;
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
           const int k = c * kChunk + j0 + u;
@@ -283,13 +287,10 @@ mi_forward_kernel(const real *__restrict__ px, const real *__restrict__ py,
           real pn = log_add(a, bb);
           if (MODIFIED && k == 0 && top_row) pn = 0;
           if (!active) pn = ninf;
-          if (active) {
-            p_last = pn;
-            if (L != nullptr) *L = a - pn;   // exponent of this cell's backward weight
-            if (BLOCKED && i == ROWS - 1) edge_out[row0 + k] = pn;
-            if (WRITE_P) P[(size_t)(box.s0 + row0 + i) * (T + 1) + box.t0 + (k - i)] = pn;
-          }
-          if (L != nullptr) L += lpitch;
+          p_last = active ? pn : p_last;
+          act_mask |= active ? 1u << u : 0u;
+          dlv[u] = a - pn;   // exponent of this cell's backward weight
+          pv[u] = pn;
           p_old = p_cur;
           p_cur = pn;
           if (NCW > 1) {
@@ -297,6 +298,23 @@ mi_forward_kernel(const real *__restrict__ px, const real *__restrict__ py,
             if (!H::kBarrier && warp > 0) early = H::peek(hand, warp - 1, k + off);  // for step k+1
             if (H::kBarrier) bar_sync_named(1, NCW * 32);
           }
+        }
+        if (L != nullptr) {
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            if (act_mask >> u & 1u) L[(size_t)u * lpitch] = dlv[u];
+          L += (size_t)8 * lpitch;
+        }
+        if (BLOCKED && i == ROWS - 1) {
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            if (act_mask >> u & 1u) edge_out[row0 + c * kChunk + j0 + u] = pv[u];
+        }
+        if (WRITE_P) {
+          real *prow = P + (size_t)(box.s0 + row0 + i) * (T + 1) + box.t0 + (c * kChunk + j0 - i);
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            if (act_mask >> u & 1u) prow[u] = pv[u];
         }
       }
     }
