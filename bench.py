@@ -332,6 +332,35 @@ def stage_table(fr, wl, dev, flush, hbm_gbs):
     return out, cells_box
 
 
+def mi_c2_table(dev, flush):
+    """The standalone recursion on the configuration the metric names for it (B=32,
+    S=128, T=512, log-probs uniform on (-6, 0)): lattice cells per second, forward alone
+    and forward + backward (what return_grad costs), without and with boundaries."""
+    from fast_rnnt_b200 import mutual_information as mi
+    out = {}
+    for tag, with_boundary in (("full", False), ("bounded", True)):
+        px, py, bnd = workloads.config_c2(with_boundary)
+        B, S, _ = px.shape
+        T = py.shape[2]
+        px, py = px.to(dev), py.to(dev)
+        cells = workloads.lattice_cells(bnd, B, S, T) if bnd is not None else B * (S + 1) * (T + 1)
+        bnd = bnd.to(dev) if bnd is not None else None
+        ones = torch.ones(B, device=dev)
+
+        def fwd():
+            return mi.mi_forward(px, py, bnd)
+
+        def fwd_bwd():
+            _, _, lat = mi.mi_forward(px, py, bnd)
+            mi.mi_backward_from_lattice(px, lat, bnd, ones, py.shape)
+
+        f_ms, fb_ms = time_call(fwd, flush), time_call(fwd_bwd, flush)
+        out[tag] = {"cells": int(cells), "fwd_ms": round(f_ms, 4), "fwd_bwd_ms": round(fb_ms, 4),
+                    "cells_per_s_fwd": round(cells / (f_ms * 1e-3), 1),
+                    "cells_per_s_fwd_bwd": round(cells / (fb_ms * 1e-3), 1)}
+    return out
+
+
 # ------------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
@@ -554,6 +583,7 @@ def main():
                              "note": "sum of the library's stages timed alone (no joiner)"}
         mi_ms = stages["mi_forward"]["ms"] + stages["mi_backward"]["ms"]
         line["mi_cells_per_s"] = round(cells / (mi_ms * 1e-3), 1)
+        line["mi_c2"] = mi_c2_table(dev, flush)
         # the dominant kernel of a step: the joiner's forward product on the tensor-core
         # engine (one kernel; the largest share of the launch list)
         tf_peak, tf_kind = measured_tensor_peak()
