@@ -320,7 +320,12 @@ static int launch_contraction(const Prob &prob, int M, int N, int B, cudaStream_
 // ---- lattice assembly -------------------------------------------------------------
 struct SmoothCfg {
   int smoothed;
-  double both, ls, as;  // 1-l-a, lm-only scale, am-only scale (zeros already replaced by 1e-20)
+  // the am-only branch is left out: am_only_scale == 0.  The reference multiplies the
+  // branch by 1e-20 in that case (rnnt_loss.py:1346-1351), which changes an fp32 / fp64
+  // px or py only if that value is exactly 0; its three extra passes (unigram, am-only
+  // normalizer) are not worth that
+  int am_only_off;
+  double both, ls, as;  // 1-l-a, lm-only scale, am-only scale (zero lm scale replaced by 1e-20)
 };
 
 template <typename real>
@@ -350,9 +355,9 @@ __global__ void assemble_kernel(const real *__restrict__ lm, const real *__restr
     real v = py_am + py_lm - norm[((size_t)b * S1 + ss) * T + t];
     if (cfg.smoothed) {
       const real lnorm = log_r(lmsum[(size_t)b * S1 + ss]) + lmmax[(size_t)b * S1 + ss];
-      const real v_am = py_am + loguni[blank] - amonly[(size_t)b * T + t];
       const real v_lm = py_lm - lnorm;
-      v = v * both + v_lm * ls + v_am * as;
+      v = v * both + v_lm * ls;
+      if (!cfg.am_only_off) v += (py_am + loguni[blank] - amonly[(size_t)b * T + t]) * as;
     }
     return v;
   };
@@ -371,10 +376,13 @@ __global__ void assemble_kernel(const real *__restrict__ lm, const real *__restr
       v = px_am + px_lm;  // the -inf column of the regular type
     }
     if (cfg.smoothed) {
-      real v_am = px_am + loguni[y];
-      if (t < T) v_am -= amonly[(size_t)b * T + t];
       const real v_lm = px_lm - lm_only_norm;
-      v = v * both + v_lm * ls + v_am * as;
+      v = v * both + v_lm * ls;
+      if (!cfg.am_only_off) {
+        real v_am = px_am + loguni[y];
+        if (t < T) v_am -= amonly[(size_t)b * T + t];
+        v += v_am * as;
+      }
     }
     if (rnnt_type == FRNNT_REGULAR) {
       if (boundary != nullptr && (long long)t == (long long)boundary[4 * b + 3]) v = ninf;
@@ -612,7 +620,8 @@ static SmoothCfg make_cfg(int smoothed, double lm_only_scale, double am_only_sca
   cfg.both = 1.0 - lm_only_scale - am_only_scale;
   // exact zeros would turn -inf * 0 into nan (rnnt_loss.py:1346-1351)
   cfg.ls = lm_only_scale == 0.0 ? 1.0e-20 : lm_only_scale;
-  cfg.as = am_only_scale == 0.0 ? 1.0e-20 : am_only_scale;
+  cfg.am_only_off = smoothed && am_only_scale == 0.0;
+  cfg.as = am_only_scale;
   if (!smoothed) {
     cfg.both = 1.0;
     cfg.ls = 0.0;
@@ -647,7 +656,7 @@ static int simple_forward_impl(const void *lm_, const void *am_, const int64_t *
   // the am row sums land in the (not yet used) am-only buffer and are overwritten below
   FRNNT_KERNEL(row_stats_kernel<real><<<warps_grid(am_rows), 256, 0, st>>>(am, ammax, amonly, am_rows, C));
   FRNNT_CUDA(cudaGetLastError());
-  if (cfg.smoothed) {
+  if (cfg.smoothed && !cfg.am_only_off) {
     const int nchunk = (int)((lm_rows + kColChunkRows - 1) / kColChunkRows);
     dim3 g1((unsigned)((C + 127) / 128), (unsigned)nchunk);
     FRNNT_KERNEL(column_partial_kernel<real, 0><<<g1, 128, 0, st>>>(lm, lmmax, lmsum, nullptr, partial, lm_rows, C));
