@@ -35,13 +35,14 @@ L2_FLUSH_BYTES = 512 << 20
 # DRAM traffic per launch measured once with ncu (dram__bytes_read.sum +
 # dram__bytes_write.sum, profiles/); keyed by stage name, bytes for workload c3.
 NCU_TRAFFIC_C3 = {
-    # profiles/kernels_c3_ncu_full.txt (the two prune_gather stages: an earlier capture of the
-    # same kernels; the joiner path of the step does not launch them)
-    "lsm_gather_bwd": 600.2e6, "lsm_gather_fwd": 329.3e6, "prune_gather_fwd": 280.0e6,
-    "prune_gather_bwd": 345.4e6, "mi_forward": 17.4e6, "mi_backward": 20.9e6,
-    "mi_forward_pruned": 17.4e6, "mi_backward_pruned": 20.9e6,
-    "joiner_linear_fwd": 944.4e6, "joiner_linear_grad_input": 944.4e6,
-    "joiner_linear_grad_weight": 681.4e6, "joiner_tanh": 347.2e6, "joiner_input_grads": 403.9e6 + 39.2e6,
+    # dram__bytes_read.sum + dram__bytes_write.sum per launch, profiles/kernels_c3_ncu_full.txt
+    # (the two prune_gather stages and the grad-input product: earlier captures of the same
+    # kernels; a capture shows the first launch of every kernel of a step)
+    "lsm_gather_bwd": 600.9e6, "lsm_gather_fwd": 327.1e6, "prune_gather_fwd": 280.0e6,
+    "prune_gather_bwd": 408.0e6 + 39.2e6, "mi_forward": 17.4e6, "mi_backward": 12.2e6,
+    "mi_forward_pruned": 17.4e6, "mi_backward_pruned": 12.2e6,
+    "joiner_linear_fwd": 600.2e6, "joiner_linear_grad_input": 944.4e6,
+    "joiner_linear_grad_weight": 651.2e6, "joiner_tanh": 347.5e6, "joiner_input_grads": 408.0e6 + 39.2e6,
 }
 
 
