@@ -99,6 +99,18 @@ __device__ __forceinline__ void async_copy_wait_all() {
   asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
 }
 
+// The chunk barrier releases all compute warps at the same instant, so a consumer warp
+// would ask for its neighbour's value of the previous step just before it becomes
+// visible -- at every step, since both run at the same pace -- and pay a poll each time.
+// Starting each warp a little after the one it depends on keeps the producer ahead.
+constexpr int kStaggerCycles = 96;
+__device__ __forceinline__ void stagger(int lag) {
+  if (lag <= 0) return;
+  const long long t0 = clock64();
+  while (clock64() - t0 < (long long)lag * kStaggerCycles) {
+  }
+}
+
 // ---- hand-off between neighbouring warps --------------------------------------
 // float: tagged 64-bit slots, polled.  double: plain slots + a barrier per step.
 template <typename real> struct Hand;
@@ -254,6 +266,7 @@ mi_forward_kernel(const real *__restrict__ px, const real *__restrict__ py,
     if (is_io) {
       if (c + 1 < nchunks) load_chunk(c + 1);
     } else {
+      if (!H::kBarrier && NCW > 1) stagger(warp);
       const real *rx = ringx + ((c & 1) * ROWS + i) * kPitch;
       const real *ry = ringy + ((c & 1) * ROWS + i) * kPitch;
       const real *ru = ringu + (c & 1) * kPitch;
@@ -496,6 +509,7 @@ mi_backward_kernel(const real *__restrict__ px, real *__restrict__ lattice,
       if (c + 1 < nchunks) drain_chunk(c + 1);
       if (c >= 1) weights_chunk(c - 1);
     } else {
+      if (!H::kBarrier && NCW > 1) stagger(NCW - 1 - warp);
       const real *rd = ringd + ((c & 1) * ROWS + i) * kPitch;
       real *rx = ringx + ((c & 1) * ROWS + i) * kPitch;
       real *ry = ringy + ((c & 1) * ROWS + i) * kPitch;

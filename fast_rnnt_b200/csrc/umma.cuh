@@ -229,6 +229,10 @@ __device__ __forceinline__ float round_tf32(float x) {
   // cvt.rna.tf32.f32 does -- with two full-rate integer instructions
   return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
 }
+// what the tensor core makes of an fp32 word it reads as tf32: the low 13 bits dropped
+__device__ __forceinline__ float trunc_tf32(float x) {
+  return __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
+}
 __device__ __forceinline__ void split_tf32(float x, float &hi, float &lo) {
   hi = round_tf32(x);
   lo = round_tf32(x - hi);

@@ -13,10 +13,11 @@
 //              (K-major: swizzle 128B; operands that are contiguous along M/N:
 //              swizzle 128B with 32-byte atoms), completion on an mbarrier;
 //              4-stage ring.  Out-of-range rows / columns arrive as zeros.
-//   warps 2-9: split every landed value x into hi = tf32(x) and lo = tf32(x - hi),
-//              both rounded to nearest.  B is split in shared memory (hi in place,
-//              lo in a second buffer; an element-wise pass that does not care
-//              about the tile layout).  A goes to TENSOR MEMORY: thread <-> row
+//   warps 2-9: split every landed value x into hi + lo in tf32.  A: hi = tf32(x) and
+//              lo = tf32(x - hi), both rounded to nearest.  B: hi is the landed word
+//              itself (the tensor core drops its low 13 bits), lo = tf32(x - trunc(x))
+//              goes to a second buffer (an element-wise pass that does not care about
+//              the tile layout).  A goes to TENSOR MEMORY: thread <-> row
 //              of the tile, tcgen05.st of its 16 k values (hi and lo), a ring of
 //              two K slices.  The tensor core then reads only B from shared
 //              memory, whose bandwidth is what bounds a 3xTF32 product whose
@@ -288,7 +289,12 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             av[4 * j] = v.x, av[4 * j + 1] = v.y, av[4 * j + 2] = v.z, av[4 * j + 3] = v.w;
           }
         }
-        // B: split in place (hi) and into the second buffer (lo); the layout does not matter
+        // B: hi and lo; an element-wise pass, the tile layout does not matter.  A plain B
+        // stays where it landed: the tensor core reads the raw fp32 word as tf32, i.e. its
+        // hi is the TRUNCATED value, and only lo = tf32(x - trunc(x)) is written.  The
+        // one-sided remainder is harmless because A is split with rounding: the neglected
+        // term lo_a * lo_b then has no preferred sign.  An exponentiated B is new data
+        // and is written in full.
 #pragma unroll
         for (int q = 0; q < kChunksPerThread; ++q) {
           if (Ext::kExpB) {
@@ -296,11 +302,18 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             x[q].y = k_ok ? expf(x[q].y - sh) : 0.f;
             x[q].z = k_ok ? expf(x[q].z - sh) : 0.f;
             x[q].w = k_ok ? expf(x[q].w - sh) : 0.f;
+            float4 h, l;
+            split_tf32(x[q], h, l);
+            braw[st_tid + q * 32 * kLinWorkers] = h;
+            blo[st_tid + q * 32 * kLinWorkers] = l;
+          } else {
+            float4 l;
+            l.x = round_tf32(x[q].x - trunc_tf32(x[q].x));
+            l.y = round_tf32(x[q].y - trunc_tf32(x[q].y));
+            l.z = round_tf32(x[q].z - trunc_tf32(x[q].z));
+            l.w = round_tf32(x[q].w - trunc_tf32(x[q].w));
+            blo[st_tid + q * 32 * kLinWorkers] = l;
           }
-          float4 h, l;
-          split_tf32(x[q], h, l);
-          braw[st_tid + q * 32 * kLinWorkers] = h;
-          blo[st_tid + q * 32 * kLinWorkers] = l;
         }
         // A: this thread's row, 16 of the 32 k values, hi and lo into tensor memory
         float hi[16], lo[16];
