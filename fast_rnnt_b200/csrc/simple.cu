@@ -99,6 +99,34 @@ __global__ void row_stats_kernel(const real *__restrict__ x, real *__restrict__ 
   }
 }
 
+// one warp per row: the maximum alone (all that is needed of the am rows), 16-byte loads
+// when the rows allow them
+template <typename real>
+__global__ void row_max_kernel(const real *__restrict__ x, real *__restrict__ rmax, long long rows,
+                               int C, int vec_ok) {
+  constexpr int VW = 16 / sizeof(real);
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long row = warp0; row < rows; row += nwarps) {
+    const real *src = x + row * (long long)C;
+    real m = neg_inf<real>();
+    if (vec_ok) {
+      const float4 *v4 = reinterpret_cast<const float4 *>(src);
+      for (int c = lane; c < C / VW; c += 32) {
+        const float4 q = v4[c];
+        const real *e = reinterpret_cast<const real *>(&q);
+#pragma unroll
+        for (int i = 0; i < VW; ++i) m = max(m, e[i]);
+      }
+    } else {
+      for (int c = lane; c < C; c += 32) m = max(m, src[c]);
+    }
+    m = warp_max(m);
+    if (lane == 0) rmax[row] = m;
+  }
+}
+
 // partial[chunk][c] = sum over the chunk's rows of f(row, c); one thread per column
 //   MODE 0: softmax(lm row)[c]                      (unigram)
 //   MODE 1: h[row] * e^{am[row,c]-ammax[row]} / Z[row]   (d unigram via the am-only normalizer)
@@ -653,8 +681,11 @@ static int simple_forward_impl(const void *lm_, const void *am_, const int64_t *
   const long long lm_rows = (long long)B * S1, am_rows = (long long)B * T;
 
   FRNNT_KERNEL(row_stats_kernel<real><<<warps_grid(lm_rows), 256, 0, st>>>(lm, lmmax, lmsum, lm_rows, C));
-  // the am row sums land in the (not yet used) am-only buffer and are overwritten below
-  FRNNT_KERNEL(row_stats_kernel<real><<<warps_grid(am_rows), 256, 0, st>>>(am, ammax, amonly, am_rows, C));
+  {
+    constexpr int VW = 16 / sizeof(real);
+    const int vec_ok = C % VW == 0 && (uintptr_t)am % 16 == 0;
+    FRNNT_KERNEL(row_max_kernel<real><<<warps_grid(am_rows), 256, 0, st>>>(am, ammax, am_rows, C, vec_ok));
+  }
   FRNNT_CUDA(cudaGetLastError());
   if (cfg.smoothed && !cfg.am_only_off) {
     const int nchunk = (int)((lm_rows + kColChunkRows - 1) / kColChunkRows);
