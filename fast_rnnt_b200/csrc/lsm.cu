@@ -87,8 +87,10 @@ __device__ __forceinline__ real group_reduce(real v, bool is_max, real *scratch,
 }
 
 // Stage 1.  rows = B*T*R, one GROUP of threads per row.
-template <typename real, int VW, int GROUP>
-__global__ void __launch_bounds__(kRowCta)
+// CACHE: vectors a thread keeps of its row (4 when the row fits: fewer registers,
+// more rows in flight per SM)
+template <typename real, int VW, int GROUP, int CACHE>
+__global__ void __launch_bounds__(kRowCta, CACHE == 4 ? 5 : 1)
 lsm_rows_forward_kernel(const real *__restrict__ logits, const int64_t *__restrict__ symbols,
                         const int64_t *__restrict__ ranges, real *__restrict__ lse,
                         real *__restrict__ pxb, real *__restrict__ pyb, long long rows, int T,
@@ -98,18 +100,18 @@ lsm_rows_forward_kernel(const real *__restrict__ logits, const int64_t *__restri
   __shared__ real scratch[kRowCta / 32];
   const int gid = threadIdx.x / GROUP, lig = threadIdx.x % GROUP;
   const int nvec = C / VW;
-  const bool cached = nvec <= GROUP * kRowCache;
+  const bool cached = nvec <= GROUP * CACHE;
   const real ninf = neg_inf<real>();
 
   for (long long row0 = (long long)blockIdx.x * GPC; row0 < rows; row0 += (long long)gridDim.x * GPC) {
     const long long row = row0 + gid;
     const bool valid = row < rows;
     const vec *src = reinterpret_cast<const vec *>(logits + (valid ? row : 0) * (long long)C);
-    vec reg[kRowCache];
+    vec reg[CACHE];
     real m = ninf;
     if (cached) {
 #pragma unroll
-      for (int j = 0; j < kRowCache; ++j) {
+      for (int j = 0; j < CACHE; ++j) {
         const int v = lig + j * GROUP;
         if (valid && v < nvec) {
           reg[j] = src[v];
@@ -130,7 +132,7 @@ lsm_rows_forward_kernel(const real *__restrict__ logits, const int64_t *__restri
     real sum = 0;
     if (cached) {
 #pragma unroll
-      for (int j = 0; j < kRowCache; ++j) {
+      for (int j = 0; j < CACHE; ++j) {
         const int v = lig + j * GROUP;
         if (valid && v < nvec) {
 #pragma unroll
@@ -262,13 +264,22 @@ static int lsm_forward_impl(const void *logits, const int64_t *symbols, const in
   const int nvec = vec_ok ? C / VWMAX : C;
   int group = 32;
   while (group < 256 && nvec > group * kRowCache) group *= 2;
+  const bool small_cache = nvec <= group * 4;
   const int gpc = kRowCta / group;
   long long want = (rows + gpc - 1) / gpc;
   const int grid = (int)(want < 148LL * 64 ? (want > 0 ? want : 1) : 148LL * 64);
-#define LSM_FWD(VW, G)                                                                         \
-  FRNNT_KERNEL(lsm_rows_forward_kernel<real, VW, G><<<grid, kRowCta, 0, st>>>(                                \
+#define LSM_FWD1(VW, G, CA)                                                                    \
+  FRNNT_KERNEL(lsm_rows_forward_kernel<real, VW, G, CA><<<grid, kRowCta, 0, st>>>(                            \
       (const real *)logits, symbols, ranges, (real *)lse, (real *)pxb, (real *)pyb, rows, T, R, \
       S, C, blank))
+#define LSM_FWD(VW, G)                  \
+  do {                                  \
+    if (small_cache) {                  \
+      LSM_FWD1(VW, G, 4);               \
+    } else {                            \
+      LSM_FWD1(VW, G, kRowCache);       \
+    }                                   \
+  } while (0)
   if (rows > 0) {
     if (vec_ok) {
       if (group == 32) LSM_FWD(VWMAX, 32);
@@ -284,6 +295,7 @@ static int lsm_forward_impl(const void *logits, const int64_t *symbols, const in
     FRNNT_CUDA(cudaGetLastError());
   }
 #undef LSM_FWD
+#undef LSM_FWD1
   if (px != nullptr && py != nullptr && B > 0) {
     dim3 grid2((unsigned)((T + 1 + 127) / 128), (unsigned)(S + 1), (unsigned)B);
     FRNNT_KERNEL(band_to_lattice_kernel<real><<<grid2, 128, 0, st>>>((const real *)pxb, (const real *)pyb,
