@@ -94,6 +94,10 @@ __device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const CUtensorMap
       : "memory");
 }
 
+__device__ __forceinline__ void prefetch_l2(const void *p) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
+
 struct LinShape {
   int M, N, K;         // K = reduction length
   int k_per_split;     // multiple of kLinBK (the whole of K when batched)
@@ -357,6 +361,17 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     for (int w = blockIdx.x; w < n_items; w += gridDim.x) {
       const LinTile t = lin_tile<BATCHED>(p, w);
       const int NG = (t.KB + kLinGroup - 1) / kLinGroup;
+      const int m = t.m0 + 32 * quarter + lane;
+      const bool row_ok = m < p.M;
+      float *out = row_ok ? ext.out_row(t.z, m) : nullptr;
+      const float *pre = row_ok ? ext.pre_row(t.z, m) : nullptr;
+      // the values the epilogue combines with come from DRAM: ask for them now, while the
+      // tile is still being computed (these warps have nothing else to do yet)
+      if (pre != nullptr) {
+#pragma unroll
+        for (int c = 0; c < kLinTile; c += 32)
+          if (t.n0 + c < p.N) prefetch_l2(pre + t.n0 + c);
+      }
       for (int g = 0; g < NG && ok; ++g, ++gg) {
         if (!mbar_wait(&bar_grp[gg & 1], (uint32_t)((gg >> 1) & 1))) {
           ok = false;
@@ -384,10 +399,6 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       ok = __all_sync(0xffffffffu, ok) && !*vfailed;
       if (!ok) *vfailed = 1;
       tc_fence_after_sync();
-      const int m = t.m0 + 32 * quarter + lane;
-      const bool row_ok = m < p.M;
-      float *out = row_ok ? ext.out_row(t.z, m) : nullptr;
-      const float *pre = row_ok ? ext.pre_row(t.z, m) : nullptr;
       // 32 columns per round: the loads of the values the epilogue combines with are
       // issued before the first accumulator read, so their latency is paid four times
       // per tile, not once per 16 columns
