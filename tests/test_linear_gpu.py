@@ -58,7 +58,10 @@ def test_linear_rejects_unaligned_rows():
 
 @pytest.mark.parametrize("shape,monotone", [((3, 19, 9, 4, 64, 36), True),
                                             ((2, 70, 33, 5, 128, 36), True),
-                                            ((2, 37, 60, 5, 64, 20), False)])
+                                            ((2, 37, 60, 5, 64, 20), False),
+                                            # more rows per frame than the kernels keep in registers,
+                                            # the narrowest rows TMA accepts
+                                            ((2, 21, 14, 9, 8, 12), True)])
 def test_pruned_joiner_matches_the_torch_composition(shape, monotone):
     """pruned_joiner == linear(tanh(am_pruned + lm_pruned)) of the reference's usage,
     values and all five gradients."""
