@@ -90,7 +90,7 @@ __device__ __forceinline__ real group_reduce(real v, bool is_max, real *scratch,
 // CACHE: vectors a thread keeps of its row (4 when the row fits: fewer registers,
 // more rows in flight per SM)
 template <typename real, int VW, int GROUP, int CACHE>
-__global__ void __launch_bounds__(kRowCta, CACHE == 4 ? 5 : 1)
+__global__ void __launch_bounds__(kRowCta, CACHE == 4 ? 5 : 4)
 lsm_rows_forward_kernel(const real *__restrict__ logits, const int64_t *__restrict__ symbols,
                         const int64_t *__restrict__ ranges, real *__restrict__ lse,
                         real *__restrict__ pxb, real *__restrict__ pyb, long long rows, int T,
