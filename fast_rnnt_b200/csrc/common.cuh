@@ -34,6 +34,10 @@ void set_error(const char *fmt, ...);
 void count_launch();
 #define FRNNT_KERNEL(...) (::frnnt::count_launch(), __VA_ARGS__)
 
+// multiprocessors of the current device (queried once per device; 148 on a B200);
+// a fallback of 148 if the query fails, since grid sizes are only a tuning matter
+int sm_count();
+
 inline int check_dtype(int dtype) { return dtype == FRNNT_F32 || dtype == FRNNT_F64; }
 inline size_t dtype_size(int dtype) { return dtype == FRNNT_F64 ? 8 : 4; }
 

@@ -87,16 +87,17 @@ extern "C" int frnnt_matmul_nt(const float *a, const float *b, const float *bias
 
 extern "C" int frnnt_matmul_tn_splits(int M, int N, int R) {
   if (M <= 0 || N <= 0 || R <= 0) return 1;
-  // The persistent CTAs (one per SM, 148 on a B200) take the tiles x splits work items
-  // round-robin, so the time is ceil(items / 148) item lengths, an item being 1 / splits
+  // The persistent CTAs (one per SM) take the tiles x splits work items
+  // round-robin, so the time is ceil(items / SMs) item lengths, an item being 1 / splits
   // of the reduction: pick the split count that minimises it, with a small price per
   // split for the partial sums, and at least 8 K slices per item.
   const long long tiles = (long long)((M + kLinTile - 1) / kLinTile) * ((N + kLinTile - 1) / kLinTile);
   const int max_splits = (R + 8 * kLinBK - 1) / (8 * kLinBK);
+  const long long sms = sm_count();
   int best = 1;
   double best_cost = 1e30;
   for (int sp = 1; sp <= 64 && sp <= max_splits; ++sp) {
-    const long long waves = (tiles * sp + 147) / 148;
+    const long long waves = (tiles * sp + sms - 1) / sms;
     const double cost = (double)waves / sp + 0.002 * sp;
     if (cost < best_cost - 1e-12) {
       best_cost = cost;

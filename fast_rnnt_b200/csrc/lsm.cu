@@ -267,7 +267,7 @@ static int lsm_forward_impl(const void *logits, const int64_t *symbols, const in
   const bool small_cache = nvec <= group * 4;
   const int gpc = kRowCta / group;
   long long want = (rows + gpc - 1) / gpc;
-  const int grid = (int)(want < 148LL * 64 ? (want > 0 ? want : 1) : 148LL * 64);
+  const int grid = (int)(want < (long long)sm_count() * 64 ? (want > 0 ? want : 1) : (long long)sm_count() * 64);
 #define LSM_FWD1(VW, G, CA)                                                                    \
   FRNNT_KERNEL(lsm_rows_forward_kernel<real, VW, G, CA><<<grid, kRowCta, 0, st>>>(                            \
       (const real *)logits, symbols, ranges, (real *)lse, (real *)pxb, (real *)pyb, rows, T, R, \
@@ -317,7 +317,7 @@ static int lsm_backward_impl(const void *logits, const int64_t *symbols, const i
   const bool vec_ok = (C % VWMAX == 0) && ((uintptr_t)logits % 16 == 0) &&
                       ((uintptr_t)g_logits % 16 == 0);
   long long want = (rows + 7) / 8;
-  const int grid = (int)(want < 148LL * 64 ? want : 148LL * 64);
+  const int grid = (int)(want < (long long)sm_count() * 64 ? want : (long long)sm_count() * 64);
   if (vec_ok)
     FRNNT_KERNEL(lsm_rows_backward_kernel<real, VWMAX><<<grid, kRowCta, 0, st>>>(
         (const real *)logits, symbols, ranges, boundary, (const real *)lse, (const real *)g_px,

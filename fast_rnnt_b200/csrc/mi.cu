@@ -334,6 +334,10 @@ mi_forward_kernel(const real *__restrict__ px, const real *__restrict__ py,
     __syncthreads();
   }
   if (!is_io && row0 + i == box.sb) ans[b] = failed ? (real)NAN : p_last;
+  // a hand-off that ran out in a block that does not hold the last row: NaN in the row
+  // it passes down, so that every later block and finally ans[b] turn NaN as well
+  if (BLOCKED && failed && edge_out != nullptr)
+    for (int k = threadIdx.x; k < nd; k += blockDim.x) edge_out[row0 + k] = (real)NAN;
 }
 
 // -----------------------------------------------------------------------------
@@ -556,7 +560,21 @@ mi_backward_kernel(const real *__restrict__ px, real *__restrict__ lattice,
   }
   if (!is_io && row0 + i == 0 && origin_grad != nullptr) origin_grad[b] = g_last;
   if (is_io && nchunks > 0) drain_chunk(0);
-  if (failed && threadIdx.x == 0 && origin_grad != nullptr) origin_grad[b] = (real)NAN;
+  __syncthreads();
+  // a hand-off that ran out: the gradients of this launch are wrong.  Say so in an
+  // output that every caller has -- NaN in the first gradient entry of this launch's
+  // rows inside the box -- and in origin_grad when it was asked for; the gradients a
+  // block passes up turn NaN too, so that the launch that holds row 0 (the last one,
+  // which writes origin_grad) sees the failure of an earlier one
+  if (BLOCKED && failed && row0 > 0)
+    for (int k = threadIdx.x; k < nd; k += blockDim.x) edge_out[row0 + k] = (real)NAN;
+  if (failed && threadIdx.x == 0) {
+    if (ib >= 0 && box.tb >= 1)
+      GY[(size_t)(box.s0 + row0) * T + box.t0] = (real)NAN;
+    else if (ib >= 0 && row0 < box.sb)
+      GX[(size_t)(box.s0 + row0) * T1 + box.t0] = (real)NAN;
+    if (origin_grad != nullptr) origin_grad[b] = (real)NAN;
+  }
 }
 
 // p in the reference's [B][S+1][T+1] layout -> the weight exponents
@@ -838,6 +856,12 @@ extern "C" int frnnt_mi_fwd_bwd_noalloc(int dtype, const void *px, const void *p
                 B, S, T, need, (size_t)FRNNT_MI_NOALLOC_SCRATCH_BYTES);
   if (B == 0) return FRNNT_OK;
   FRNNT_REQUIRE(ans != nullptr && ans_grad != nullptr, FRNNT_EINVAL, "ans or ans_grad is NULL");
+  // everything either sweep would refuse is refused here, before the first launch
+  FRNNT_REQUIRE((px != nullptr || S == 0 || (modified && T == 0)) && (py != nullptr || T == 0),
+                FRNNT_EINVAL, "px or py is NULL");
+  FRNNT_REQUIRE((px_grad != nullptr || S == 0 || (modified && T == 0)) &&
+                    (py_grad != nullptr || T == 0),
+                FRNNT_EINVAL, "px_grad or py_grad is NULL");
   void *scratch = nullptr;
   rc = static_scratch_address(&scratch);
   if (rc != FRNNT_OK) return rc;

@@ -497,7 +497,7 @@ extern "C" int frnnt_prune_gather(int dtype, const void *lm, const int64_t *rang
   cudaStream_t st = (cudaStream_t)stream;
   const size_t row_bytes = (size_t)D * dtype_size(dtype);
   long long want = (rows + 7) / 8;
-  const int grid = (int)(want < 148LL * 32 ? want : 148LL * 32);
+  const int grid = (int)(want < (long long)sm_count() * 32 ? want : (long long)sm_count() * 32);
   if (row_bytes % 16 == 0 && (uintptr_t)lm % 16 == 0 && (uintptr_t)out % 16 == 0) {
     FRNNT_KERNEL(prune_gather_kernel<float4><<<grid, 256, 0, st>>>((const float4 *)lm, ranges, (float4 *)out,
                                                      rows, T * R, S1, (int)(row_bytes / 16)));
@@ -552,7 +552,7 @@ extern "C" int frnnt_pruned_tanh(int dtype, const void *enc, const void *dec, co
   FRNNT_REQUIRE(enc && dec && ranges && act, FRNNT_EINVAL, "NULL argument");
   cudaStream_t st = (cudaStream_t)stream;
   long long want = (rows + 7) / 8;
-  const int grid = (int)(want < 148LL * 32 ? want : 148LL * 32);
+  const int grid = (int)(want < (long long)sm_count() * 32 ? want : (long long)sm_count() * 32);
   const bool al = (uintptr_t)enc % 16 == 0 && (uintptr_t)dec % 16 == 0 && (uintptr_t)act % 16 == 0;
   if (dtype == FRNNT_F32) {
     if (al && D % 4 == 0)
@@ -581,7 +581,7 @@ extern "C" int frnnt_sum_over_range(int dtype, const void *gz, void *out, long l
   FRNNT_REQUIRE(gz && out, FRNNT_EINVAL, "NULL argument");
   cudaStream_t st = (cudaStream_t)stream;
   long long want = (frames + 7) / 8;
-  const int grid = (int)(want < 148LL * 32 ? want : 148LL * 32);
+  const int grid = (int)(want < (long long)sm_count() * 32 ? want : (long long)sm_count() * 32);
   const bool al = (uintptr_t)gz % 16 == 0 && (uintptr_t)out % 16 == 0;
   if (dtype == FRNNT_F32) {
     if (al && D % 4 == 0)

@@ -661,7 +661,7 @@ static SmoothCfg make_cfg(int smoothed, double lm_only_scale, double am_only_sca
 static inline int warps_grid(long long rows) {
   long long want = (rows + 7) / 8;
   if (want < 1) want = 1;
-  return (int)(want < 148LL * 32 ? want : 148LL * 32);
+  return (int)(want < (long long)sm_count() * 32 ? want : (long long)sm_count() * 32);
 }
 
 template <typename real>

@@ -505,17 +505,8 @@ inline int make_operand_map(CUtensorMap *map, const float *base, int rows, int c
 // one persistent CTA per SM (shared memory and tensor memory allow no more), fewer when
 // there are fewer work items
 inline int lin_grid(long long items, int *ctas) {
-  static int sm_count[64] = {0};
-  int dev = 0;
-  FRNNT_CUDA(cudaGetDevice(&dev));
-  FRNNT_REQUIRE(dev >= 0 && dev < 64, FRNNT_EUNSUPPORTED, "device index %d too large", dev);
-  if (sm_count[dev] == 0) {
-    int n = 0;
-    FRNNT_CUDA(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
-    FRNNT_REQUIRE(n > 0, FRNNT_ECUDA, "no multiprocessors reported");
-    sm_count[dev] = n;
-  }
-  *ctas = (int)(items < sm_count[dev] ? items : sm_count[dev]);
+  const int sms = sm_count();
+  *ctas = (int)(items < sms ? items : sms);
   return FRNNT_OK;
 }
 

@@ -14,8 +14,17 @@
  *   - `stream` is a cudaStream_t passed as void*; work is enqueued on it and
  *     nothing synchronises;
  *   - nothing allocates device memory: outputs and scratch are the caller's
- *     (scratch sizes come from the *_workspace_bytes functions);
- *   - re-entrant; no global state besides the thread-local error string.
+ *     (scratch sizes come from the frnnt_*_bytes / frnnt_*_floats functions next
+ *     to each entry point);
+ *   - re-entrant.  Global state: the thread-local error string, the launch
+ *     counter, a per-device cache of the multiprocessor count, and -- for
+ *     frnnt_mi_fwd_bwd_noalloc only -- the built-in scratch region and its cached
+ *     per-device address;
+ *   - waits inside the kernels are bounded.  A wait that runs out does not fail
+ *     the call (nothing synchronises, so the host cannot know): the affected
+ *     outputs are poisoned with NaN instead -- ans[b] of the forward recursion,
+ *     the first in-box gradient entry (and origin_grad[b]) of the reverse sweep,
+ *     the output tile of a tensor-core product.
  *
  * Lattice layouts (identical to the reference's tensors):
  *   px   [B][S][T1]     T1 = T+1 ("regular") or T ("modified"/"constrained")
@@ -126,8 +135,12 @@ int frnnt_mi_backward(int dtype, const void *px, const void *py, const int64_t *
  * the device.  frnnt_mi_forward / frnnt_mi_backward_from_lattice need a
  * caller-provided scratch of frnnt_mi_lattice_bytes(); this entry point instead
  * keeps the lattice in a region of FRNNT_MI_NOALLOC_SCRATCH_BYTES
- * (32 MiB) that is part of the library image: every GPU that loads the library
- * holds those 32 MiB from load until the process exits.
+ * (32 MiB) that is part of the library image: every GPU whose context loads the
+ * library's code holds those 32 MiB until the process exits.  With CUDA's
+ * default lazy module loading that happens at the first call into the module,
+ * which may itself stall or run out of memory on a host that has given all of
+ * it away: make one warm-up call during initialisation (or run with
+ * CUDA_MODULE_LOADING=EAGER), after which calls take nothing from the device.
  *
  *   - inputs px, py, boundary, ans_grad [B] and outputs ans [B], px_grad, py_grad
  *     are the caller's, exactly as for the two functions it combines;
@@ -135,7 +148,10 @@ int frnnt_mi_backward(int dtype, const void *px, const void *py, const int64_t *
  *     refused with FRNNT_EUNSUPPORTED before anything is launched;
  *   - it calls no cudaMalloc / cudaFree and no allocating library routine;
  *   - the FIRST call on each device looks up the region's device address (with
- *     that device current); make that first call outside of any stream capture;
+ *     that device current); make that first call outside of any stream capture.
+ *     The address is cached per device ordinal and does not survive a
+ *     cudaDeviceReset() of that device: do not reset a device between calls;
+ *   - every argument is checked before the first of the two sweeps is launched;
  *   - all calls on a device share the one region, which still holds the previous
  *     call's lattice when the next call starts (nothing needs clearing: each
  *     call overwrites what it later reads).  Two calls whose kernels overlap on

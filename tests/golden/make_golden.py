@@ -103,9 +103,10 @@ def case_mi(fr):
              joint=joint)
 
 
-def run_pipeline(fr, wl, rnnt_type, full_arrays):
+def run_pipeline(fr, wl, rnnt_type, full_arrays, keep_full=()):
     """The documented usage (reference README.md:150-190): smoothed simple loss
-    with return_grad -> ranges -> pruning -> joiner -> pruned loss -> backward."""
+    with return_grad -> ranges -> pruning -> joiner -> pruned loss -> backward.
+    Without full_arrays only summaries are kept, plus the arrays named in keep_full."""
     am = wl["am"].clone().requires_grad_(True)
     lm = wl["lm"].clone().requires_grad_(True)
     enc = wl["enc"].clone().requires_grad_(True)
@@ -145,6 +146,7 @@ def run_pipeline(fr, wl, rnnt_type, full_arrays):
     else:
         out.update({k + "_sample": sample(v) for k, v in big.items()})
         out.update({k + "_sum": v.detach().double().clamp(min=-1e30).sum() for k, v in big.items()})
+        out.update({k: big[k] for k in keep_full})
     return out
 
 
@@ -213,6 +215,14 @@ def case_c3(fr):
     save("c3_pipeline", **run_pipeline(fr, wl, "regular", False))
 
 
+def case_c5_shape(fr):
+    # the large-vocabulary shape (T=400, S=60, C=5000, s_range=5) on a batch the CPU
+    # handles; the occupancies are kept in full so that the range stage can be checked
+    # bit for bit on the reference's own inputs
+    wl = workloads.pipeline_workload("c5", rnnt_type="regular", batch=3, seed=2)
+    save("c5_shape_pipeline", **run_pipeline(fr, wl, "regular", False, keep_full=("occ_x", "occ_y")))
+
+
 def case_c4(fr):
     wl = workloads.config_c4()
     logits = wl["logits"].clone().requires_grad_(True)
@@ -270,13 +280,16 @@ def case_prune_edges(fr):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("FAST_RNNT_REFERENCE"), required=False,
+                    help="checkout of k2-fsa/fast_rnnt (or set FAST_RNNT_REFERENCE)")
     ap.add_argument("--only", default="")
     args = ap.parse_args()
+    if not args.ref:
+        ap.error("--ref (or FAST_RNNT_REFERENCE) must name a checkout of the reference")
     fr = load_reference(args.ref)
     torch.set_num_threads(max(1, min(8, os.cpu_count() or 1)))
     cases = dict(basic=case_basic, mi=case_mi, pipelines=case_pipelines, c1=case_c1,
-                 c2=case_c2, c3=case_c3, c4=case_c4, joint_small=case_joint_small,
+                 c2=case_c2, c3=case_c3, c4=case_c4, c5_shape=case_c5_shape, joint_small=case_joint_small,
                  prune_edges=case_prune_edges)
     for name, fn in cases.items():
         if args.only and name not in args.only.split(","):

@@ -64,7 +64,23 @@ def test_basic_known_answers():
                  g["smoothed0"], LOSS_RTOL, 1e-5, "smoothed shifted")
 
 
-def run_pipeline(wl, rnnt_type, dtype=torch.float32):
+def joiner_logits(kind, enc, dec, ranges, W, bias):
+    """The joiner between do_rnnt_pruning and rnnt_loss_pruned: the reference's documented
+    composition in torch ("torch"), or this library's pruned_joiner ("fused")."""
+    f = fr()
+    if kind == "fused":
+        return f.pruned_joiner(enc, dec, ranges, W, bias)
+    am_p, lm_p = f.do_rnnt_pruning(am=enc, lm=dec, ranges=ranges)
+    return torch.nn.functional.linear(torch.tanh(am_p + lm_p), W, bias)
+
+
+def samp(x):
+    """The strided sample tests/golden/make_golden.py keeps of a full-size tensor."""
+    flat = x.detach().reshape(-1)
+    return flat[:: max(1, flat.numel() // 4096)]
+
+
+def run_pipeline(wl, rnnt_type, dtype=torch.float32, joiner="torch"):
     f = fr()
     conv = lambda x: x.to(dtype).cuda() if x.is_floating_point() else x.cuda()  # noqa: E731
     am = conv(wl["am"]).requires_grad_(True)
@@ -83,8 +99,7 @@ def run_pipeline(wl, rnnt_type, dtype=torch.float32):
                                             rnnt_type=rnnt_type, reduction="sum", return_grad=True)
     occ_x, occ_y = ox.clone(), oy.clone()
     ranges = f.get_rnnt_prune_ranges(px_grad=ox, py_grad=oy, boundary=bnd, s_range=wl["s_range"])
-    am_p, lm_p = f.do_rnnt_pruning(am=enc, lm=dec, ranges=ranges)
-    logits = torch.nn.functional.linear(torch.tanh(am_p + lm_p), W, bias)
+    logits = joiner_logits(joiner, enc, dec, ranges, W, bias)
     logits.retain_grad()
     ppx, ppy = f.get_rnnt_logprobs_pruned(logits=logits.detach(), symbols=sym, ranges=ranges,
                                           termination_symbol=blank, boundary=bnd,
@@ -280,17 +295,15 @@ def test_small_pipeline_float64_vs_oracle(rnnt_type):
         assert_close(out[k], v, 1e-8, 1e-9, k)
 
 
-def test_c3_full_size_against_reference_summary():
-    """BASELINE config 3 (B=64, T=500, S=100, C=500, s_range=5) against the
-    summaries the reference wrote: losses, prune-range starts, strided samples."""
+@pytest.mark.parametrize("joiner", ["torch", "fused"])
+def test_c3_full_size_against_reference_summary(joiner):
+    """The full pruned pipeline at B=64, T=500, S=100, C=500, s_range=5 against the
+    summaries the reference wrote: losses, prune-range starts, strided samples; with the
+    joiner in torch and on this library's pruned_joiner (what bench.py times)."""
     g = load_golden("c3_pipeline")
     wl = workloads.pipeline_workload("c3")
-    out = run_pipeline(wl, "regular")
+    out = run_pipeline(wl, "regular", joiner=joiner)
     assert_close(out["simple"], torch.tensor(g["simple"]), LOSS_RTOL, 0, "simple loss")
-
-    def samp(x):
-        flat = x.detach().reshape(-1)
-        return flat[:: max(1, flat.numel() // 4096)]
 
     assert_close(samp(out["px"]), g["px_sample"], 0, LATTICE_ATOL, "px")
     assert_close(samp(out["py"]), g["py_sample"], 0, LATTICE_ATOL, "py")
@@ -310,6 +323,69 @@ def test_c3_full_size_against_reference_summary():
     assert torch.equal(out["ranges"].cpu(), ranges_oracle)
 
 
+def pruned_stage(wl, ranges, joiner):
+    """Pruning -> joiner -> pruned loss -> backward on GIVEN ranges (regular type)."""
+    f = fr()
+    enc = wl["enc"].cuda().requires_grad_(True)
+    dec = wl["dec"].cuda().requires_grad_(True)
+    W = wl["joiner_w"].cuda().requires_grad_(True)
+    bias = wl["joiner_b"].cuda().requires_grad_(True)
+    sym, bnd = wl["symbols"].cuda(), wl["boundary"].cuda()
+    logits = joiner_logits(joiner, enc, dec, ranges, W, bias)
+    logits.retain_grad()
+    ppx, ppy = f.get_rnnt_logprobs_pruned(logits=logits.detach(), symbols=sym, ranges=ranges,
+                                          termination_symbol=0, boundary=bnd)
+    pruned = f.rnnt_loss_pruned(logits=logits, symbols=sym, ranges=ranges, termination_symbol=0,
+                                boundary=bnd, reduction="sum")
+    pruned.backward()
+    return dict(pruned=pruned, logits=logits, pruned_px=ppx, pruned_py=ppy,
+                logits_grad=logits.grad, enc_grad=enc.grad, dec_grad=dec.grad, w_grad=W.grad,
+                b_grad=bias.grad)
+
+
+def check_pruned_stage(out, g):
+    """Pruned stage on the reference's own ranges: loss 1e-5 relative, lattices 1e-5,
+    gradients 1e-4 absolute (plus 1e-4 relative: the weight and bias gradients are sums
+    over all frames of the batch and reach 1e3..1e4)."""
+    assert_close(out["pruned"], torch.tensor(g["pruned"]), LOSS_RTOL, 0, "pruned loss")
+    assert_close(samp(out["logits"]), g["logits_sample"], 0, LATTICE_ATOL, "logits")
+    assert_close(samp(out["pruned_px"]), g["pruned_px_sample"], 0, LATTICE_ATOL, "pruned px")
+    assert_close(samp(out["pruned_py"]), g["pruned_py_sample"], 0, LATTICE_ATOL, "pruned py")
+    for k in ("logits_grad", "enc_grad", "dec_grad", "w_grad", "b_grad"):
+        assert_close(samp(out[k]), g[k + "_sample"], 1e-4, GRAD_ATOL, k)
+
+
+@pytest.mark.parametrize("joiner", ["torch", "fused"])
+def test_c3_full_size_pruned_stage_on_reference_ranges(joiner):
+    """Stage-wise at full size: with the reference's prune ranges injected the argmax
+    no longer matters, so the pruned loss must agree to 1e-5 and the gradients of the
+    logits, the encoder / decoder activations and the joiner's weights to 1e-4."""
+    g = load_golden("c3_pipeline")
+    wl = workloads.pipeline_workload("c3")
+    ranges = (g["s_begin"].to(torch.int64).unsqueeze(-1) + torch.arange(g["s_range"])).cuda()
+    check_pruned_stage(pruned_stage(wl, ranges, joiner), g)
+
+
+def test_c3_bench_step_matches_the_reference():
+    """The step bench.py times (its make_step with pruned_joiner) on the same workload:
+    loss and input gradients against the reference's summary."""
+    import bench
+    g = load_golden("c3_pipeline")
+    wl = workloads.pipeline_workload("c3")
+    step = bench.make_step(fr(), wl, lambda f, enc, dec, ranges, W, b: f.pruned_joiner(enc, dec, ranges, W, b))
+    t = {k: wl[k].cuda() for k in bench.TENSOR_KEYS}
+    loss = step(t)
+    # own ranges: a few frames may pick a neighbouring window (see the test above)
+    assert_close(loss, torch.tensor(g["simple"] + g["pruned"]), 5e-4, 0, "simple + pruned")
+    assert_close(samp(t["am"].grad), g["am_grad_sample"], 0, GRAD_ATOL, "am grad")
+    assert_close(samp(t["lm"].grad), g["lm_grad_sample"], 0, GRAD_ATOL, "lm grad")
+    # a moved window changes the encoder gradient of its own frame only, and the decoder
+    # gradient of the few rows it covers
+    for k, allowed in (("enc", 0.02), ("dec", 0.3)):
+        err = (samp(t[k].grad).cpu() - g[k + "_grad_sample"]).abs()
+        assert (err > 1e-3).float().mean().item() < allowed, k
+
+
 def test_c4_unpruned_against_reference_summary():
     g = load_golden("c4_unpruned")
     wl = workloads.config_c4()
@@ -325,8 +401,43 @@ def test_c4_unpruned_against_reference_summary():
                  "logits grad")
 
 
+@pytest.mark.parametrize("joiner", ["torch", "fused"])
+def test_c5_shape_against_reference_summary(joiner):
+    """The large-vocabulary shape (T=400, S=60, C=5000, s_range=5, batch of 3) against
+    vectors the reference itself wrote: simple stage, ranges bit for bit on the
+    reference's occupancies, pruned stage on the reference's ranges.  Single lm
+    gradients reach 3e2 here, where the reference's own float32 result is 1.2e-2 away
+    from its float64 result: those are compared with a relative term of 1e-4."""
+    g = load_golden("c5_shape_pipeline")
+    wl = workloads.pipeline_workload("c5", batch=3, seed=2)
+    f = fr()
+    sym, bnd = wl["symbols"].cuda(), wl["boundary"].cuda()
+    am = wl["am"].cuda().requires_grad_(True)
+    lm = wl["lm"].cuda().requires_grad_(True)
+    px, py = f.get_rnnt_logprobs_smoothed(lm=lm.detach(), am=am.detach(), symbols=sym,
+                                          termination_symbol=0, lm_only_scale=wl["lm_only_scale"],
+                                          am_only_scale=wl["am_only_scale"], boundary=bnd)
+    assert_close(samp(px), g["px_sample"], 0, LATTICE_ATOL, "px")
+    assert_close(samp(py), g["py_sample"], 0, LATTICE_ATOL, "py")
+    simple, (gx, gy) = f.rnnt_loss_smoothed(lm=lm, am=am, symbols=sym, termination_symbol=0,
+                                            lm_only_scale=wl["lm_only_scale"],
+                                            am_only_scale=wl["am_only_scale"], boundary=bnd,
+                                            reduction="sum", return_grad=True)
+    assert_close(simple, torch.tensor(g["simple"]), LOSS_RTOL, 0, "simple loss")
+    assert_close(gx, g["occ_x"], 0, GRAD_ATOL, "occ_x")
+    assert_close(gy, g["occ_y"], 0, GRAD_ATOL, "occ_y")
+    simple.backward()
+    assert_close(samp(am.grad), g["am_grad_sample"], 1e-4, GRAD_ATOL, "am grad")
+    assert_close(samp(lm.grad), g["lm_grad_sample"], 1e-4, GRAD_ATOL, "lm grad")
+    ref_ranges = g["s_begin"].to(torch.int64).unsqueeze(-1) + torch.arange(g["s_range"])
+    r = f.get_rnnt_prune_ranges(px_grad=g["occ_x"].cuda(), py_grad=g["occ_y"].cuda(), boundary=bnd,
+                                s_range=wl["s_range"])
+    assert torch.equal(r.cpu(), ref_ranges)
+    check_pruned_stage(pruned_stage(wl, ref_ranges.cuda(), joiner), g)
+
+
 def test_c5_shape_stagewise_vs_oracle():
-    """BASELINE config 5's shape (T=400, S=60, C=5000, s_range=5) on a batch of 2:
+    """The large-vocabulary shape (T=400, S=60, C=5000, s_range=5) on a batch of 2:
     large-vocabulary rows take the multi-warp log-softmax path.  Stage-wise
     against the CPU oracle with the oracle's occupancies, ranges and logits
     injected; gradients that reach 1e2 in magnitude are compared relatively."""
