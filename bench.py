@@ -121,16 +121,15 @@ class ClockSampler:
 # ------------------------------------------------------------------------------
 # the step
 # ------------------------------------------------------------------------------
-def torch_joiner(fr, enc, dec, ranges, W, bias):
-    """The joiner of the reference's documented usage, in plain torch."""
-    am_p, lm_p = fr.do_rnnt_pruning(am=enc, lm=dec, ranges=ranges)
-    return torch.nn.functional.linear(torch.tanh(am_p + lm_p), W, bias)
-
-
-def make_step(fr, wl, joiner=torch_joiner):
-    """Returns step(inputs) -> loss for the pruned pipeline; `fr` is the loss
-    package (ours on CUDA, or the CPU oracle wrapped to the same names) and
-    `joiner` computes the logits from (enc, dec, ranges, W, bias)."""
+def make_step(fr, wl, joiner="torch"):
+    """Returns step(inputs) -> loss for the pruned pipeline; `fr` is the loss package
+    (ours on CUDA, or the CPU oracle / the reference wrapped to the same names).
+    joiner: how the caller's network between pruning and the pruned loss runs --
+      "torch"       do_rnnt_pruning + torch Linear(tanh(.)) + rnnt_loss_pruned (the
+                    reference's documented usage, the only form the reference offers),
+      "tensorcore"  this library's pruned_joiner (3xTF32 products) + rnnt_loss_pruned,
+      "fused"       this library's rnnt_loss_pruned_joiner: one operator from enc / dec to
+                    the pruned lattices (fp16-pair products, log-sum-exp in the epilogue)."""
     blank, R = wl["blank"], wl["s_range"]
     ls, as_ = wl["lm_only_scale"], wl["am_only_scale"]
 
@@ -147,10 +146,20 @@ def make_step(fr, wl, joiner=torch_joiner):
             lm=lm, am=am, symbols=t["symbols"], termination_symbol=blank, lm_only_scale=ls,
             am_only_scale=as_, boundary=t["boundary"], reduction="sum", return_grad=True)
         ranges = fr.get_rnnt_prune_ranges(px_grad=gx, py_grad=gy, boundary=t["boundary"], s_range=R)
-        logits = joiner(fr, enc, dec, ranges, W, bias)
-        pruned = fr.rnnt_loss_pruned(logits=logits, symbols=t["symbols"], ranges=ranges,
-                                     termination_symbol=blank, boundary=t["boundary"],
-                                     reduction="sum")
+        if joiner == "fused":
+            pruned = fr.rnnt_loss_pruned_joiner(
+                am=enc, lm=dec, ranges=ranges, joiner_weight=W, joiner_bias=bias,
+                symbols=t["symbols"], termination_symbol=blank, boundary=t["boundary"],
+                reduction="sum")
+        else:
+            if joiner == "tensorcore":
+                logits = fr.pruned_joiner(enc, dec, ranges, W, bias)
+            else:
+                am_p, lm_p = fr.do_rnnt_pruning(am=enc, lm=dec, ranges=ranges)
+                logits = torch.nn.functional.linear(torch.tanh(am_p + lm_p), W, bias)
+            pruned = fr.rnnt_loss_pruned(logits=logits, symbols=t["symbols"], ranges=ranges,
+                                         termination_symbol=blank, boundary=t["boundary"],
+                                         reduction="sum")
         loss = simple + pruned
         loss.backward()
         return loss.detach()
@@ -371,8 +380,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c3", choices=["c3", "c5", "small"])
     ap.add_argument("--batch", type=int, default=None, help="utterances per GPU")
-    ap.add_argument("--joiner", default="tensorcore", choices=["tensorcore", "torch"],
-                    help="projection of the joiner: this library's 3xTF32 tcgen05 linear, or "
+    ap.add_argument("--joiner", default="fused", choices=["fused", "tensorcore", "torch"],
+                    help="the caller's joiner: this library's fused rnnt_loss_pruned_joiner "
+                         "(fp16-pair tcgen05 products), its pruned_joiner (3xTF32 products), or "
                          "torch.nn.functional.linear (cuBLAS fp32)")
     ap.add_argument("--no-stages", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -389,10 +399,13 @@ def main():
            "B_per_gpu": batch, "T": sizes[1], "S": sizes[2], "C": sizes[3], "D": sizes[4],
            "s_range": sizes[5], "global_batch": batch * world,
            "parallelism": f"batch sharded over {world} GPU(s), scalar-loss all-reduce",
-           "joiner": ("Linear(tanh(enc_pruned+dec_pruned)) as fast_rnnt_b200.pruned_joiner: fused "
-                      "gather+add+tanh, projection fwd+bwd on tcgen05 with 3xTF32 (fp32-level accuracy)"
-                      if args.joiner == "tensorcore" and args.impl == "ours" else
-                      "torch Linear(tanh(enc+dec)), fp32"),
+           "joiner": ({"fused": "Linear(tanh(enc_pruned+dec_pruned)) + pruned log-probs as "
+                                "fast_rnnt_b200.rnnt_loss_pruned_joiner: one operator, fp16-pair tcgen05 "
+                                "products (fp32-level accuracy), log-sum-exp in the product's epilogue",
+                       "tensorcore": "Linear(tanh(enc_pruned+dec_pruned)) as fast_rnnt_b200.pruned_joiner: "
+                                     "gather+add+tanh kernel, projection fwd+bwd on tcgen05 with 3xTF32",
+                       "torch": "torch Linear(tanh(enc+dec)), fp32"}[args.joiner]
+                      if args.impl == "ours" else "torch Linear(tanh(enc+dec)), fp32"),
            "l2": f"value and stages: flushed between timed steps ({L2_FLUSH_BYTES >> 20} MiB write); e2e: "
                  "every step's inputs are a fresh upload larger than L2",
            "e2e_upload": "all inputs of a step collated in one page-locked (cudaHostRegister) buffer, "
@@ -434,12 +447,7 @@ def main():
     wl = workloads.pipeline_workload(args.workload, batch=batch, seed=rank)
     host = {k: wl[k].pin_memory() for k in TENSOR_KEYS}
     resident = {k: v.to(dev) for k, v in host.items()}
-    if args.joiner == "tensorcore":
-        def joiner(fr_, enc, dec, ranges, W, bias):
-            return fr_.pruned_joiner(enc, dec, ranges, W, bias)
-    else:
-        joiner = torch_joiner
-    inner = make_step(fr, wl, joiner)
+    inner = make_step(fr, wl, args.joiner)
 
     from fast_rnnt_b200 import sharding
 

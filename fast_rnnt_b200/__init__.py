@@ -21,6 +21,7 @@ from .rnnt_loss import rnnt_loss_smoothed  # noqa: F401
 # additions that have no counterpart in the reference: the caller's joiner on the tensor
 # cores, and a way to hand over the host copy of `boundary` that a data loader already has
 from .linear import linear, pruned_joiner  # noqa: F401,E402
+from .rnnt_loss import get_rnnt_logprobs_pruned_joiner, rnnt_loss_pruned_joiner  # noqa: F401,E402
 from .mutual_information import provide_boundary_rows  # noqa: F401,E402
 
 

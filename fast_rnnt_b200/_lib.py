@@ -34,7 +34,9 @@ def lib():
         _lib.frnnt_last_error.restype = ctypes.c_char_p
         for name in ("frnnt_mi_lattice_bytes", "frnnt_simple_saved_bytes",
                      "frnnt_simple_scratch_bytes", "frnnt_matmul_tn_scratch_floats",
-                     "frnnt_joiner_input_grads_scratch_bytes"):
+                     "frnnt_joiner_input_grads_scratch_bytes", "frnnt_pruned_joiner_saved_bytes",
+                     "frnnt_pruned_joiner_forward_scratch_bytes",
+                     "frnnt_pruned_joiner_backward_scratch_bytes"):
             if hasattr(_lib, name):
                 getattr(_lib, name).restype = _c_sz
     return _lib

@@ -1,0 +1,623 @@
+// The pruned joiner and the pruned log-prob lattices as ONE operator:
+//
+//   px, py = get_rnnt_logprobs_pruned(Linear(tanh(am_pruned + lm_pruned)), symbols, ranges, ...)
+//   with am_pruned, lm_pruned = do_rnnt_pruning(enc, dec, ranges)
+//
+// i.e. the caller's network between do_rnnt_pruning and rnnt_loss_pruned in the
+// reference's documented usage (README.md:180-190) together with
+// fast_rnnt/python/fast_rnnt/rnnt_loss.py:810-817 (pruning) and :940-1022 (log-softmax,
+// symbol / blank gather, placement into the lattices), forward and backward.  No
+// counterpart in the reference, which leaves the joiner to the caller and therefore
+// cannot fuse across it.
+//
+// What the fusion buys: every matrix that feeds a tensor-core product is written by its
+// producer as a pair of fp16 planes (umma_pairs.cuh), so the three products run as pure
+// TMA -> tcgen05 pipelines at the fp16 rate with fp32-level accuracy:
+//   forward    tanh(enc + dec[ranges]) -> act planes;  W -> planes (both orientations);
+//              logits = act * W^T + bias on the tensor cores, whose epilogue also leaves
+//              a (max, sum exp) pair per row and 128-column tile, so that no second pass
+//              over the logits is needed for the log-sum-exp; a small kernel combines the
+//              pairs, picks logit[symbol] and logit[blank] and the bands go into px, py.
+//   backward   g = d loss / d logits from logits, lse and the lattice gradients -> planes,
+//              with the column sums of g (the bias gradient) taken on the way;
+//              gz = (g * W) * (1 - act^2) on the tensor cores (tanh' in the epilogue);
+//              enc_grad / dec_grad from one pass over gz;  W_grad = g^T * act, split-K.
+#include <cuda_fp16.h>
+
+#include "lsm_band.cuh"
+#include "umma_pairs.cuh"
+
+namespace frnnt {
+
+constexpr float kActScale = 16384.f;  // 2^14: |tanh| <= 1, so the planes stay below 2^14
+constexpr int kMaxParts = 1024;       // per-CTA partial maxima of a reduction
+constexpr int kRowWarps = 8;
+
+enum { kScaleAct = 0, kScaleW = 1, kScaleG = 2 };  // slots of the inverse scales
+
+static inline size_t up256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+static int pair_tn_splits(int M, int N, long long R) {
+  if (M <= 0 || N <= 0 || R <= 0) return 1;
+  const long long tiles = (long long)((M + kPairTile - 1) / kPairTile) * ((N + kPairTile - 1) / kPairTile);
+  const long long max_splits = (R + 8 * kPairBK - 1) / (8 * kPairBK);
+  const long long sms = sm_count();
+  int best = 1;
+  double best_cost = 1e30;
+  for (int sp = 1; sp <= 64 && sp <= max_splits; ++sp) {
+    const long long waves = (tiles * sp + sms - 1) / sms;
+    const double cost = (double)waves / sp + 0.002 * sp;
+    if (cost < best_cost - 1e-12) {
+      best_cost = cost;
+      best = sp;
+    }
+  }
+  return best;
+}
+
+static int colsum_ctas(long long rows) {
+  long long want = (rows + kRowWarps - 1) / kRowWarps;
+  const long long cap = (long long)sm_count() * 8;
+  return (int)(want < 1 ? 1 : (want < cap ? want : cap));
+}
+
+// Offsets (bytes) of everything the operator keeps: `saved` lives from forward to
+// backward, the two scratch areas only during one call.
+struct PjlLayout {
+  size_t M, Cp;
+  int tiles_n, splits, cs_ctas;
+  size_t act_hi, act_lo, logits, lse, wt_hi, wt_lo, scales, saved_bytes;
+  size_t w_hi, w_lo, stats, pxb, pyb, amax_part, fwd_bytes;
+  size_t g_hi, g_lo, gz, gxb, gyb, gmax_part, dw_part, cs_part, jg, bwd_bytes;
+};
+
+static PjlLayout pjl_layout(int B, int T, int R, int S1, int C, int D) {
+  PjlLayout L;
+  const size_t M = (size_t)B * T * R;
+  const size_t Cp = (size_t)(C + 7) / 8 * 8;
+  L.M = M;
+  L.Cp = Cp;
+  L.tiles_n = (C + kPairTile - 1) / kPairTile;
+  L.splits = pair_tn_splits(C, D, (long long)M);
+  L.cs_ctas = colsum_ctas((long long)M);
+  size_t o = 0;
+  auto take = [&](size_t bytes) {
+    const size_t r = o;
+    o += up256(bytes);
+    return r;
+  };
+  L.act_hi = take(M * D * 2);
+  L.act_lo = take(M * D * 2);
+  L.logits = take(M * C * 4);
+  L.lse = take(M * 4);
+  L.wt_hi = take((size_t)D * Cp * 2);
+  L.wt_lo = take((size_t)D * Cp * 2);
+  L.scales = take(16 * 4);
+  L.saved_bytes = o;
+  o = 0;
+  L.w_hi = take((size_t)C * D * 2);
+  L.w_lo = take((size_t)C * D * 2);
+  L.stats = take(M * L.tiles_n * 8);
+  L.pxb = take(M * 4);
+  L.pyb = take(M * 4);
+  L.amax_part = take(kMaxParts * 4);
+  L.fwd_bytes = o;
+  o = 0;
+  L.g_hi = take(M * Cp * 2);
+  L.g_lo = take(M * Cp * 2);
+  L.gz = take(M * D * 4);
+  L.gxb = take(M * 4);
+  L.gyb = take(M * 4);
+  L.gmax_part = take(kMaxParts * 4);
+  L.dw_part = take(L.splits > 1 ? (size_t)L.splits * C * D * 4 : 0);
+  L.cs_part = take((size_t)L.cs_ctas * C * 4);
+  L.jg = take(frnnt_joiner_input_grads_scratch_bytes(B, T, D));
+  L.bwd_bytes = o;
+  (void)S1;
+  return L;
+}
+
+// ---- small reductions ---------------------------------------------------------------------
+// max over part[0..n), computed by warp 0 and handed to every thread of the block
+__device__ float block_max_of_partials(const float *__restrict__ part, int n, float *slot) {
+  if (threadIdx.x < 32) {
+    float m = 0.f;
+    for (int i = threadIdx.x; i < n; i += 32) m = fmaxf(m, part[i]);
+    m = warp_max(m);
+    if (threadIdx.x == 0) *slot = m;
+  }
+  __syncthreads();
+  return *slot;
+}
+
+__global__ void __launch_bounds__(256)
+absmax_partial_kernel(const float *__restrict__ x, long long n, float *__restrict__ part) {
+  __shared__ float s[8];
+  float m = 0.f;
+  for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < n; i += (long long)gridDim.x * 256)
+    m = fmaxf(m, fabsf(x[i]));
+  m = warp_max(m);
+  if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w) m = fmaxf(m, s[w]);
+    part[blockIdx.x] = m;
+  }
+}
+
+// W [C][D] -> planes in both orientations: w [C][D] (forward: B operand, K = D) and
+// wt [D][Cp] (grad-input: B operand, K = C)
+__global__ void __launch_bounds__(256)
+split_weights_kernel(const float *__restrict__ W, int C, int D, int Cp, const float *__restrict__ part,
+                     int nparts, __half *__restrict__ w_hi, __half *__restrict__ w_lo,
+                     __half *__restrict__ wt_hi, __half *__restrict__ wt_lo, float *__restrict__ scales) {
+  __shared__ float slot;
+  const float scale = fp16_pair_scale(block_max_of_partials(part, nparts, &slot));
+  if (blockIdx.x == 0 && threadIdx.x == 0) scales[kScaleW] = 1.f / scale;
+  const long long n = (long long)C * D;
+  for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < n; i += (long long)gridDim.x * 256) {
+    const int c = (int)(i / D), d = (int)(i - (long long)c * D);
+    __half hi, lo;
+    fp16_pair(W[i], scale, hi, lo);
+    w_hi[i] = hi;
+    w_lo[i] = lo;
+    wt_hi[(size_t)d * Cp + c] = hi;
+    wt_lo[(size_t)d * Cp + c] = lo;
+  }
+}
+
+// act[b][t][k][:] = tanh(enc[b][t][:] + dec[b][ranges[b][t][k]][:]) as planes; one warp per
+// row, eight columns per lane
+__global__ void __launch_bounds__(256)
+pruned_tanh_pairs_kernel(const float *__restrict__ enc, const float *__restrict__ dec,
+                         const int64_t *__restrict__ ranges, __half *__restrict__ act_hi,
+                         __half *__restrict__ act_lo, long long rows, int R, int TR, int S1, int D,
+                         float *__restrict__ scales) {
+  if (blockIdx.x == 0 && threadIdx.x == 0) scales[kScaleAct] = 1.f / kActScale;
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  const int d8 = D / 8;
+  for (long long row = warp0; row < rows; row += nwarps) {
+    const long long b = row / TR, bt = row / R;
+    long long s = ranges[row];
+    s = s < 0 ? 0 : (s >= S1 ? S1 - 1 : s);
+    const float4 *e = reinterpret_cast<const float4 *>(enc + (size_t)bt * D);
+    const float4 *d = reinterpret_cast<const float4 *>(dec + ((size_t)b * S1 + s) * D);
+    uint4 *oh = reinterpret_cast<uint4 *>(act_hi + (size_t)row * D);
+    uint4 *ol = reinterpret_cast<uint4 *>(act_lo + (size_t)row * D);
+    for (int v = lane; v < d8; v += 32) {
+      const float4 x0 = e[2 * v], x1 = e[2 * v + 1], y0 = d[2 * v], y1 = d[2 * v + 1];
+      const float a[8] = {x0.x + y0.x, x0.y + y0.y, x0.z + y0.z, x0.w + y0.w,
+                          x1.x + y1.x, x1.y + y1.y, x1.z + y1.z, x1.w + y1.w};
+      __align__(16) __half hi[8], lo[8];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) fp16_pair(tanhf(a[c]), kActScale, hi[c], lo[c]);
+      oh[v] = *reinterpret_cast<const uint4 *>(hi);
+      ol[v] = *reinterpret_cast<const uint4 *>(lo);
+    }
+  }
+}
+
+// ---- epilogues of the three products ----------------------------------------------------------
+// logits = acc * (1/scales) + bias, and per row and tile (max, sum exp(logit - max))
+struct PjlFwdExt {
+  float *out;
+  const float *bias;
+  float2 *stats;
+  const float *scales;
+  int N, tiles_n;
+  struct Row {
+    float sc, mx, sum;
+  };
+  __device__ void row_begin(Row &r, int, int, int) const {
+    r.sc = scales[kScaleAct] * scales[kScaleW];
+    r.mx = -INFINITY;
+    r.sum = 0.f;
+  }
+  __device__ float *out_row(int, int m) const { return out + (size_t)m * N; }
+  __device__ void finish(Row &r, int, int, int n, float (&v)[16]) const {
+    float cm = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const bool in = n + i < N;
+      v[i] = v[i] * r.sc + ((bias != nullptr && in) ? bias[n + i] : 0.f);
+      cm = in ? fmaxf(cm, v[i]) : cm;
+    }
+    if (cm > r.mx) {
+      r.sum *= __expf(r.mx - cm);
+      r.mx = cm;
+    }
+    const float base = (r.mx - r.mx != 0.f) ? 0.f : r.mx;  // an infinite maximum: as torch.logsumexp
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      if (n + i < N) r.sum += __expf(v[i] - base);
+  }
+  __device__ void row_end(Row &r, int, int m, int n0) const {
+    stats[(size_t)m * tiles_n + n0 / kPairTile] = make_float2(r.mx, r.sum);
+  }
+};
+
+// gz = acc * (1/scales) * (1 - act^2): the gradient with respect to enc + dec
+struct PjlGradInExt {
+  float *out;
+  const __half *act_hi, *act_lo;
+  const float *scales;
+  int N;  // = D
+  struct Row {
+    float sc;
+  };
+  __device__ void row_begin(Row &r, int, int, int) const { r.sc = scales[kScaleG] * scales[kScaleW]; }
+  __device__ float *out_row(int, int m) const { return out + (size_t)m * N; }
+  __device__ void finish(Row &r, int, int m, int n, float (&v)[16]) const {
+    const __half *h = act_hi + (size_t)m * N + n, *l = act_lo + (size_t)m * N + n;
+    if (n + 16 <= N) {
+      __align__(16) __half hh[16], ll[16];
+      *reinterpret_cast<uint4 *>(hh) = *reinterpret_cast<const uint4 *>(h);
+      *reinterpret_cast<uint4 *>(hh + 8) = *reinterpret_cast<const uint4 *>(h + 8);
+      *reinterpret_cast<uint4 *>(ll) = *reinterpret_cast<const uint4 *>(l);
+      *reinterpret_cast<uint4 *>(ll + 8) = *reinterpret_cast<const uint4 *>(l + 8);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float a = (__half2float(hh[i]) + __half2float(ll[i])) * (1.f / kActScale);
+        v[i] = v[i] * r.sc * (1.f - a * a);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        if (n + i < N) {
+          const float a = (__half2float(h[i]) + __half2float(l[i])) * (1.f / kActScale);
+          v[i] = v[i] * r.sc * (1.f - a * a);
+        }
+      }
+    }
+  }
+  __device__ void row_end(Row &, int, int, int) const {}
+};
+
+// W_grad partial sums: acc * (1/scales)
+struct PjlGradWExt {
+  float *out;  // [splits][M][N]
+  const float *scales;
+  int M, N;
+  struct Row {
+    float sc;
+  };
+  __device__ void row_begin(Row &r, int, int, int) const { r.sc = scales[kScaleG] * scales[kScaleAct]; }
+  __device__ float *out_row(int z, int m) const { return out + ((size_t)z * M + m) * N; }
+  __device__ void finish(Row &r, int, int, int, float (&v)[16]) const {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] *= r.sc;
+  }
+  __device__ void row_end(Row &, int, int, int) const {}
+};
+
+// out[i] = sum over z of partial[z][i], z in order
+__global__ void ordered_sum_kernel(const float *__restrict__ partial, float *__restrict__ out,
+                                   long long n, int parts) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float acc = 0;
+  for (int z = 0; z < parts; ++z) acc += partial[(size_t)z * n + i];
+  out[i] = acc;
+}
+
+// ---- bands ------------------------------------------------------------------------------------
+// per row (b, t, k): lse from the per-tile (max, sum) pairs, logit[symbol] - lse, logit[blank] - lse
+__global__ void __launch_bounds__(256)
+joiner_band_kernel(const float *__restrict__ logits, const float2 *__restrict__ stats,
+                   const int64_t *__restrict__ symbols, const int64_t *__restrict__ ranges,
+                   float *__restrict__ lse, float *__restrict__ pxb, float *__restrict__ pyb,
+                   long long rows, int T, int R, int S, int C, int blank, int tiles_n) {
+  const long long row = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (row >= rows) return;
+  const float2 *st = stats + (size_t)row * tiles_n;
+  float m = -INFINITY;
+  for (int j = 0; j < tiles_n; ++j) m = fmaxf(m, st[j].x);
+  const float m0 = (m - m != 0.f) ? 0.f : m;
+  float sum = 0.f;
+  for (int j = 0; j < tiles_n; ++j) {
+    const float2 q = st[j];
+    const float base = (q.x - q.x != 0.f) ? 0.f : q.x;  // what the tile's sum was taken against
+    sum += q.y * __expf(base - m0);
+  }
+  const float l = logf(sum) + m0;
+  const long long bt = row / R;
+  const int k = (int)(row % R), b = (int)(bt / T);
+  const int y = band_symbol(symbols, ranges, b, (size_t)row, k, S, blank, C);
+  const float *x = logits + (size_t)row * C;
+  lse[row] = l;
+  pxb[row] = x[y] - l;
+  pyb[row] = x[blank] - l;
+}
+
+// per row (b, t, k): the gradients that reach its two band entries from the lattices
+// (the inverse of band_to_lattice_kernel), and the largest |gx| + |gy| of each CTA's rows
+__global__ void __launch_bounds__(256)
+band_grad_kernel(const float *__restrict__ g_px, const float *__restrict__ g_py,
+                 const int64_t *__restrict__ ranges, const int64_t *__restrict__ boundary,
+                 float *__restrict__ gxb, float *__restrict__ gyb, float *__restrict__ part,
+                 long long rows, int T, int R, int S, int rnnt_type) {
+  __shared__ float sm[8];
+  const int S1 = S + 1;
+  const int T1 = (rnnt_type == FRNNT_REGULAR) ? T + 1 : T;
+  float mx = 0.f;
+  for (long long row = (long long)blockIdx.x * 256 + threadIdx.x; row < rows; row += (long long)gridDim.x * 256) {
+    const long long bt = row / R;
+    const int k = (int)(row % R);
+    const int b = (int)(bt / T), t = (int)(bt % T);
+    const int s = band_row(ranges, (size_t)bt, R, k, S1);
+    float gx = 0.f, gy = g_py[((size_t)b * S1 + s) * T + t];
+    const bool masked = rnnt_type == FRNNT_REGULAR && boundary != nullptr &&
+                        (long long)t == (long long)boundary[4 * b + 3];
+    if (s < S && !masked) gx = g_px[((size_t)b * S + s) * T1 + t];
+    if (rnnt_type == FRNNT_CONSTRAINED && s >= 1) gy += g_px[((size_t)b * S + s - 1) * T1 + t];
+    gxb[row] = gx;
+    gyb[row] = gy;
+    mx = fmaxf(mx, fabsf(gx) + fabsf(gy));
+  }
+  mx = warp_max(mx);
+  if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = mx;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w) mx = fmaxf(mx, sm[w]);
+    part[blockIdx.x] = mx;
+  }
+}
+
+// g[row][c] = -(gx + gy) * exp(logit - lse) + gx * [c == symbol] + gy * [c == blank], written
+// as planes (|g| <= |gx| + |gy|, whose maximum sets the scale); one warp per row.  Column
+// sums of g (the bias gradient): every warp adds its rows into its own row of a shared
+// array, lane <-> fixed columns, the warps' rows are added in order at the end -> one
+// partial per CTA, no atomics.
+__global__ void __launch_bounds__(32 * kRowWarps)
+lsm_backward_pairs_kernel(const float *__restrict__ logits, const int64_t *__restrict__ symbols,
+                          const int64_t *__restrict__ ranges, const float *__restrict__ lse,
+                          const float *__restrict__ gxb, const float *__restrict__ gyb,
+                          const float *__restrict__ gmax_part, int nparts, __half *__restrict__ g_hi,
+                          __half *__restrict__ g_lo, float *__restrict__ cs_part,
+                          float *__restrict__ scales, long long rows, int T, int R, int S, int C,
+                          int Cp, int blank, int warps_used) {
+  extern __shared__ __align__(16) float cs[];  // [warps_used][C]   (C is a multiple of 4)
+  __shared__ float slot;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const float scale = fp16_pair_scale(block_max_of_partials(gmax_part, nparts, &slot));
+  if (blockIdx.x == 0 && threadIdx.x == 0) scales[kScaleG] = 1.f / scale;
+  for (int i = threadIdx.x; i < warps_used * C; i += blockDim.x) cs[i] = 0.f;
+  __syncthreads();
+  if (warp < warps_used) {
+    float4 *mine = reinterpret_cast<float4 *>(cs + (size_t)warp * C);
+    const long long warp0 = (long long)blockIdx.x * warps_used + warp;
+    const long long nwarps = (long long)gridDim.x * warps_used;
+    const int nvec = C / 4;
+    for (long long row = warp0; row < rows; row += nwarps) {
+      const long long bt = row / R;
+      const int k = (int)(row % R), b = (int)(bt / T);
+      const float gx = gxb[row], gy = gyb[row];
+      const int y = band_symbol(symbols, ranges, b, (size_t)row, k, S, blank, C);
+      const float l = lse[row];
+      const float neg = -(gx + gy);
+      const float4 *src = reinterpret_cast<const float4 *>(logits + (size_t)row * C);
+      uint2 *dh = reinterpret_cast<uint2 *>(g_hi + (size_t)row * Cp);
+      uint2 *dl = reinterpret_cast<uint2 *>(g_lo + (size_t)row * Cp);
+      for (int v = lane; v < nvec; v += 32) {
+        const float4 q = src[v];
+        const float x[4] = {q.x, q.y, q.z, q.w};
+        float g[4];
+        __align__(8) __half hi[4], lo[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int c = v * 4 + e;
+          float gg = neg * __expf(x[e] - l);
+          if (c == y) gg += gx;
+          if (c == blank) gg += gy;
+          g[e] = gg;
+          fp16_pair(gg, scale, hi[e], lo[e]);
+        }
+        dh[v] = *reinterpret_cast<const uint2 *>(hi);
+        dl[v] = *reinterpret_cast<const uint2 *>(lo);
+        float4 a = mine[v];
+        a.x += g[0], a.y += g[1], a.z += g[2], a.w += g[3];
+        mine[v] = a;
+      }
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float acc = 0.f;
+    for (int w = 0; w < warps_used; ++w) acc += cs[(size_t)w * C + c];
+    cs_part[(size_t)blockIdx.x * C + c] = acc;
+  }
+}
+
+static int pjl_check(int B, int T, int R, int S, int C, int D, int blank, int rnnt_type) {
+  FRNNT_REQUIRE(B >= 0 && T >= 0 && R >= 1 && S >= 0 && C >= 1 && D >= 1, FRNNT_EINVAL,
+                "bad sizes B=%d T=%d R=%d S=%d C=%d D=%d", B, T, R, S, C, D);
+  FRNNT_REQUIRE(R <= S + 1, FRNNT_EINVAL, "band width R=%d exceeds S+1=%d", R, S + 1);
+  FRNNT_REQUIRE(blank >= 0 && blank < C, FRNNT_EINVAL, "blank=%d outside [0,%d)", blank, C);
+  FRNNT_REQUIRE(rnnt_type >= 0 && rnnt_type <= 2, FRNNT_EINVAL, "bad rnnt_type %d", rnnt_type);
+  FRNNT_REQUIRE(D % 8 == 0 && C % 4 == 0, FRNNT_EUNSUPPORTED,
+                "the fused joiner needs D (=%d) to be a multiple of 8 and C (=%d) a multiple of 4", D, C);
+  FRNNT_REQUIRE(S + 1 <= 65535 && B <= 65535, FRNNT_EUNSUPPORTED, "S or B too large for the grid");
+  FRNNT_REQUIRE((long long)B * T * R < (1LL << 31) - 256, FRNNT_EUNSUPPORTED,
+                "more than 2^31 joiner rows");
+  return FRNNT_OK;
+}
+
+static int parts_for(long long n) {
+  long long want = (n + 255) / 256;
+  return (int)(want < 1 ? 1 : (want < kMaxParts ? want : kMaxParts));
+}
+
+}  // namespace frnnt
+
+using namespace frnnt;
+
+extern "C" size_t frnnt_pruned_joiner_saved_bytes(int B, int T, int R, int S, int C, int D) {
+  if (B <= 0 || T <= 0 || R <= 0 || C <= 0 || D <= 0) return 0;
+  return pjl_layout(B, T, R, S + 1, C, D).saved_bytes;
+}
+extern "C" size_t frnnt_pruned_joiner_forward_scratch_bytes(int B, int T, int R, int S, int C, int D) {
+  if (B <= 0 || T <= 0 || R <= 0 || C <= 0 || D <= 0) return 0;
+  return pjl_layout(B, T, R, S + 1, C, D).fwd_bytes;
+}
+extern "C" size_t frnnt_pruned_joiner_backward_scratch_bytes(int B, int T, int R, int S, int C, int D) {
+  if (B <= 0 || T <= 0 || R <= 0 || C <= 0 || D <= 0) return 0;
+  return pjl_layout(B, T, R, S + 1, C, D).bwd_bytes;
+}
+
+extern "C" int frnnt_pruned_joiner_logprobs_forward(const float *enc, const float *dec,
+                                                    const int64_t *ranges, const float *weight,
+                                                    const float *bias, const int64_t *symbols,
+                                                    const int64_t *boundary, float *px, float *py,
+                                                    void *saved, void *scratch, int B, int T, int R,
+                                                    int S, int C, int D, int blank, int rnnt_type,
+                                                    void *stream) {
+  int rc = pjl_check(B, T, R, S, C, D, blank, rnnt_type);
+  if (rc != FRNNT_OK) return rc;
+  if (B == 0 || T == 0) return FRNNT_OK;
+  FRNNT_REQUIRE(enc && dec && ranges && weight && px && py && saved && scratch && (symbols || S == 0),
+                FRNNT_EINVAL, "NULL argument");
+  FRNNT_REQUIRE((uintptr_t)enc % 16 == 0 && (uintptr_t)dec % 16 == 0 && (uintptr_t)saved % 256 == 0 &&
+                    (uintptr_t)scratch % 256 == 0,
+                FRNNT_EINVAL, "enc / dec must be 16-byte aligned, saved / scratch 256-byte aligned");
+  const PjlLayout L = pjl_layout(B, T, R, S + 1, C, D);
+  cudaStream_t st = (cudaStream_t)stream;
+  uint8_t *sv = (uint8_t *)saved, *sc = (uint8_t *)scratch;
+  __half *act_hi = (__half *)(sv + L.act_hi), *act_lo = (__half *)(sv + L.act_lo);
+  __half *wt_hi = (__half *)(sv + L.wt_hi), *wt_lo = (__half *)(sv + L.wt_lo);
+  __half *w_hi = (__half *)(sc + L.w_hi), *w_lo = (__half *)(sc + L.w_lo);
+  float *logits = (float *)(sv + L.logits), *lse = (float *)(sv + L.lse), *scales = (float *)(sv + L.scales);
+  float2 *stats = (float2 *)(sc + L.stats);
+  float *pxb = (float *)(sc + L.pxb), *pyb = (float *)(sc + L.pyb), *amax = (float *)(sc + L.amax_part);
+  const long long rows = (long long)L.M;
+  const int M = (int)rows;
+
+  // tensor maps first: nothing has been launched if one of them is refused
+  CUtensorMap mah, mal, mbh, mbl;
+  rc = make_pair_map(&mah, act_hi, M, D, D, false);
+  if (rc == FRNNT_OK) rc = make_pair_map(&mal, act_lo, M, D, D, false);
+  if (rc == FRNNT_OK) rc = make_pair_map(&mbh, w_hi, C, D, D, false);
+  if (rc == FRNNT_OK) rc = make_pair_map(&mbl, w_lo, C, D, D, false);
+  if (rc != FRNNT_OK) return rc;
+
+  const long long nW = (long long)C * D;
+  const int wparts = parts_for(nW);
+  FRNNT_KERNEL(absmax_partial_kernel<<<wparts, 256, 0, st>>>(weight, nW, amax));
+  FRNNT_KERNEL(split_weights_kernel<<<wparts, 256, 0, st>>>(weight, C, D, (int)L.Cp, amax, wparts, w_hi, w_lo,
+                                                           wt_hi, wt_lo, scales));
+  {
+    long long want = (rows + 7) / 8;
+    const int grid = (int)(want < (long long)sm_count() * 32 ? want : (long long)sm_count() * 32);
+    FRNNT_KERNEL(pruned_tanh_pairs_kernel<<<grid, 256, 0, st>>>(enc, dec, ranges, act_hi, act_lo, rows, R,
+                                                               T * R, S + 1, D, scales));
+  }
+  FRNNT_CUDA(cudaGetLastError());
+  const int mt = (M + kPairTile - 1) / kPairTile;
+  const LinShape shape{M, C, D, ((D + kPairBK - 1) / kPairBK) * kPairBK, mt, L.tiles_n, 1};
+  rc = launch_pair_umma<false, false>(mah, mal, mbh, mbl, shape,
+                                      PjlFwdExt{logits, bias, stats, scales, C, L.tiles_n}, st);
+  if (rc != FRNNT_OK) return rc;
+  FRNNT_KERNEL(joiner_band_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(
+      logits, stats, symbols, ranges, lse, pxb, pyb, rows, T, R, S, C, blank, L.tiles_n));
+  dim3 grid2((unsigned)((T + 1 + 127) / 128), (unsigned)(S + 1), (unsigned)B);
+  FRNNT_KERNEL(band_to_lattice_kernel<float><<<grid2, 128, 0, st>>>(pxb, pyb, ranges, boundary, px, py, S, T, R,
+                                                                   rnnt_type));
+  FRNNT_CUDA(cudaGetLastError());
+  return FRNNT_OK;
+}
+
+extern "C" int frnnt_pruned_joiner_logprobs_backward(const float *px_grad, const float *py_grad,
+                                                     const int64_t *ranges, const int64_t *symbols,
+                                                     const int64_t *boundary, void *saved,
+                                                     void *scratch, float *enc_grad, float *dec_grad,
+                                                     float *weight_grad, float *bias_grad, int B, int T,
+                                                     int R, int S, int C, int D, int blank, int rnnt_type,
+                                                     void *stream) {
+  int rc = pjl_check(B, T, R, S, C, D, blank, rnnt_type);
+  if (rc != FRNNT_OK) return rc;
+  if (B == 0 || T == 0) return FRNNT_OK;
+  FRNNT_REQUIRE(py_grad && ranges && saved && scratch && (px_grad || S == 0) && (symbols || S == 0),
+                FRNNT_EINVAL, "NULL argument");
+  FRNNT_REQUIRE((enc_grad == nullptr) == (dec_grad == nullptr), FRNNT_EINVAL,
+                "enc_grad and dec_grad are computed together: pass both or neither");
+  FRNNT_REQUIRE((uintptr_t)saved % 256 == 0 && (uintptr_t)scratch % 256 == 0 &&
+                    (uintptr_t)enc_grad % 16 == 0 && (uintptr_t)dec_grad % 16 == 0 &&
+                    (uintptr_t)weight_grad % 16 == 0,
+                FRNNT_EINVAL, "misaligned buffer");
+  const PjlLayout L = pjl_layout(B, T, R, S + 1, C, D);
+  cudaStream_t st = (cudaStream_t)stream;
+  uint8_t *sv = (uint8_t *)saved, *sc = (uint8_t *)scratch;
+  const __half *act_hi = (const __half *)(sv + L.act_hi), *act_lo = (const __half *)(sv + L.act_lo);
+  const __half *wt_hi = (const __half *)(sv + L.wt_hi), *wt_lo = (const __half *)(sv + L.wt_lo);
+  const float *logits = (const float *)(sv + L.logits), *lse = (const float *)(sv + L.lse);
+  float *scales = (float *)(sv + L.scales);  // slot kScaleG is written here
+  __half *g_hi = (__half *)(sc + L.g_hi), *g_lo = (__half *)(sc + L.g_lo);
+  float *gz = (float *)(sc + L.gz), *gxb = (float *)(sc + L.gxb), *gyb = (float *)(sc + L.gyb);
+  float *gmax = (float *)(sc + L.gmax_part), *dw_part = (float *)(sc + L.dw_part);
+  float *cs_part = (float *)(sc + L.cs_part);
+  const long long rows = (long long)L.M;
+  const int M = (int)rows, Cp = (int)L.Cp;
+
+  CUtensorMap gih, gil, wth, wtl, gwh, gwl, ach, acl;
+  rc = make_pair_map(&gih, g_hi, M, C, Cp, false);                    // grad-input: A = g, K = C
+  if (rc == FRNNT_OK) rc = make_pair_map(&gil, g_lo, M, C, Cp, false);
+  if (rc == FRNNT_OK) rc = make_pair_map(&wth, wt_hi, D, C, Cp, false);   // B = W^T planes [D][C]
+  if (rc == FRNNT_OK) rc = make_pair_map(&wtl, wt_lo, D, C, Cp, false);
+  if (rc == FRNNT_OK) rc = make_pair_map(&gwh, g_hi, M, C, Cp, true);     // grad-weight: K = rows
+  if (rc == FRNNT_OK) rc = make_pair_map(&gwl, g_lo, M, C, Cp, true);
+  if (rc == FRNNT_OK) rc = make_pair_map(&ach, act_hi, M, D, D, true);
+  if (rc == FRNNT_OK) rc = make_pair_map(&acl, act_lo, M, D, D, true);
+  if (rc != FRNNT_OK) return rc;
+
+  const int gparts = parts_for(rows);
+  FRNNT_KERNEL(band_grad_kernel<<<gparts, 256, 0, st>>>(px_grad, py_grad, ranges, boundary, gxb, gyb, gmax,
+                                                       rows, T, R, S, rnnt_type));
+  {
+    // as many warps per CTA as have room for their column sums in shared memory
+    int warps_used = kRowWarps;
+    while (warps_used > 1 && (size_t)warps_used * C * 4 > 160 * 1024) --warps_used;
+    FRNNT_REQUIRE((size_t)warps_used * C * 4 <= 200 * 1024, FRNNT_EUNSUPPORTED, "C=%d too large", C);
+    const size_t smem = (size_t)warps_used * C * 4;
+    auto kern = lsm_backward_pairs_kernel;
+    FRNNT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    FRNNT_KERNEL(kern<<<L.cs_ctas, 32 * kRowWarps, smem, st>>>(logits, symbols, ranges, lse, gxb, gyb, gmax, gparts,
+                                                             g_hi, g_lo, cs_part, scales, rows, T, R, S, C,
+                                                             Cp, blank, warps_used));
+  }
+  FRNNT_CUDA(cudaGetLastError());
+  if (bias_grad != nullptr) {
+    FRNNT_KERNEL(ordered_sum_kernel<<<(unsigned)((C + 255) / 256), 256, 0, st>>>(cs_part, bias_grad, C, L.cs_ctas));
+    FRNNT_CUDA(cudaGetLastError());
+  }
+  const int mt = (M + kPairTile - 1) / kPairTile;
+  if (enc_grad != nullptr) {
+    const LinShape shape{M, D, C, ((C + kPairBK - 1) / kPairBK) * kPairBK, mt, (D + kPairTile - 1) / kPairTile, 1};
+    rc = launch_pair_umma<false, false>(gih, gil, wth, wtl, shape, PjlGradInExt{gz, act_hi, act_lo, scales, D}, st);
+    if (rc != FRNNT_OK) return rc;
+    if (D % 4 == 0 && D <= 3200) {
+      rc = frnnt_joiner_input_grads(gz, ranges, enc_grad, dec_grad, sc + L.jg, B, S + 1, T, R, D, stream);
+    } else {
+      rc = frnnt_sum_over_range(FRNNT_F32, gz, enc_grad, (long long)B * T, R, D, stream);
+      if (rc == FRNNT_OK)
+        rc = frnnt_prune_gather_backward(FRNNT_F32, gz, ranges, dec_grad, B, S + 1, T, R, D, stream);
+    }
+    if (rc != FRNNT_OK) return rc;
+  }
+  if (weight_grad != nullptr) {
+    const int splits = L.splits;
+    const long long kblocks = (rows + kPairBK - 1) / kPairBK;
+    const int k_per_split = (int)((kblocks + splits - 1) / splits) * kPairBK;
+    const LinShape shape{C, D, M, k_per_split, (C + kPairTile - 1) / kPairTile, (D + kPairTile - 1) / kPairTile,
+                         splits};
+    float *out = splits == 1 ? weight_grad : dw_part;
+    rc = launch_pair_umma<true, true>(gwh, gwl, ach, acl, shape, PjlGradWExt{out, scales, C, D}, st);
+    if (rc != FRNNT_OK) return rc;
+    if (splits > 1) {
+      const long long n = (long long)C * D;
+      FRNNT_KERNEL(ordered_sum_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(dw_part, weight_grad, n, splits));
+      FRNNT_CUDA(cudaGetLastError());
+    }
+  }
+  return FRNNT_OK;
+}

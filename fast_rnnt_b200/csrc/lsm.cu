@@ -18,6 +18,7 @@
 //   g[row][c] = -(gx+gy) * exp(logit - lse) + gx*[c == symbol] + gy*[c == blank]
 //   with gx, gy picked out of the lattice gradients by the inverse placement.
 #include "common.cuh"
+#include "lsm_band.cuh"
 
 namespace frnnt {
 
@@ -47,24 +48,6 @@ __device__ __forceinline__ void set_elem(double &v, int, double x) { v = x; }
 
 constexpr int kRowCta = 256;  // threads per CTA of the row kernels
 constexpr int kRowCache = 8;  // vectors a thread keeps in registers
-
-// Lattice row of band entry k at frame (b, t).
-__device__ __forceinline__ int band_row(const int64_t *ranges, size_t bt, int R, int k, int S1) {
-  if (ranges == nullptr) return k;
-  long long s = (long long)ranges[bt * R] + k;
-  s %= S1;
-  if (s < 0) s += S1;
-  return (int)s;
-}
-
-// Symbol whose log-prob goes to px for band entry (b, t, k).
-__device__ __forceinline__ int band_symbol(const int64_t *symbols, const int64_t *ranges, int b,
-                                           size_t row, int k, int S, int blank, int C) {
-  long long r = ranges ? (long long)ranges[row] : k;
-  long long y = (r >= 0 && r < S) ? (long long)symbols[(size_t)b * S + r] : blank;
-  if (y < 0 || y >= C) y = blank;  // never index outside the row
-  return (int)y;
-}
 
 template <typename real, int GROUP>
 __device__ __forceinline__ real group_reduce(real v, bool is_max, real *scratch, int gid, int lane_in_group) {
@@ -158,49 +141,6 @@ lsm_rows_forward_kernel(const real *__restrict__ logits, const int64_t *__restri
       pxb[row] = x[y] - l;
       pyb[row] = x[blank] - l;
     }
-  }
-}
-
-// Stage 2: bands -> lattices.
-template <typename real>
-__global__ void band_to_lattice_kernel(const real *__restrict__ pxb, const real *__restrict__ pyb,
-                                       const int64_t *__restrict__ ranges,
-                                       const int64_t *__restrict__ boundary, real *__restrict__ px,
-                                       real *__restrict__ py, int S, int T, int R, int rnnt_type) {
-  const int b = blockIdx.z, s = blockIdx.y;
-  const int t = blockIdx.x * blockDim.x + threadIdx.x;
-  const int S1 = S + 1;
-  const int T1 = (rnnt_type == FRNNT_REGULAR) ? T + 1 : T;
-  if (t > T) return;
-  const real ninf = neg_inf<real>();
-  real vy = ninf, vx = ninf, vy_next = ninf;
-  if (t < T) {
-    const size_t bt = (size_t)b * T + t;
-    long long shift = ranges ? (long long)ranges[bt * R] : 0;
-    shift %= S1;
-    if (shift < 0) shift += S1;
-    int k = s - (int)shift;
-    if (k < 0) k += S1;
-    if (k < R) {
-      vy = pyb[bt * R + k];
-      vx = pxb[bt * R + k];
-    }
-    if (rnnt_type == FRNNT_CONSTRAINED && s < S) {
-      int k1 = s + 1 - (int)shift;
-      if (k1 < 0) k1 += S1;
-      if (k1 >= S1) k1 -= S1;
-      if (k1 < R) vy_next = pyb[bt * R + k1];
-    }
-    py[((size_t)b * S1 + s) * T + t] = vy;
-  }
-  if (s < S && t < T1) {
-    if (rnnt_type == FRNNT_REGULAR) {
-      if (t == T) vx = ninf;
-      if (boundary != nullptr && (long long)t == (long long)boundary[4 * b + 3]) vx = ninf;
-    } else if (rnnt_type == FRNNT_CONSTRAINED) {
-      vx = vx + vy_next;
-    }
-    px[((size_t)b * S + s) * T1 + t] = vx;
   }
 }
 

@@ -1,0 +1,379 @@
+// The second tensor-core product engine of this library (sm_100a): D = A * B^T-like
+// products whose operands are already stored as PAIRS OF HALF-PRECISION PLANES,
+// x * 2^e ~= hi + lo with hi = fp16(x * 2^e) and lo = fp16(x * 2^e - hi).  An fp16 value
+// carries an 11-bit significand like a tf32 value, so hi*hi + hi*lo + lo*hi has the
+// accuracy of the 3xTF32 scheme (22 bits per operand) -- but kind::f16 MMAs run at twice
+// the tf32 rate on half the operand bytes, and because the producers of the operands
+// (the tanh kernel, the log-softmax backward, a small pass over the weights) write the
+// planes themselves, nothing has to be split inside this kernel: it is a pure
+// TMA -> tcgen05.mma pipeline with both operands read from shared memory.
+//
+// fp16 has a 5-bit exponent; the power-of-two scale 2^e of every operand is chosen by
+// its producer so that the largest magnitude lands in [2^14, 2^15).  Values down to
+// 2^-18 of the largest keep all 22 bits, smaller ones an absolute error of 2^-40 of the
+// largest (see fp16_pair()).  The scales are undone in the epilogue (exactly).
+//
+// Kernel structure (one 128x128 output tile per work item, 6 warps, one persistent CTA
+// per SM):
+//   warp 0   : TMA producer.  Per 64-wide K slice four 16 KB boxes (A hi, A lo, B hi, B lo)
+//              land in 128-byte-swizzled tiles; 3-stage ring; rows / columns outside the
+//              matrices arrive as zeros.  K-major operands (rows = M or N index): one box
+//              of 64 k x 128 rows.  Operands that are contiguous along M / N (rows = k
+//              index): two boxes of 64 values x 64 k rows.
+//   warp 1   : one thread issues, per K = 16 step, hi*hi, hi*lo, lo*hi into a 128x128 fp32
+//              accumulator in tensor memory.  The tensor core adds into its accumulator
+//              with truncation, so every 128-wide K group gets a fresh accumulator and
+//   warps 2-5 fold finished groups into a running sum with round-to-nearest adds
+//              (tcgen05.ld / add / tcgen05.st), one group behind the MMAs, and run the
+//              epilogue while the other warps are already on the next item.
+// No multicast, no clusters.  Every wait is bounded; a timeout poisons the tile with NaN.
+//
+// Policy ("Ext") interface, all __device__:
+//   struct Row;                                    per-row state across one tile's columns
+//   void row_begin(Row &, int z, int m, int n0) const;
+//   void finish(Row &, int z, int m, int n, float (&v)[16]) const;   columns n..n+15 of
+//                                                  row m, in place; only columns < N count
+//   void row_end(Row &, int z, int m, int n0) const;
+//   float *out_row(int z, int m) const;            where row m of the result goes
+#pragma once
+#include <cuda_fp16.h>
+
+#include "umma_linear.cuh"
+
+namespace frnnt {
+
+constexpr int kPairThreads = 192;  // TMA warp, MMA warp, 4 fold / epilogue warps
+constexpr int kPairFolders = 4;
+constexpr int kPairTile = 128;
+constexpr int kPairBK = 64;        // K slice: 128 bytes of fp16 per row
+constexpr int kPairStages = 3;
+constexpr int kPairGroup = 2;      // K slices per accumulator group (128 values of K)
+constexpr uint32_t kPairOpBytes = kPairTile * 128;       // one plane of one operand tile
+constexpr uint32_t kPairStageBytes = 4 * kPairOpBytes;   // A hi, A lo, B hi, B lo
+constexpr size_t kPairSmemBytes = (size_t)kPairStages * kPairStageBytes + 1024;
+// tensor-memory columns: two group accumulators and the running sum
+constexpr uint32_t kPairCols = 512, kPairAcc1 = 128, kPairRun = 256;
+
+// x * scale as a pair of fp16 values.  |x * scale| must stay below 65504.  hi has 11
+// significant bits; lo = fp16(x * scale - hi) is exact to 11 more bits while it is a
+// normal fp16 number (|x * scale| >= 2^-3), below that to half a subnormal step, 2^-25.
+__device__ __forceinline__ void fp16_pair(float x, float scale, __half &hi, __half &lo) {
+  const float xs = x * scale;
+  hi = __float2half_rn(xs);
+  lo = __float2half_rn(xs - __half2float(hi));
+}
+
+// power-of-two scale that brings a largest magnitude `amax` into [2^14, 2^15); 1 when
+// amax is zero or not finite (then the data decides the result anyway)
+__device__ __forceinline__ float fp16_pair_scale(float amax) {
+  if (!(amax > 0.f) || amax - amax != 0.f) return 1.f;
+  int e;
+  frexpf(amax, &e);  // amax = m * 2^e, m in [0.5, 1)
+  e = 15 - e;        // amax * 2^(15 - e) in [2^14, 2^15)
+  e = e > 100 ? 100 : (e < -100 ? -100 : e);
+  return ldexpf(1.f, e);
+}
+
+__host__ __device__ inline uint32_t idesc_f16(int M, int N, bool a_mn_major, bool b_mn_major) {
+  uint32_t d = 0;
+  d |= 1u << 4;  // D format: F32; A and B formats: 0 = F16
+  d |= (a_mn_major ? 1u : 0u) << 15;
+  d |= (b_mn_major ? 1u : 0u) << 16;
+  d |= (uint32_t)(N >> 3) << 17;
+  d |= (uint32_t)(M >> 4) << 24;
+  return d;
+}
+
+// D[tmem] (+)= A[smem] * B[smem], fp16 operands, fp32 accumulation; issued by ONE thread
+__device__ __forceinline__ void mma_f16_ss(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+struct PairTile {
+  int m0, n0, z, KB, k_begin;
+};
+// work item w -> (z, m tile, n tile); the n tiles of one m tile are neighbours, so the
+// CTAs that run at the same time share their A rows in L2
+__device__ __forceinline__ PairTile pair_tile(const LinShape &p, int w) {
+  PairTile t;
+  const int per_z = p.tiles_m * p.tiles_n;
+  t.z = w / per_z;
+  const int r = w - t.z * per_z;
+  t.m0 = (r / p.tiles_n) * kPairTile;
+  t.n0 = (r % p.tiles_n) * kPairTile;
+  t.k_begin = t.z * p.k_per_split;
+  const int k_end = min(p.K, t.k_begin + p.k_per_split);
+  t.KB = k_end > t.k_begin ? (k_end - t.k_begin + kPairBK - 1) / kPairBK : 0;
+  return t;
+}
+
+template <bool A_MN, bool B_MN, class Ext>
+__global__ void __launch_bounds__(kPairThreads, 1)
+pair_umma_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constant__ CUtensorMap map_alo,
+                 const __grid_constant__ CUtensorMap map_bhi, const __grid_constant__ CUtensorMap map_blo,
+                 LinShape p, Ext ext) {
+  extern __shared__ uint8_t smem_dyn[];
+  __shared__ __align__(8) uint64_t bar_full[kPairStages];   // TMA bytes have landed
+  __shared__ __align__(8) uint64_t bar_empty[kPairStages];  // the MMAs are done with the stage
+  __shared__ __align__(8) uint64_t bar_grp[2];              // a group's accumulator is complete
+  __shared__ __align__(8) uint64_t bar_fold[2];             // ... and has been folded away
+  __shared__ uint32_t tmem_slot;
+  __shared__ int failed;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_items = p.tiles_m * p.tiles_n * p.nz;
+  const uint32_t tiles = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+
+  if (tid == 0) {
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(&bar_full[s], 1);
+      mbar_init(&bar_empty[s], 1);
+    }
+    for (int r = 0; r < 2; ++r) {
+      mbar_init(&bar_grp[r], 1);
+      mbar_init(&bar_fold[r], kPairFolders);
+    }
+    failed = 0;
+    mbar_init_fence();
+  }
+  if (warp == 1) tmem_alloc(&tmem_slot, kPairCols);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_d = tmem_slot;
+  volatile int *vfailed = &failed;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int it = 0;  // K slices issued so far, over all items
+      for (int w = blockIdx.x; w < n_items && !*vfailed; w += gridDim.x) {
+        const PairTile t = pair_tile(p, w);
+        for (int kb = 0; kb < t.KB && !*vfailed; ++kb, ++it) {
+          const int s = it % kPairStages;
+          if (it >= kPairStages && !mbar_wait(&bar_empty[s], (uint32_t)((it / kPairStages - 1) & 1))) {
+            *vfailed = 1;
+            break;
+          }
+          const int k0 = t.k_begin + kb * kPairBK;
+          const uint32_t st = tiles + (uint32_t)s * kPairStageBytes;
+          mbar_expect_tx(&bar_full[s], kPairStageBytes);
+          if (A_MN) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              tma_load_2d(st + j * 8192, &map_ahi, t.m0 + 64 * j, k0, &bar_full[s]);
+              tma_load_2d(st + kPairOpBytes + j * 8192, &map_alo, t.m0 + 64 * j, k0, &bar_full[s]);
+            }
+          } else {
+            tma_load_2d(st, &map_ahi, k0, t.m0, &bar_full[s]);
+            tma_load_2d(st + kPairOpBytes, &map_alo, k0, t.m0, &bar_full[s]);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              tma_load_2d(st + 2 * kPairOpBytes + j * 8192, &map_bhi, t.n0 + 64 * j, k0, &bar_full[s]);
+              tma_load_2d(st + 3 * kPairOpBytes + j * 8192, &map_blo, t.n0 + 64 * j, k0, &bar_full[s]);
+            }
+          } else {
+            tma_load_2d(st + 2 * kPairOpBytes, &map_bhi, k0, t.n0, &bar_full[s]);
+            tma_load_2d(st + 3 * kPairOpBytes, &map_blo, k0, t.n0, &bar_full[s]);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = idesc_f16(kPairTile, kPairTile, A_MN, B_MN);
+      // a K = 16 step inside a tile: 32 bytes along a K-major row, or two 8-row atoms
+      // (2048 bytes) of a tile whose rows run along M / N; LBO = next block of 64
+      // M / N values (only the latter layout uses it), SBO = next group of 8 rows
+      constexpr uint32_t a_step = A_MN ? 2048u : 32u, b_step = B_MN ? 2048u : 32u;
+      constexpr uint32_t a_lbo = A_MN ? 8192u : 16u, b_lbo = B_MN ? 8192u : 16u;
+      int it = 0, gg = 0;  // K slices and accumulator groups so far, over all items
+      for (int w = blockIdx.x; w < n_items && !*vfailed; w += gridDim.x) {
+        const PairTile t = pair_tile(p, w);
+        for (int kb = 0; kb < t.KB && !*vfailed; ++kb, ++it) {
+          const int s = it % kPairStages;
+          const bool group_start = kb % kPairGroup == 0;
+          // this accumulator was last used two groups ago: it must have been folded away
+          if (group_start && gg >= 2 && !mbar_wait(&bar_fold[gg & 1], (uint32_t)(((gg - 2) >> 1) & 1))) {
+            *vfailed = 1;
+            break;
+          }
+          if (!mbar_wait(&bar_full[s], (uint32_t)((it / kPairStages) & 1))) {
+            *vfailed = 1;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t acc = tmem_d + ((gg & 1) ? kPairAcc1 : 0u);
+          const uint32_t st = tiles + (uint32_t)s * kPairStageBytes;
+#pragma unroll
+          for (int ks = 0; ks < kPairBK / 16; ++ks) {
+            const uint64_t dah = smem_desc_sw128(st + ks * a_step, a_lbo, 1024u);
+            const uint64_t dal = smem_desc_sw128(st + kPairOpBytes + ks * a_step, a_lbo, 1024u);
+            const uint64_t dbh = smem_desc_sw128(st + 2 * kPairOpBytes + ks * b_step, b_lbo, 1024u);
+            const uint64_t dbl = smem_desc_sw128(st + 3 * kPairOpBytes + ks * b_step, b_lbo, 1024u);
+            mma_f16_ss(acc, dah, dbh, idesc, (!group_start || ks > 0) ? 1u : 0u);
+            mma_f16_ss(acc, dah, dbl, idesc, 1u);
+            mma_f16_ss(acc, dal, dbh, idesc, 1u);
+          }
+          mma_commit(&bar_empty[s]);
+          if (kb % kPairGroup == kPairGroup - 1 || kb == t.KB - 1) {
+            mma_commit(&bar_grp[gg & 1]);
+            ++gg;
+          }
+        }
+      }
+    }
+  } else {
+    // ---- fold finished groups into the running sum, then the epilogue -------------------------
+    const int quarter = warp & 3;  // tensor-memory lanes 32*quarter..
+    const uint32_t lane_base = (uint32_t)(32 * quarter) << 16;
+    const uint32_t run = tmem_d + lane_base + kPairRun;
+    const bool vec = (p.N % 4) == 0;
+    bool ok = true;
+    int gg = 0;
+    for (int w = blockIdx.x; w < n_items; w += gridDim.x) {
+      const PairTile t = pair_tile(p, w);
+      const int NG = (t.KB + kPairGroup - 1) / kPairGroup;
+      const int m = t.m0 + 32 * quarter + lane;
+      const bool row_ok = m < p.M;
+      float *out = row_ok ? ext.out_row(t.z, m) : nullptr;
+      typename Ext::Row rs;
+      if (row_ok) ext.row_begin(rs, t.z, m, t.n0);
+      for (int g = 0; g < NG && ok; ++g, ++gg) {
+        if (!mbar_wait(&bar_grp[gg & 1], (uint32_t)((gg >> 1) & 1))) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t acc = tmem_d + lane_base + ((gg & 1) ? kPairAcc1 : 0u);
+        if (g + 1 < NG) {
+          // 32 columns at a time: both loads in flight, one wait; the stores drain behind
+          for (int c = 0; c < kPairTile; c += 32) {
+            float pv[32], rv[32];
+            tmem_ld32_nowait(acc + c, pv);
+            if (g > 0) tmem_ld32_nowait(run + c, rv);
+            tmem_ld_wait();
+            if (g > 0) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) pv[i] = rv[i] + pv[i];
+            }
+            tmem_st32_nowait(run + c, pv);
+          }
+          tmem_st_wait();
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bar_fold[gg & 1]);
+        } else {
+          // the last group is added on its way out: running sum + accumulator -> epilogue
+          ok = __all_sync(0xffffffffu, ok) && !*vfailed;
+          for (int c0 = 0; c0 < kPairTile; c0 += 32) {
+            float pv[32], rv[32];
+            tmem_ld32_nowait(acc + c0, pv);
+            if (g > 0) tmem_ld32_nowait(run + c0, rv);
+            tmem_ld_wait();
+            if (g > 0) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) pv[i] = rv[i] + pv[i];
+            }
+#pragma unroll
+            for (int cc = 0; cc < 2; ++cc) {
+              const int n = t.n0 + c0 + 16 * cc;
+              if (row_ok && n < p.N) {
+                float v[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[i] = pv[16 * cc + i];
+                ext.finish(rs, t.z, m, n, v);
+                if (!ok) {
+#pragma unroll
+                  for (int i = 0; i < 16; ++i) v[i] = NAN;
+                }
+                float *dst = out + n;
+                if (vec && n + 16 <= p.N) {
+#pragma unroll
+                  for (int i = 0; i < 16; i += 4)
+                    *reinterpret_cast<float4 *>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                } else {
+#pragma unroll
+                  for (int i = 0; i < 16; ++i)
+                    if (n + i < p.N) dst[i] = v[i];
+                }
+              }
+            }
+          }
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bar_fold[gg & 1]);
+        }
+      }
+      ok = __all_sync(0xffffffffu, ok) && !*vfailed;
+      if (!ok) *vfailed = 1;
+      if (t.KB == 0 || !ok) {
+        // nothing was accumulated (an empty reduction), or a wait ran out: zeros / NaN
+        for (int n = t.n0; n < t.n0 + kPairTile && n < p.N; n += 16) {
+          if (!row_ok) break;
+          float v[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = 0.f;
+          if (ok) ext.finish(rs, t.z, m, n, v);
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            if (n + i < p.N) out[n + i] = ok ? v[i] : NAN;
+        }
+      }
+      if (row_ok) ext.row_end(rs, t.z, m, t.n0);
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_d, kPairCols);
+}
+
+// ---- host -----------------------------------------------------------------------------------
+// map of a row-major fp16 matrix [rows][cols] whose rows are `pitch` halves apart; box =
+// box_cols x box_rows, 128-byte swizzle.  Elements outside [rows][cols] read as zeros.
+inline int make_map_f16(CUtensorMap *map, const void *base, int rows, int cols, long long pitch,
+                        int box_cols, int box_rows) {
+  auto enc = tensor_map_encoder();
+  FRNNT_REQUIRE(enc != nullptr, FRNNT_ECUDA, "cuTensorMapEncodeTiled is not available");
+  FRNNT_REQUIRE((uintptr_t)base % 16 == 0 && pitch % 8 == 0, FRNNT_EUNSUPPORTED,
+                "TMA needs a 16-byte aligned base and a row pitch that is a multiple of 8 halves");
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)pitch * 2};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(base), dims, strides, box,
+                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  FRNNT_REQUIRE(r == CUDA_SUCCESS, FRNNT_ECUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
+  return FRNNT_OK;
+}
+// operand plane for the engine: K-major ([M or N rows][K cols], box 64 k x 128 rows) or
+// contiguous along M / N ([K rows][M or N cols], boxes of 64 values x 64 k rows)
+inline int make_pair_map(CUtensorMap *map, const void *base, int rows, int cols, long long pitch,
+                         bool mn_major) {
+  return mn_major ? make_map_f16(map, base, rows, cols, pitch, 64, kPairBK)
+                  : make_map_f16(map, base, rows, cols, pitch, kPairBK, kPairTile);
+}
+
+template <bool A_MN, bool B_MN, class Ext>
+int launch_pair_umma(const CUtensorMap &mah, const CUtensorMap &mal, const CUtensorMap &mbh,
+                     const CUtensorMap &mbl, const LinShape &shape, const Ext &ext, cudaStream_t st) {
+  auto kern = pair_umma_kernel<A_MN, B_MN, Ext>;
+  FRNNT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPairSmemBytes));
+  int ctas = 0;
+  const int rc = lin_grid((long long)shape.tiles_m * shape.tiles_n * shape.nz, &ctas);
+  if (rc != FRNNT_OK) return rc;
+  if (ctas == 0) return FRNNT_OK;
+  FRNNT_KERNEL(kern<<<ctas, kPairThreads, kPairSmemBytes, st>>>(mah, mal, mbh, mbl, shape, ext));
+  FRNNT_CUDA(cudaGetLastError());
+  return FRNNT_OK;
+}
+
+}  // namespace frnnt

@@ -211,6 +211,95 @@ def get_rnnt_logprobs_pruned(logits: Tensor, symbols: Tensor, ranges: Tensor,
                             _RNNT_TYPES[rnnt_type])
 
 
+class _PrunedJoinerLogprobs(torch.autograd.Function):
+    """(px, py) of the pruned loss from the joiner's inputs as one autograd node
+    (csrc/joiner_pairs.cu): pruning gather + tanh, the joiner's projection and its two
+    gradient products on the tensor cores, log-softmax and symbol / blank gather."""
+
+    @staticmethod
+    def forward(ctx, enc, dec, ranges, weight, bias, symbols, boundary, blank, rnnt_type):
+        B, T, D = enc.shape
+        S = symbols.shape[1]
+        R = ranges.shape[2]
+        C = weight.shape[0]
+        dev = enc.device
+        T1 = T + 1 if rnnt_type == 0 else T
+        enc, dec, ranges, weight = _contig(enc), _contig(dec), _contig(ranges), _contig(weight)
+        bias, symbols, boundary = _contig(bias), _contig(symbols), _contig(boundary)
+        lib = _lib.lib()
+        with torch.cuda.device(dev):
+            px = torch.empty(B, S, T1, dtype=torch.float32, device=dev)
+            py = torch.empty(B, S + 1, T, dtype=torch.float32, device=dev)
+            saved = _bytes(lib.frnnt_pruned_joiner_saved_bytes(B, T, R, S, C, D), dev)
+            scratch = _bytes(lib.frnnt_pruned_joiner_forward_scratch_bytes(B, T, R, S, C, D), dev)
+            _lib.call("frnnt_pruned_joiner_logprobs_forward", _lib.ptr(enc), _lib.ptr(dec),
+                      _lib.ptr(ranges), _lib.ptr(weight), _lib.ptr(bias), _lib.ptr(symbols),
+                      _lib.ptr(boundary), _lib.ptr(px), _lib.ptr(py), _lib.ptr(saved),
+                      _lib.ptr(scratch), B, T, R, S, C, D, blank, rnnt_type, _lib.stream_ptr(dev))
+        ctx.save_for_backward(ranges, symbols, boundary, saved)
+        ctx.cfg = (B, T, R, S, C, D, blank, rnnt_type, bias is not None)
+        return px, py
+
+    @staticmethod
+    def backward(ctx, g_px, g_py):
+        ranges, symbols, boundary, saved = ctx.saved_tensors
+        B, T, R, S, C, D, blank, rnnt_type, has_bias = ctx.cfg
+        dev = saved.device
+        T1 = T + 1 if rnnt_type == 0 else T
+        need = ctx.needs_input_grad
+        lib = _lib.lib()
+        with torch.cuda.device(dev):
+            g_px = (torch.zeros(B, S, T1, dtype=torch.float32, device=dev) if g_px is None
+                    else g_px.contiguous())
+            g_py = (torch.zeros(B, S + 1, T, dtype=torch.float32, device=dev) if g_py is None
+                    else g_py.contiguous())
+            want_in = need[0] or need[1]
+            enc_grad = torch.empty(B, T, D, dtype=torch.float32, device=dev) if want_in else None
+            dec_grad = torch.empty(B, S + 1, D, dtype=torch.float32, device=dev) if want_in else None
+            w_grad = torch.empty(C, D, dtype=torch.float32, device=dev) if need[3] else None
+            b_grad = (torch.empty(C, dtype=torch.float32, device=dev)
+                      if has_bias and need[4] else None)
+            scratch = _bytes(lib.frnnt_pruned_joiner_backward_scratch_bytes(B, T, R, S, C, D), dev)
+            _lib.call("frnnt_pruned_joiner_logprobs_backward", _lib.ptr(g_px), _lib.ptr(g_py),
+                      _lib.ptr(ranges), _lib.ptr(symbols), _lib.ptr(boundary), _lib.ptr(saved),
+                      _lib.ptr(scratch), _lib.ptr(enc_grad), _lib.ptr(dec_grad), _lib.ptr(w_grad),
+                      _lib.ptr(b_grad), B, T, R, S, C, D, blank, rnnt_type, _lib.stream_ptr(dev))
+        return (enc_grad if need[0] else None, dec_grad if need[1] else None, None, w_grad, b_grad,
+                None, None, None, None)
+
+
+def get_rnnt_logprobs_pruned_joiner(am: Tensor, lm: Tensor, ranges: Tensor, joiner_weight: Tensor,
+                                    joiner_bias: Optional[Tensor], symbols: Tensor,
+                                    termination_symbol: int, boundary: Optional[Tensor] = None,
+                                    rnnt_type: str = "regular") -> Tuple[Tensor, Tensor]:
+    """(px, py) of the pruned loss for the joiner of the reference's documented usage
+    (README.md:180-190), in one fused operator::
+
+        am_pruned, lm_pruned = do_rnnt_pruning(am, lm, ranges)
+        logits = linear(tanh(am_pruned + lm_pruned), joiner_weight, joiner_bias)
+        px, py = get_rnnt_logprobs_pruned(logits, symbols, ranges, termination_symbol, ...)
+
+    am [B][T][D], lm [B][S+1][D], ranges [B][T][s_range], joiner_weight [C][D]; float32
+    CUDA tensors, D a multiple of 8 and C a multiple of 4.  No counterpart in the
+    reference (which leaves the joiner to the caller); the pruned tensors, and a
+    second pass over the logits for their log-sum-exp, never exist."""
+    assert am.ndim == 3 and lm.ndim == 3 and ranges.ndim == 3, (am.shape, lm.shape, ranges.shape)
+    (B, T, D) = am.shape
+    (B2, S1, D2) = lm.shape
+    assert B2 == B and D2 == D, (am.shape, lm.shape)
+    s_range = ranges.shape[2]
+    assert ranges.shape == (B, T, s_range), f"{ranges.shape} == ({B}, {T}, {s_range})"
+    S = S1 - 1
+    assert symbols.shape == (B, S), symbols.shape
+    assert joiner_weight.ndim == 2 and joiner_weight.shape[1] == D, joiner_weight.shape
+    assert am.dtype == torch.float32 and lm.dtype == torch.float32
+    assert joiner_weight.dtype == torch.float32
+    validate_st_lengths(S, T, rnnt_type == "regular", boundary)
+    assert rnnt_type in ["regular", "modified", "constrained"], rnnt_type
+    return _PrunedJoinerLogprobs.apply(am, lm, ranges, joiner_weight, joiner_bias, symbols, boundary,
+                                       int(termination_symbol), _RNNT_TYPES[rnnt_type])
+
+
 # ------------------------------------------------------------------------------
 # pruning
 # ------------------------------------------------------------------------------
@@ -383,4 +472,19 @@ def rnnt_loss_pruned(logits: Tensor, symbols: Tensor, ranges: Tensor, terminatio
     px, py = get_rnnt_logprobs_pruned(logits=logits, symbols=symbols, ranges=ranges,
                                       termination_symbol=termination_symbol, boundary=boundary,
                                       rnnt_type=rnnt_type)
+    return _finish(px, py, boundary, rnnt_type, delay_penalty, reduction, return_grad)
+
+
+def rnnt_loss_pruned_joiner(am: Tensor, lm: Tensor, ranges: Tensor, joiner_weight: Tensor,
+                            joiner_bias: Optional[Tensor], symbols: Tensor, termination_symbol: int,
+                            boundary: Optional[Tensor] = None, rnnt_type: str = "regular",
+                            delay_penalty: float = 0.0, reduction: Optional[str] = "mean",
+                            return_grad: bool = False) -> Tensor:
+    """rnnt_loss_pruned (reference rnnt_loss.py:1027-1132) on the logits of the joiner
+    ``linear(tanh(am_pruned + lm_pruned))``, computed by the fused operator behind
+    get_rnnt_logprobs_pruned_joiner instead of being passed in."""
+    px, py = get_rnnt_logprobs_pruned_joiner(am=am, lm=lm, ranges=ranges,
+                                             joiner_weight=joiner_weight, joiner_bias=joiner_bias,
+                                             symbols=symbols, termination_symbol=termination_symbol,
+                                             boundary=boundary, rnnt_type=rnnt_type)
     return _finish(px, py, boundary, rnnt_type, delay_penalty, reduction, return_grad)

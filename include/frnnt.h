@@ -288,6 +288,46 @@ size_t frnnt_joiner_input_grads_scratch_bytes(int B, int T, int D);
 int frnnt_joiner_input_grads(const float *gz, const int64_t *ranges, float *enc_grad, float *dec_grad,
                              void *scratch, int B, int S1, int T, int R, int D, void *stream);
 
+/* ----------------------------------------------------------------------------
+ * Pruned joiner and pruned log-prob lattices as one operator
+ * ------------------------------------------------------------------------- */
+
+/* px [B][S][T1], py [B][S+1][T] of the pruned loss straight from the joiner's inputs:
+ *   logits[b][t][k][:] = weight * tanh(enc[b][t][:] + dec[b][ranges[b][t][k]][:]) + bias
+ *   (px, py) = get_rnnt_logprobs_pruned(logits, symbols, ranges, ...)
+ * i.e. do_rnnt_pruning (fast_rnnt/python/fast_rnnt/rnnt_loss.py:780-818), the joiner of
+ * the reference's documented usage (README.md:180-190, which the reference leaves to the
+ * caller) and get_rnnt_logprobs_pruned (rnnt_loss.py:856-1024) in one call; the reference
+ * has no counterpart of the combination.  float32 only.
+ *   enc [B][T][D], dec [B][S+1][D], ranges [B][T][R], weight [C][D], bias [C] or NULL,
+ *   symbols [B][S], boundary [B][4] or NULL; D a multiple of 8, C a multiple of 4.
+ * The three products run on the tensor cores from operands stored as pairs of fp16
+ * planes (x * 2^e = hi + lo, 22 significant bits, e chosen per operand from its largest
+ * magnitude): fp32-level accuracy at the fp16 rate.  The log-sum-exp over C comes out of
+ * the forward product's epilogue.
+ * `saved` (frnnt_pruned_joiner_saved_bytes) must stay untouched until the backward call;
+ * `scratch` is per-call (…_forward_scratch_bytes / …_backward_scratch_bytes); both
+ * 256-byte aligned. */
+size_t frnnt_pruned_joiner_saved_bytes(int B, int T, int R, int S, int C, int D);
+size_t frnnt_pruned_joiner_forward_scratch_bytes(int B, int T, int R, int S, int C, int D);
+size_t frnnt_pruned_joiner_backward_scratch_bytes(int B, int T, int R, int S, int C, int D);
+int frnnt_pruned_joiner_logprobs_forward(const float *enc, const float *dec, const int64_t *ranges,
+                                         const float *weight, const float *bias,
+                                         const int64_t *symbols, const int64_t *boundary, float *px,
+                                         float *py, void *saved, void *scratch, int B, int T, int R,
+                                         int S, int C, int D, int blank, int rnnt_type, void *stream);
+
+/* Gradients of the above given the gradients of px and py: enc_grad [B][T][D] and
+ * dec_grad [B][S+1][D] (both or neither), weight_grad [C][D], bias_grad [C] (each may be
+ * NULL); all fully written.  Sums are taken in a fixed order (no atomics) for ranges
+ * written by frnnt_prune_ranges. */
+int frnnt_pruned_joiner_logprobs_backward(const float *px_grad, const float *py_grad,
+                                          const int64_t *ranges, const int64_t *symbols,
+                                          const int64_t *boundary, void *saved, void *scratch,
+                                          float *enc_grad, float *dec_grad, float *weight_grad,
+                                          float *bias_grad, int B, int T, int R, int S, int C, int D,
+                                          int blank, int rnnt_type, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

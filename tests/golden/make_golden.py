@@ -137,6 +137,8 @@ def run_pipeline(fr, wl, rnnt_type, full_arrays, keep_full=()):
     (simple + pruned).backward()
     out = dict(simple=simple, pruned=pruned, s_begin=ranges[:, :, 0].to(torch.int16),
                s_range=ranges.shape[2])
+    if not full_arrays:
+        out.update(float64_samples(fr, wl, rnnt_type, ranges))
     big = dict(px=px, py=py, occ_x=occ_x_keep, occ_y=occ_y_keep, pruned_px=ppx, pruned_py=ppy,
                am_grad=am.grad, lm_grad=lm.grad, enc_grad=enc.grad, dec_grad=dec.grad,
                logits=logits, logits_grad=logits.grad, w_grad=W.grad, b_grad=bias.grad)
@@ -147,6 +149,33 @@ def run_pipeline(fr, wl, rnnt_type, full_arrays, keep_full=()):
         out.update({k + "_sample": sample(v) for k, v in big.items()})
         out.update({k + "_sum": v.detach().double().clamp(min=-1e30).sum() for k, v in big.items()})
         out.update({k: big[k] for k in keep_full})
+    return out
+
+
+def float64_samples(fr, wl, rnnt_type, ranges):
+    """The same pipeline in float64 on the float32 run's ranges: samples of what exact
+    arithmetic gives.  |float32 sample - float64 sample| is the reference's own rounding
+    noise, the floor below which a comparison with its float32 output means nothing."""
+    d = lambda x: x.double().clone().requires_grad_(True)  # noqa: E731
+    am, lm, enc, dec, W, bias = (d(wl[k]) for k in ("am", "lm", "enc", "dec", "joiner_w", "joiner_b"))
+    symbols, boundary, blank = wl["symbols"], wl["boundary"], wl["blank"]
+    simple, (occ_x, occ_y) = fr.rnnt_loss_smoothed(
+        lm=lm, am=am, symbols=symbols, termination_symbol=blank,
+        lm_only_scale=wl["lm_only_scale"], am_only_scale=wl["am_only_scale"],
+        boundary=boundary, rnnt_type=rnnt_type, reduction="sum", return_grad=True)
+    occ_x, occ_y = occ_x.clone(), occ_y.clone()
+    am_p, lm_p = fr.do_rnnt_pruning(am=enc, lm=dec, ranges=ranges)
+    logits = torch.nn.functional.linear(torch.tanh(am_p + lm_p), W, bias)
+    logits.retain_grad()
+    pruned = fr.rnnt_loss_pruned(logits=logits, symbols=symbols, ranges=ranges,
+                                 termination_symbol=blank, boundary=boundary,
+                                 rnnt_type=rnnt_type, reduction="sum")
+    (simple + pruned).backward()
+    big = dict(occ_x=occ_x, occ_y=occ_y, am_grad=am.grad, lm_grad=lm.grad, enc_grad=enc.grad,
+               dec_grad=dec.grad, logits=logits, logits_grad=logits.grad, w_grad=W.grad,
+               b_grad=bias.grad)
+    out = {k + "_f64_sample": sample(v) for k, v in big.items()}
+    out.update(simple_f64=simple, pruned_f64=pruned)
     return out
 
 

@@ -324,38 +324,69 @@ def test_c3_full_size_against_reference_summary(joiner):
 
 
 def pruned_stage(wl, ranges, joiner):
-    """Pruning -> joiner -> pruned loss -> backward on GIVEN ranges (regular type)."""
+    """Pruning -> joiner -> pruned loss -> backward on GIVEN ranges (regular type).
+    joiner: "torch" (the reference's composition), "fused" (pruned_joiner) or "logprobs"
+    (the single operator behind rnnt_loss_pruned_joiner, which never exposes logits)."""
     f = fr()
     enc = wl["enc"].cuda().requires_grad_(True)
     dec = wl["dec"].cuda().requires_grad_(True)
     W = wl["joiner_w"].cuda().requires_grad_(True)
     bias = wl["joiner_b"].cuda().requires_grad_(True)
     sym, bnd = wl["symbols"].cuda(), wl["boundary"].cuda()
-    logits = joiner_logits(joiner, enc, dec, ranges, W, bias)
-    logits.retain_grad()
-    ppx, ppy = f.get_rnnt_logprobs_pruned(logits=logits.detach(), symbols=sym, ranges=ranges,
-                                          termination_symbol=0, boundary=bnd)
-    pruned = f.rnnt_loss_pruned(logits=logits, symbols=sym, ranges=ranges, termination_symbol=0,
-                                boundary=bnd, reduction="sum")
-    pruned.backward()
-    return dict(pruned=pruned, logits=logits, pruned_px=ppx, pruned_py=ppy,
-                logits_grad=logits.grad, enc_grad=enc.grad, dec_grad=dec.grad, w_grad=W.grad,
-                b_grad=bias.grad)
+    out = {}
+    if joiner == "logprobs":
+        ppx, ppy = f.get_rnnt_logprobs_pruned_joiner(
+            am=enc.detach(), lm=dec.detach(), ranges=ranges, joiner_weight=W.detach(),
+            joiner_bias=bias.detach(), symbols=sym, termination_symbol=0, boundary=bnd)
+        pruned = f.rnnt_loss_pruned_joiner(am=enc, lm=dec, ranges=ranges, joiner_weight=W,
+                                           joiner_bias=bias, symbols=sym, termination_symbol=0,
+                                           boundary=bnd, reduction="sum")
+        pruned.backward()
+    else:
+        logits = joiner_logits(joiner, enc, dec, ranges, W, bias)
+        logits.retain_grad()
+        ppx, ppy = f.get_rnnt_logprobs_pruned(logits=logits.detach(), symbols=sym, ranges=ranges,
+                                              termination_symbol=0, boundary=bnd)
+        pruned = f.rnnt_loss_pruned(logits=logits, symbols=sym, ranges=ranges,
+                                    termination_symbol=0, boundary=bnd, reduction="sum")
+        pruned.backward()
+        out.update(logits=logits, logits_grad=logits.grad)
+    out.update(pruned=pruned, pruned_px=ppx, pruned_py=ppy, enc_grad=enc.grad, dec_grad=dec.grad,
+               w_grad=W.grad, b_grad=bias.grad)
+    return out
+
+
+def assert_as_close_as_the_reference(ours, g, key, atol):
+    """ours against the reference's float32 sample of tensor `key`.  Where the reference
+    also wrote a float64 sample, its own float32 rounding noise max|f32 - f64| is known;
+    a difference from the float32 sample below twice that noise says nothing, so the
+    bound is atol + 2 * noise (sums over all 160 000 joiner rows of a batch -- the
+    weight, bias and decoder gradients -- carry noise far above 1e-4 in the reference
+    itself)."""
+    ref = g[key + "_sample"]
+    noise = 0.0
+    if key + "_f64_sample" in g:
+        r64 = g[key + "_f64_sample"]
+        fin = torch.isfinite(r64)
+        noise = float((ref.double()[fin] - r64[fin]).abs().max())
+    assert_close(samp(ours), ref, 0, atol + 2 * noise, key)
+    return noise
 
 
 def check_pruned_stage(out, g):
     """Pruned stage on the reference's own ranges: loss 1e-5 relative, lattices 1e-5,
-    gradients 1e-4 absolute (plus 1e-4 relative: the weight and bias gradients are sums
-    over all frames of the batch and reach 1e3..1e4)."""
+    gradients 1e-4 absolute on top of the reference's own float32 noise."""
     assert_close(out["pruned"], torch.tensor(g["pruned"]), LOSS_RTOL, 0, "pruned loss")
-    assert_close(samp(out["logits"]), g["logits_sample"], 0, LATTICE_ATOL, "logits")
+    if "logits" in out:
+        assert_close(samp(out["logits"]), g["logits_sample"], 0, LATTICE_ATOL, "logits")
     assert_close(samp(out["pruned_px"]), g["pruned_px_sample"], 0, LATTICE_ATOL, "pruned px")
     assert_close(samp(out["pruned_py"]), g["pruned_py_sample"], 0, LATTICE_ATOL, "pruned py")
     for k in ("logits_grad", "enc_grad", "dec_grad", "w_grad", "b_grad"):
-        assert_close(samp(out[k]), g[k + "_sample"], 1e-4, GRAD_ATOL, k)
+        if k in out:
+            assert_as_close_as_the_reference(out[k], g, k, GRAD_ATOL)
 
 
-@pytest.mark.parametrize("joiner", ["torch", "fused"])
+@pytest.mark.parametrize("joiner", ["torch", "fused", "logprobs"])
 def test_c3_full_size_pruned_stage_on_reference_ranges(joiner):
     """Stage-wise at full size: with the reference's prune ranges injected the argmax
     no longer matters, so the pruned loss must agree to 1e-5 and the gradients of the
@@ -366,19 +397,20 @@ def test_c3_full_size_pruned_stage_on_reference_ranges(joiner):
     check_pruned_stage(pruned_stage(wl, ranges, joiner), g)
 
 
-def test_c3_bench_step_matches_the_reference():
-    """The step bench.py times (its make_step with pruned_joiner) on the same workload:
-    loss and input gradients against the reference's summary."""
+@pytest.mark.parametrize("joiner", ["fused", "tensorcore"])
+def test_c3_bench_step_matches_the_reference(joiner):
+    """The step bench.py times (its make_step with the joiner it selects) on the same
+    workload: loss and input gradients against the reference's summary."""
     import bench
     g = load_golden("c3_pipeline")
     wl = workloads.pipeline_workload("c3")
-    step = bench.make_step(fr(), wl, lambda f, enc, dec, ranges, W, b: f.pruned_joiner(enc, dec, ranges, W, b))
+    step = bench.make_step(fr(), wl, joiner)
     t = {k: wl[k].cuda() for k in bench.TENSOR_KEYS}
     loss = step(t)
     # own ranges: a few frames may pick a neighbouring window (see the test above)
     assert_close(loss, torch.tensor(g["simple"] + g["pruned"]), 5e-4, 0, "simple + pruned")
-    assert_close(samp(t["am"].grad), g["am_grad_sample"], 0, GRAD_ATOL, "am grad")
-    assert_close(samp(t["lm"].grad), g["lm_grad_sample"], 0, GRAD_ATOL, "lm grad")
+    assert_as_close_as_the_reference(t["am"].grad, g, "am_grad", GRAD_ATOL)
+    assert_as_close_as_the_reference(t["lm"].grad, g, "lm_grad", GRAD_ATOL)
     # a moved window changes the encoder gradient of its own frame only, and the decoder
     # gradient of the few rows it covers
     for k, allowed in (("enc", 0.02), ("dec", 0.3)):
@@ -401,13 +433,13 @@ def test_c4_unpruned_against_reference_summary():
                  "logits grad")
 
 
-@pytest.mark.parametrize("joiner", ["torch", "fused"])
+@pytest.mark.parametrize("joiner", ["torch", "fused", "logprobs"])
 def test_c5_shape_against_reference_summary(joiner):
     """The large-vocabulary shape (T=400, S=60, C=5000, s_range=5, batch of 3) against
     vectors the reference itself wrote: simple stage, ranges bit for bit on the
     reference's occupancies, pruned stage on the reference's ranges.  Single lm
     gradients reach 3e2 here, where the reference's own float32 result is 1.2e-2 away
-    from its float64 result: those are compared with a relative term of 1e-4."""
+    from its float64 result: gradients are compared on top of that measured noise."""
     g = load_golden("c5_shape_pipeline")
     wl = workloads.pipeline_workload("c5", batch=3, seed=2)
     f = fr()
@@ -427,8 +459,8 @@ def test_c5_shape_against_reference_summary(joiner):
     assert_close(gx, g["occ_x"], 0, GRAD_ATOL, "occ_x")
     assert_close(gy, g["occ_y"], 0, GRAD_ATOL, "occ_y")
     simple.backward()
-    assert_close(samp(am.grad), g["am_grad_sample"], 1e-4, GRAD_ATOL, "am grad")
-    assert_close(samp(lm.grad), g["lm_grad_sample"], 1e-4, GRAD_ATOL, "lm grad")
+    assert_as_close_as_the_reference(am.grad, g, "am_grad", GRAD_ATOL)
+    assert_as_close_as_the_reference(lm.grad, g, "lm_grad", GRAD_ATOL)
     ref_ranges = g["s_begin"].to(torch.int64).unsqueeze(-1) + torch.arange(g["s_range"])
     r = f.get_rnnt_prune_ranges(px_grad=g["occ_x"].cuda(), py_grad=g["occ_y"].cuda(), boundary=bnd,
                                 s_range=wl["s_range"])
