@@ -8,12 +8,20 @@ One "step" is the whole pruned pipeline of the reference's documented usage,
 forward and backward, on one batch of synthetic utterances:
   rnnt_loss_smoothed(return_grad) -> get_rnnt_prune_ranges -> do_rnnt_pruning ->
   joiner Linear(tanh(enc+dec)) -> rnnt_loss_pruned -> (simple+pruned).backward()
-The joiner is the caller's network: by default this library's pruned_joiner (fused
-gather+add+tanh, 3xTF32 tensor-core projection), or plain torch with --joiner torch; everything else
+The joiner is the caller's network: by default this library's fused operator
+rnnt_loss_pruned_joiner (fp16-pair tensor-core products, log-sum-exp in the epilogue), or
+its pruned_joiner (--joiner tensorcore) or plain torch (--joiner torch); everything else
 runs in libfrnnt_sm100.so.  Rank 0 prints ONE JSON line.
 
-Under torchrun every rank works on its own batch (weak scaling); the only
-collective is an NCCL all-reduce of the scalar loss.
+Under torchrun every rank works on its own batch (weak scaling; for --workload c5 the
+global batch is built once from seed 0 and rank r takes its slice, so the all-reduced
+loss does not depend on the number of ranks); the only collective is an NCCL all-reduce
+of the scalar loss.
+
+--impl reference times the reference's own python package on the host cores (its CPU
+extension compiled into oracle/_ref, its python files installed under baseline/_ref by
+__graft_entry__.build() where a checkout exists), or, where that install is absent,
+the CPU oracle port of the same algorithm.
 """
 import argparse
 import json
@@ -31,18 +39,13 @@ sys.path.insert(0, ROOT)
 from tests import workloads  # noqa: E402  (seeded synthetic inputs)
 
 L2_FLUSH_BYTES = 512 << 20
+# all-reduced loss of the c5 global batch (B=512, seed 0); None until measured
+C5_GLOBAL_LOSS = None
 
-# DRAM traffic per launch measured once with ncu (dram__bytes_read.sum +
-# dram__bytes_write.sum, profiles/); keyed by stage name, bytes for workload c3.
+# DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the kernels
+# the roofline lines name, workload c3, from the ncu captures summarised under profiles/
+# (one small capture per kernel; the file names the command).  None: not captured.
 NCU_TRAFFIC_C3 = {
-    # dram__bytes_read.sum + dram__bytes_write.sum per launch, profiles/kernels_c3_ncu_full.txt
-    # (the two prune_gather stages and the grad-input product: earlier captures of the same
-    # kernels; a capture shows the first launch of every kernel of a step)
-    "lsm_gather_bwd": 600.9e6, "lsm_gather_fwd": 327.1e6, "prune_gather_fwd": 280.0e6,
-    "prune_gather_bwd": 408.0e6 + 39.2e6, "mi_forward": 17.4e6, "mi_backward": 12.2e6,
-    "mi_forward_pruned": 17.4e6, "mi_backward_pruned": 12.2e6,
-    "joiner_linear_fwd": 600.2e6, "joiner_linear_grad_input": 944.4e6,
-    "joiner_linear_grad_weight": 651.2e6, "joiner_tanh": 347.5e6, "joiner_input_grads": 408.0e6 + 39.2e6,
 }
 
 
@@ -193,21 +196,93 @@ class OracleApi:
 
 TENSOR_KEYS = ("am", "lm", "enc", "dec", "joiner_w", "joiner_b", "symbols", "boundary")
 
+_REFERENCE = None
+
+
+def load_reference_package():
+    """The reference's own python package, if it was installed next to this file:
+    baseline/_ref/fast_rnnt (its python files) on one of its compiled extensions --
+    oracle/_ref/cuda/_fast_rnnt.so (CPU + CUDA kernels) or oracle/_ref/_fast_rnnt.so (CPU).
+    Returns (module, has_cuda_kernels) or None."""
+    global _REFERENCE
+    if _REFERENCE is not None:
+        return _REFERENCE or None
+    _REFERENCE = False
+    pkg = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isfile(os.path.join(pkg, "fast_rnnt", "__init__.py")):
+        return None
+    for d in (os.path.join(ROOT, "oracle", "_ref", "cuda"), os.path.join(ROOT, "oracle", "_ref")):
+        if os.path.exists(os.path.join(d, "_fast_rnnt.so")):
+            sys.path.insert(0, d)
+            sys.path.insert(0, pkg)
+            try:
+                import _fast_rnnt  # noqa: F401  (the package imports it by this name)
+                import fast_rnnt
+                _REFERENCE = (fast_rnnt, bool(_fast_rnnt.with_cuda()))
+                return _REFERENCE
+            except Exception as e:  # pragma: no cover
+                print(f"reference package not importable from {d}: {e}", file=sys.stderr)
+                sys.path.remove(d)
+                sys.path.remove(pkg)
+    return None
+
 
 def cpu_reference_run(workload, sample_batch, steps, warmup):
-    """Times the CPU oracle (the reference's algorithm on the host cores)."""
+    """Times the reference's CPU implementation on the host cores: its own package where
+    installed (kind "reference"), else the CPU oracle port (kind "port").  Returns
+    (utt/s, ms per step, kind, loss of the sample)."""
     wl = workloads.pipeline_workload(workload, batch=sample_batch)
-    step = make_step(OracleApi(), wl)
+    ref = load_reference_package()
+    api, kind = (ref[0], "reference") if ref else (OracleApi(), "port")
+    step = make_step(api, wl)
     t = {k: wl[k].clone() for k in TENSOR_KEYS}
     for _ in range(warmup):
         step(t)
-    times = []
+    times, loss = [], None
     for _ in range(steps):
         t0 = time.perf_counter()
-        step(t)
+        loss = step(t)
         times.append(time.perf_counter() - t0)
     sec = sum(times) / len(times)
-    return sample_batch / sec, sec * 1e3
+    grads = {k: t[k].grad.detach().clone() for k in ("am", "lm", "enc", "dec", "joiner_w")}
+    return sample_batch / sec, sec * 1e3, kind, float(loss), grads
+
+
+def reference_cuda_run(workload, batch, sample_batch, cpu_grads, dev):
+    """The reference's own pipeline on the GPU (its torch ops on device tensors + its CUDA
+    mutual-information kernels), device-timed, and -- on the CPU leg's sample -- the
+    reference's own CPU <-> CUDA gradient gap: the noise floor of any comparison."""
+    ref = load_reference_package()
+    if not ref or not ref[1]:
+        return None, None
+    api = ref[0]
+    wl = workloads.pipeline_workload(workload, batch=batch)
+    step = make_step(api, wl)
+    t = {k: wl[k].to(dev) for k in TENSOR_KEYS}
+    for _ in range(2):
+        step(t)
+    torch.cuda.synchronize()
+    ms = []
+    for _ in range(5):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        step(t)
+        e.record()
+        e.synchronize()
+        ms.append(s.elapsed_time(e))
+    med = statistics.median(ms)
+    out = {"ms_per_step": round(med, 3), "value": round(batch / (med * 1e-3), 1), "unit": "utt/s",
+           "what": "the reference's python package on CUDA tensors with its own CUDA kernels, "
+                   "joiner in torch (cuBLAS fp32), same workload, CUDA events, median of 5"}
+    noise = None
+    if cpu_grads is not None:
+        wl_s = workloads.pipeline_workload(workload, batch=sample_batch)
+        ts = {k: wl_s[k].to(dev) for k in TENSOR_KEYS}
+        make_step(api, wl_s)(ts)
+        noise = {k: float((ts[k].grad.cpu() - cpu_grads[k]).abs().max()) for k in cpu_grads}
+        noise["what"] = (f"max |gradient on CPU - gradient on CUDA| of the reference itself, "
+                         f"{sample_batch} utterances")
+    return out, noise
 
 
 # ------------------------------------------------------------------------------
@@ -331,6 +406,68 @@ def stage_table(fr, wl, dev, flush, hbm_gbs):
             _lib.ptr(dec_g), _lib.ptr(jscratch), B, S + 1, T, R, D, sp),
          es * (M * D + B * (T + S + 1) * D), None),
     ]
+    # the fused operator (--joiner fused): as a whole, and its three products alone on the
+    # fp16-pair engine (planes made from the same random matrices)
+    lib = _lib.lib()
+    sym, bnd = t["symbols"], t["boundary"]
+    S1 = S + 1
+    pj_saved = torch.empty(max(1, lib.frnnt_pruned_joiner_saved_bytes(B, T, R, S, C, D)),
+                           dtype=torch.uint8, device=dev)
+    pj_fs = torch.empty(max(1, lib.frnnt_pruned_joiner_forward_scratch_bytes(B, T, R, S, C, D)),
+                        dtype=torch.uint8, device=dev)
+    pj_bs = torch.empty(max(1, lib.frnnt_pruned_joiner_backward_scratch_bytes(B, T, R, S, C, D)),
+                        dtype=torch.uint8, device=dev)
+    w_g, b_g = torch.empty(C, D, device=dev), torch.empty(C, device=dev)
+
+    def pj_fwd():
+        _lib.call("frnnt_pruned_joiner_logprobs_forward", _lib.ptr(t["enc"]), _lib.ptr(t["dec"]),
+                  _lib.ptr(ranges), _lib.ptr(W), _lib.ptr(t["joiner_b"]), _lib.ptr(sym), _lib.ptr(bnd),
+                  _lib.ptr(ppxd), _lib.ptr(ppyd), _lib.ptr(pj_saved), _lib.ptr(pj_fs), B, T, R, S, C, D,
+                  0, 0, sp)
+
+    def pj_bwd():
+        _lib.call("frnnt_pruned_joiner_logprobs_backward", _lib.ptr(gpx), _lib.ptr(gpy), _lib.ptr(ranges),
+                  _lib.ptr(sym), _lib.ptr(bnd), _lib.ptr(pj_saved), _lib.ptr(pj_bs), _lib.ptr(enc_g),
+                  _lib.ptr(dec_g), _lib.ptr(w_g), _lib.ptr(b_g), B, T, R, S, C, D, 0, 0, sp)
+
+    Cp = (C + 7) // 8 * 8
+    half = lambda *shape: torch.empty(*shape, dtype=torch.float16, device=dev)  # noqa: E731
+    pscr = torch.empty(lib.frnnt_pairs_scratch_floats(), device=dev)
+    inv = torch.empty(4, device=dev)
+    a_hi, a_lo, w_hi, w_lo = half(M, D), half(M, D), half(C, D), half(C, D)
+    g_hi, g_lo, wt_hi, wt_lo = half(M, Cp), half(M, Cp), half(D, Cp), half(D, Cp)
+
+    def planes(x, rows, cols, pitch, hi, lo, slot):
+        _lib.call("frnnt_pairs_from_f32", _lib.ptr(x), _lib._c_longlong(rows), cols,
+                  _lib._c_longlong(pitch), _lib.ptr(hi), _lib.ptr(lo), _lib.ptr(inv[slot:]),
+                  _lib.ptr(pscr), sp)
+
+    planes(act2, M, D, D, a_hi, a_lo, 0)
+    planes(W, C, D, D, w_hi, w_lo, 1)
+    planes(g_logits, M, C, Cp, g_hi, g_lo, 2)
+    planes(Wt, D, C, Cp, wt_hi, wt_lo, 3)
+    out_mc, out_md = torch.empty(M, C, device=dev), torch.empty(M, D, device=dev)
+    tn_parts = torch.empty(max(1, lib.frnnt_pair_matmul_tn_splits(C, D, _lib._c_longlong(M)) * C * D),
+                           device=dev)
+    LL = _lib._c_longlong
+    stages += [
+        ("fused_joiner_lattices_fwd", pj_fwd,
+         es * (B * (T + S1) * D + 8 * M // 4 + M * D + M * C + C * D) + lat, gemm_flops),
+        ("fused_joiner_lattices_bwd", pj_bwd,
+         lat + es * (2 * M * C + 2 * M * D + B * (T + S1) * D + 2 * C * D), 2 * gemm_flops),
+        ("pair_linear_fwd", lambda: _lib.call(
+            "frnnt_pair_matmul_nt", _lib.ptr(a_hi), _lib.ptr(a_lo), _lib.ptr(w_hi), _lib.ptr(w_lo),
+            _lib.ptr(inv[0:]), _lib.ptr(inv[1:]), _lib.ptr(t["joiner_b"]), _lib.ptr(out_mc), M, C, D,
+            LL(D), LL(D), sp), es * (M * D + M * C + C * D), gemm_flops),
+        ("pair_linear_grad_input", lambda: _lib.call(
+            "frnnt_pair_matmul_nt", _lib.ptr(g_hi), _lib.ptr(g_lo), _lib.ptr(wt_hi), _lib.ptr(wt_lo),
+            _lib.ptr(inv[2:]), _lib.ptr(inv[3:]), None, _lib.ptr(out_md), M, D, C, LL(Cp), LL(Cp), sp),
+         es * (M * C + M * D + C * D), gemm_flops),
+        ("pair_linear_grad_weight", lambda: _lib.call(
+            "frnnt_pair_matmul_tn", _lib.ptr(g_hi), _lib.ptr(g_lo), _lib.ptr(a_hi), _lib.ptr(a_lo),
+            _lib.ptr(inv[2:]), _lib.ptr(inv[0:]), _lib.ptr(w_g), _lib.ptr(tn_parts), C, D, LL(M),
+            LL(Cp), LL(D), sp), es * (M * C + M * D + C * D), gemm_flops),
+    ]
     out = {}
     for name, fn, nbytes, flops in stages:
         ms = time_call(fn, flush)
@@ -340,6 +477,22 @@ def stage_table(fr, wl, dev, flush, hbm_gbs):
         if flops:
             out[name]["tflops"] = round(flops / (ms * 1e-3) / 1e12, 2)
     return out, cells_box
+
+
+COMMON_STAGES = ["simple_logprobs_fwd", "simple_logprobs_bwd", "mi_forward", "mi_backward",
+                 "mi_forward_pruned", "mi_backward_pruned", "prune_ranges"]
+STEP_STAGES = {
+    # stages of the table above that one timed step launches, by --joiner
+    "fused": COMMON_STAGES + ["fused_joiner_lattices_fwd", "fused_joiner_lattices_bwd"],
+    "tensorcore": COMMON_STAGES + ["joiner_tanh", "joiner_linear_fwd", "lsm_gather_fwd", "lsm_gather_bwd",
+                                   "joiner_linear_grad_input", "joiner_linear_grad_weight",
+                                   "joiner_input_grads"],
+    "torch": COMMON_STAGES + ["prune_gather_fwd", "lsm_gather_fwd", "lsm_gather_bwd", "prune_gather_bwd"],
+}
+PRODUCT_STAGES = {"fused": ["pair_linear_fwd", "pair_linear_grad_input", "pair_linear_grad_weight"],
+                  "tensorcore": ["joiner_linear_fwd", "joiner_linear_grad_input",
+                                 "joiner_linear_grad_weight"],
+                  "torch": []}
 
 
 def mi_c2_table(dev, flush):
@@ -393,23 +546,24 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     sizes = workloads.PIPELINE_SIZES[args.workload]
-    batch = args.batch or (sizes[0] if args.workload != "c5" else sizes[0] // 8)
+    batch = args.batch or (sizes[0] if args.workload != "c5" else sizes[0] // world)
     cfg = {"workload": f"{args.workload}: pruned RNN-T loss pipeline fwd+bwd (smoothed simple loss, "
                        f"prune ranges, pruning, joiner, pruned loss)",
            "B_per_gpu": batch, "T": sizes[1], "S": sizes[2], "C": sizes[3], "D": sizes[4],
            "s_range": sizes[5], "global_batch": batch * world,
            "parallelism": f"batch sharded over {world} GPU(s), scalar-loss all-reduce",
-           "joiner": ({"fused": "Linear(tanh(enc_pruned+dec_pruned)) + pruned log-probs as "
-                                "fast_rnnt_b200.rnnt_loss_pruned_joiner: one operator, fp16-pair tcgen05 "
-                                "products (fp32-level accuracy), log-sum-exp in the product's epilogue",
-                       "tensorcore": "Linear(tanh(enc_pruned+dec_pruned)) as fast_rnnt_b200.pruned_joiner: "
-                                     "gather+add+tanh kernel, projection fwd+bwd on tcgen05 with 3xTF32",
-                       "torch": "torch Linear(tanh(enc+dec)), fp32"}[args.joiner]
-                      if args.impl == "ours" else "torch Linear(tanh(enc+dec)), fp32"),
+           "joiner": f"Linear({sizes[4]}->{sizes[3]})(tanh(enc_pruned + dec_pruned)), float32 results",
            "l2": f"value and stages: flushed between timed steps ({L2_FLUSH_BYTES >> 20} MiB write); e2e: "
                  "every step's inputs are a fresh upload larger than L2",
            "e2e_upload": "all inputs of a step collated in one page-locked (cudaHostRegister) buffer, "
                          "one H2D copy per step on a copy stream that runs one step ahead"}
+
+    joiner_impl = {"fused": "fast_rnnt_b200.rnnt_loss_pruned_joiner: one operator from enc / dec to the "
+                            "pruned lattices, fp16-pair tcgen05 products (fp32-level accuracy), "
+                            "log-sum-exp in the forward product's epilogue",
+                   "tensorcore": "fast_rnnt_b200.pruned_joiner (gather+add+tanh kernel, 3xTF32 tcgen05 "
+                                 "products) + rnnt_loss_pruned",
+                   "torch": "do_rnnt_pruning + torch Linear(tanh(.)) (cuBLAS fp32) + rnnt_loss_pruned"}
 
     # -------------------------------------------------------------- reference arm
     if args.impl == "reference":
@@ -417,16 +571,19 @@ def main():
             return
         torch.set_num_threads(os.cpu_count() or 1)
         sample = min(batch, 16)
-        value, ms = cpu_reference_run(args.workload, sample, max(1, args.steps), args.warmup)
+        value, ms, kind, _, _ = cpu_reference_run(args.workload, sample, max(1, args.steps), args.warmup)
         cores = torch.get_num_threads()
+        what = ("the reference's own python package on its CPU extension" if kind == "reference"
+                else "CPU oracle port: torch CPU ops + C recursion")
         line = {"impl": "reference", "metric": "utterances/sec", "value": round(value, 3),
                 "unit": "utt/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": cfg,
+                "joiner_impl": "do_rnnt_pruning + torch Linear(tanh(.)) on the CPU + rnnt_loss_pruned",
                 "cpu_baseline": {"value": round(value, 3), "unit": "utt/s", "cores": cores,
-                                 "kind": "port",
+                                 "kind": kind,
                                  "sample": f"{sample} utterances of the {args.workload} batch per step "
-                                           f"(CPU oracle: torch CPU ops + C recursion)"},
+                                           f"({what})"},
                 "e2e": {"value": round(value, 3), "unit": "utt/s", "h2d_bytes_per_step": 0,
                         "d2h_bytes_per_step": 0}}
         print(json.dumps(line))
@@ -444,15 +601,27 @@ def main():
     lib = _lib.lib()
     lib.frnnt_launch_count.restype = __import__("ctypes").c_longlong
 
-    wl = workloads.pipeline_workload(args.workload, batch=batch, seed=rank)
+    if args.workload == "c5" and args.batch is None:
+        # one global batch from seed 0, rank r takes rows [r*B/n, (r+1)*B/n): the all-reduced
+        # loss is then the same number at every n
+        from fast_rnnt_b200 import sharding
+        full = workloads.pipeline_workload("c5", batch=sizes[0], seed=0)
+        wl = sharding.shard_batch(full, [k for k in TENSOR_KEYS if k not in ("joiner_w", "joiner_b")],
+                                  rank, world)
+        del full
+    else:
+        wl = workloads.pipeline_workload(args.workload, batch=batch, seed=rank)
     host = {k: wl[k].pin_memory() for k in TENSOR_KEYS}
     resident = {k: v.to(dev) for k, v in host.items()}
     inner = make_step(fr, wl, args.joiner)
 
     from fast_rnnt_b200 import sharding
 
+    last_loss = [None]
+
     def step(t):
-        return sharding.allreduce_loss(inner(t))
+        last_loss[0] = sharding.allreduce_loss(inner(t))
+        return last_loss[0]
 
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
 
@@ -579,37 +748,60 @@ def main():
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": cfg,
-            "clocks": clocks.summary(),
+            "joiner_impl": joiner_impl[args.joiner], "clocks": clocks.summary(),
             "e2e": {"value": round(e2e_value, 1), "unit": "utt/s", "h2d_bytes_per_step": int(h2d),
-                    "d2h_bytes_per_step": 4, "ms_per_step": round(e2e_ms, 4)},
-            "gpu_launches": int(launches)}
+                    "d2h_bytes_per_step": 4, "ms_per_step": round(e2e_ms, 4),
+                    "note": "uploads every input of the step, reads back the loss; the input "
+                            "gradients (about as many bytes as the inputs) stay on the device, "
+                            "where a training step consumes them"},
+            "gpu_launches": int(launches),
+            "loss_allreduced": float(last_loss[0]) if last_loss[0] is not None else None}
+    if args.workload == "c5" and args.batch is None and C5_GLOBAL_LOSS is not None:
+        rel = abs(line["loss_allreduced"] - C5_GLOBAL_LOSS) / abs(C5_GLOBAL_LOSS)
+        line["loss_check"] = {"expected": C5_GLOBAL_LOSS, "rel_err": rel,
+                              "what": "sum over the global batch of 512 utterances; the same "
+                                      "number at every count of ranks"}
+        assert rel < 1e-5, line["loss_check"]
 
     if rank == 0 and not args.no_stages:
         stages, cells = stage_table(fr, wl, dev, flush, hbm_gbs)
-        loss_path_ms = sum(v["ms"] for k, v in stages.items() if not k.startswith("joiner_"))
+        in_step = STEP_STAGES[args.joiner]
+        products = PRODUCT_STAGES[args.joiner]
+        step_sum = sum(stages[k]["ms"] for k in in_step)
+        prod_sum = sum(stages[k]["ms"] for k in products)
         line["stages"] = stages
-        line["loss_path"] = {"ms_per_step": round(loss_path_ms, 4),
-                             "value": round(batch / (loss_path_ms * 1e-3), 1), "unit": "utt/s",
-                             "note": "sum of the library's stages timed alone (no joiner)"}
+        line["step_stages"] = {"launched_by_the_timed_step": in_step,
+                               "sum_ms": round(step_sum, 4),
+                               "note": "each stage timed alone with a flushed L2; their sum is not "
+                                       "the step time (ms_per_step is), it shows where it goes"}
+        line["loss_path"] = {"ms_per_step": round(step_sum - prod_sum, 4),
+                             "value": round(batch / ((step_sum - prod_sum) * 1e-3), 1), "unit": "utt/s",
+                             "note": "the stages the timed step launches minus the joiner's three "
+                                     "tensor-core products " + str(products) + " (the caller's network)"}
         mi_ms = stages["mi_forward"]["ms"] + stages["mi_backward"]["ms"]
         line["mi_cells_per_s"] = round(cells / (mi_ms * 1e-3), 1)
         line["mi_c2"] = mi_c2_table(dev, flush)
-        # the dominant kernel of a step: the joiner's forward product on the tensor-core
-        # engine (one kernel; the largest share of the launch list)
+        # the dominant kernel of a step: the slowest of the joiner's products
         tf_peak, tf_kind = measured_tensor_peak()
-        top = max((k for k in stages if "tflops" in stages[k] and k.startswith("joiner_")),
-                  key=lambda k: stages[k]["ms"])
-        line["roofline"] = {"kernel": top + " (linear_umma_kernel, 3xTF32 tcgen05)", "bound": "tensor",
-                            "achieved": stages[top]["tflops"], "peak": tf_peak, "unit": "TFLOP/s",
-                            "frac": round(stages[top]["tflops"] / tf_peak, 4),
-                            "peak_kind": f"dense bf16 burst, of {tf_kind}",
-                            "note": "achieved counts the useful 2*M*N*K flops of an fp32-accurate product; "
-                                    "the kernel issues 3x that as tf32 MMAs, and tf32 runs at half the bf16 "
-                                    "rate, so 1/6 of the bf16 peak is the ceiling of this formulation",
-                            "issued_tflops": round(3 * stages[top]["tflops"], 1),
-                            "traffic": NCU_TRAFFIC_C3.get(top) if args.workload == "c3" else None}
-        # and the slowest kernel of the loss path proper
-        single = [k for k in stages if not k.startswith(("simple_", "joiner_"))]
+        if products:
+            top = max(products, key=lambda k: stages[k]["ms"])
+            pairs = args.joiner == "fused"
+            line["roofline"] = {
+                "kernel": top + (" (pair_umma_kernel, fp16-pair tcgen05)" if pairs else
+                                 " (linear_umma_kernel, 3xTF32 tcgen05)"),
+                "bound": "tensor", "achieved": stages[top]["tflops"], "peak": tf_peak, "unit": "TFLOP/s",
+                "frac": round(stages[top]["tflops"] / tf_peak, 4),
+                "peak_kind": f"dense bf16 burst, of {tf_kind}",
+                "note": ("achieved counts the useful 2*M*N*K flops of an fp32-accurate product; the "
+                         "kernel issues 3x that as fp16 MMAs (hi*hi + hi*lo + lo*hi), so 1/3 of the "
+                         "16-bit peak is the ceiling of this formulation" if pairs else
+                         "achieved counts the useful 2*M*N*K flops of an fp32-accurate product; the "
+                         "kernel issues 3x that as tf32 MMAs, and tf32 runs at half the bf16 rate, so "
+                         "1/6 of the bf16 peak is the ceiling of this formulation"),
+                "issued_tflops": round(3 * stages[top]["tflops"], 1),
+                "traffic": NCU_TRAFFIC_C3.get(top) if args.workload == "c3" else None}
+        # and the slowest single-kernel stage among the others the step launches
+        single = [k for k in in_step if not k.startswith(("simple_", "fused_")) and k not in products]
         lp = max(single, key=lambda k: stages[k]["ms"])
         line["roofline_loss_path"] = {
             "kernel": lp, "bound": "hbm", "achieved": stages[lp]["gbs"], "peak": hbm_gbs, "unit": "GB/s",
@@ -622,12 +814,32 @@ def main():
         torch.set_num_threads(os.cpu_count() or 1)
         sample = min(batch, 16)
         cpu_steps = 20 if args.workload == "c3" else 3   # about 10 s of host work
-        v, ms = cpu_reference_run(args.workload, sample, cpu_steps, 1)
+        v, ms, kind, cpu_loss, cpu_grads = cpu_reference_run(args.workload, sample, cpu_steps, 1)
+        what = ("the reference's own python package on its CPU extension" if kind == "reference"
+                else "CPU oracle port: torch CPU ops + C recursion")
         line["cpu_baseline"] = {"value": round(v, 3), "unit": "utt/s",
-                                "cores": torch.get_num_threads(), "kind": "port",
-                                "sample": f"{sample} utterances of the {args.workload} batch, {cpu_steps} steps "
-                                          f"(CPU oracle: torch CPU ops + C recursion)",
+                                "cores": torch.get_num_threads(), "kind": kind,
+                                "sample": f"{sample} utterances of the {args.workload} batch, {cpu_steps} "
+                                          f"steps ({what})",
                                 "ms_per_step": round(ms, 2)}
+        # the same utterances through the timed GPU path: loss against the CPU leg's loss
+        wl_s = workloads.pipeline_workload(args.workload, batch=sample)
+        ts = {k: wl_s[k].to(dev) for k in TENSOR_KEYS}
+        gpu_loss = float(make_step(fr, wl_s, args.joiner)(ts))
+        line["parity"] = {"cpu_loss": cpu_loss, "gpu_loss": gpu_loss,
+                          "rel_err": abs(gpu_loss - cpu_loss) / abs(cpu_loss),
+                          "what": f"simple + pruned loss of the CPU leg's {sample} utterances, this "
+                                  "library on the GPU (own prune ranges) against the CPU leg"}
+        if args.workload == "c3":
+            try:
+                ref_cuda, noise = reference_cuda_run(args.workload, batch, sample,
+                                                     cpu_grads if kind == "reference" else None, dev)
+            except Exception as e:  # pragma: no cover
+                ref_cuda, noise = {"unavailable": f"{type(e).__name__}: {e}"[:200]}, None
+            if ref_cuda is not None:
+                line["reference_cuda"] = ref_cuda
+            if noise is not None:
+                line["noise_floor"] = noise
     if rank == 0:
         print(json.dumps(line))
     if world > 1:

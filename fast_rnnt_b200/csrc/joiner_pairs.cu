@@ -24,6 +24,8 @@
 //              enc_grad / dec_grad from one pass over gz;  W_grad = g^T * act, split-K.
 #include <cuda_fp16.h>
 
+#include <algorithm>
+
 #include "lsm_band.cuh"
 #include "umma_pairs.cuh"
 
@@ -430,6 +432,44 @@ lsm_backward_pairs_kernel(const float *__restrict__ logits, const int64_t *__res
   }
 }
 
+// ---- plain products on planes (the engine without the joiner around it) -------------------------
+// D = acc * inv_scale_a * inv_scale_b (+ bias[n])
+struct PlainPairExt {
+  float *out;  // [splits][M][N]
+  const float *bias, *inv_a, *inv_b;
+  int M, N;
+  struct Row {
+    float sc;
+  };
+  __device__ void row_begin(Row &r, int, int, int) const { r.sc = *inv_a * *inv_b; }
+  __device__ float *out_row(int z, int m) const { return out + ((size_t)z * M + m) * N; }
+  __device__ void finish(Row &r, int, int, int n, float (&v)[16]) const {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = v[i] * r.sc + ((bias != nullptr && n + i < N) ? bias[n + i] : 0.f);
+  }
+  __device__ void row_end(Row &, int, int, int) const {}
+};
+
+// x [rows][cols] -> planes [rows][pitch], scaled by the power of two that the largest
+// magnitude (from the per-CTA partial maxima) asks for
+__global__ void __launch_bounds__(256)
+split_matrix_kernel(const float *__restrict__ x, long long rows, int cols, long long pitch,
+                    const float *__restrict__ part, int nparts, __half *__restrict__ hi,
+                    __half *__restrict__ lo, float *__restrict__ inv_scale) {
+  __shared__ float slot;
+  const float scale = fp16_pair_scale(block_max_of_partials(part, nparts, &slot));
+  if (blockIdx.x == 0 && threadIdx.x == 0) *inv_scale = 1.f / scale;
+  const long long n = rows * cols;
+  for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < n; i += (long long)gridDim.x * 256) {
+    const long long r = i / cols;
+    const int c = (int)(i - r * cols);
+    __half h, l;
+    fp16_pair(x[i], scale, h, l);
+    hi[r * pitch + c] = h;
+    lo[r * pitch + c] = l;
+  }
+}
+
 static int pjl_check(int B, int T, int R, int S, int C, int D, int blank, int rnnt_type) {
   FRNNT_REQUIRE(B >= 0 && T >= 0 && R >= 1 && S >= 0 && C >= 1 && D >= 1, FRNNT_EINVAL,
                 "bad sizes B=%d T=%d R=%d S=%d C=%d D=%d", B, T, R, S, C, D);
@@ -618,6 +658,84 @@ extern "C" int frnnt_pruned_joiner_logprobs_backward(const float *px_grad, const
       FRNNT_KERNEL(ordered_sum_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(dw_part, weight_grad, n, splits));
       FRNNT_CUDA(cudaGetLastError());
     }
+  }
+  return FRNNT_OK;
+}
+
+// ---- plain products on planes ---------------------------------------------------------------------
+extern "C" size_t frnnt_pairs_scratch_floats(void) { return kMaxParts; }
+
+extern "C" int frnnt_pairs_from_f32(const float *x, long long rows, int cols, long long pitch, void *hi,
+                                    void *lo, float *inv_scale, float *scratch, void *stream) {
+  FRNNT_REQUIRE(rows >= 0 && cols >= 0 && pitch >= cols && pitch % 8 == 0, FRNNT_EINVAL,
+                "bad sizes rows=%lld cols=%d pitch=%lld (the pitch must be a multiple of 8)", rows, cols, pitch);
+  if (rows == 0 || cols == 0) return FRNNT_OK;
+  FRNNT_REQUIRE(x && hi && lo && inv_scale && scratch, FRNNT_EINVAL, "NULL argument");
+  cudaStream_t st = (cudaStream_t)stream;
+  const long long n = rows * cols;
+  const int parts = parts_for(n);
+  const int grid = (int)std::min<long long>((n + 255) / 256, (long long)sm_count() * 16);
+  FRNNT_KERNEL(absmax_partial_kernel<<<parts, 256, 0, st>>>(x, n, scratch));
+  FRNNT_KERNEL(split_matrix_kernel<<<grid, 256, 0, st>>>(x, rows, cols, pitch, scratch, parts, (__half *)hi,
+                                                        (__half *)lo, inv_scale));
+  FRNNT_CUDA(cudaGetLastError());
+  return FRNNT_OK;
+}
+
+extern "C" int frnnt_pair_matmul_nt(const void *a_hi, const void *a_lo, const void *b_hi, const void *b_lo,
+                                    const float *inv_scale_a, const float *inv_scale_b, const float *bias,
+                                    float *d, int M, int N, int K, long long pitch_a, long long pitch_b,
+                                    void *stream) {
+  FRNNT_REQUIRE(M >= 0 && N >= 0 && K > 0, FRNNT_EINVAL, "bad sizes M=%d N=%d K=%d", M, N, K);
+  if (M == 0 || N == 0) return FRNNT_OK;
+  FRNNT_REQUIRE(a_hi && a_lo && b_hi && b_lo && inv_scale_a && inv_scale_b && d, FRNNT_EINVAL, "NULL argument");
+  FRNNT_REQUIRE((uintptr_t)d % 16 == 0, FRNNT_EINVAL, "d is misaligned");
+  CUtensorMap mah, mal, mbh, mbl;
+  int rc = make_pair_map(&mah, a_hi, M, K, pitch_a, false);
+  if (rc == FRNNT_OK) rc = make_pair_map(&mal, a_lo, M, K, pitch_a, false);
+  if (rc == FRNNT_OK) rc = make_pair_map(&mbh, b_hi, N, K, pitch_b, false);
+  if (rc == FRNNT_OK) rc = make_pair_map(&mbl, b_lo, N, K, pitch_b, false);
+  if (rc != FRNNT_OK) return rc;
+  const LinShape shape{M, N, K, ((K + kPairBK - 1) / kPairBK) * kPairBK, (M + kPairTile - 1) / kPairTile,
+                       (N + kPairTile - 1) / kPairTile, 1};
+  return launch_pair_umma<false, false>(mah, mal, mbh, mbl, shape,
+                                        PlainPairExt{d, bias, inv_scale_a, inv_scale_b, M, N},
+                                        (cudaStream_t)stream);
+}
+
+extern "C" int frnnt_pair_matmul_tn_splits(int M, int N, long long R) { return pair_tn_splits(M, N, R); }
+
+extern "C" int frnnt_pair_matmul_tn(const void *a_hi, const void *a_lo, const void *b_hi, const void *b_lo,
+                                    const float *inv_scale_a, const float *inv_scale_b, float *d,
+                                    float *partials, int M, int N, long long R, long long pitch_a,
+                                    long long pitch_b, void *stream) {
+  FRNNT_REQUIRE(M >= 0 && N >= 0 && R > 0 && R < (1LL << 31) - 256, FRNNT_EINVAL,
+                "bad sizes M=%d N=%d R=%lld", M, N, R);
+  if (M == 0 || N == 0) return FRNNT_OK;
+  FRNNT_REQUIRE(a_hi && a_lo && b_hi && b_lo && inv_scale_a && inv_scale_b && d, FRNNT_EINVAL, "NULL argument");
+  const int splits = pair_tn_splits(M, N, R);
+  FRNNT_REQUIRE(splits == 1 || partials != nullptr, FRNNT_EINVAL,
+                "a scratch of frnnt_pair_matmul_tn_splits() * M * N floats is required");
+  FRNNT_REQUIRE((uintptr_t)d % 16 == 0 && (uintptr_t)partials % 16 == 0, FRNNT_EINVAL, "misaligned buffer");
+  CUtensorMap mah, mal, mbh, mbl;
+  int rc = make_pair_map(&mah, a_hi, (int)R, M, pitch_a, true);
+  if (rc == FRNNT_OK) rc = make_pair_map(&mal, a_lo, (int)R, M, pitch_a, true);
+  if (rc == FRNNT_OK) rc = make_pair_map(&mbh, b_hi, (int)R, N, pitch_b, true);
+  if (rc == FRNNT_OK) rc = make_pair_map(&mbl, b_lo, (int)R, N, pitch_b, true);
+  if (rc != FRNNT_OK) return rc;
+  const long long kblocks = (R + kPairBK - 1) / kPairBK;
+  const int k_per_split = (int)((kblocks + splits - 1) / splits) * kPairBK;
+  const LinShape shape{M, N, (int)R, k_per_split, (M + kPairTile - 1) / kPairTile,
+                       (N + kPairTile - 1) / kPairTile, splits};
+  cudaStream_t st = (cudaStream_t)stream;
+  float *out = splits == 1 ? d : partials;
+  rc = launch_pair_umma<true, true>(mah, mal, mbh, mbl, shape,
+                                    PlainPairExt{out, nullptr, inv_scale_a, inv_scale_b, M, N}, st);
+  if (rc != FRNNT_OK) return rc;
+  if (splits > 1) {
+    const long long n = (long long)M * N;
+    FRNNT_KERNEL(ordered_sum_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(partials, d, n, splits));
+    FRNNT_CUDA(cudaGetLastError());
   }
   return FRNNT_OK;
 }

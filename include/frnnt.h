@@ -328,6 +328,33 @@ int frnnt_pruned_joiner_logprobs_backward(const float *px_grad, const float *py_
                                           float *bias_grad, int B, int T, int R, int S, int C, int D,
                                           int blank, int rnnt_type, void *stream);
 
+/* ----------------------------------------------------------------------------
+ * Products of matrices stored as pairs of fp16 planes (no counterpart in the reference)
+ * ------------------------------------------------------------------------- */
+
+/* The engine behind the fused joiner on its own.  A float32 matrix x [rows][cols] becomes
+ * two fp16 planes hi, lo [rows][pitch] (pitch >= cols, a multiple of 8) with
+ * x * 2^e = hi + lo, e chosen from the largest |x|; *inv_scale (device) receives 2^-e.
+ * `scratch` holds frnnt_pairs_scratch_floats() floats. */
+size_t frnnt_pairs_scratch_floats(void);
+int frnnt_pairs_from_f32(const float *x, long long rows, int cols, long long pitch, void *hi, void *lo,
+                         float *inv_scale, float *scratch, void *stream);
+
+/* D[M][N] = A[M][K] * B[N][K]^T (+ bias[N]), A and B given as planes with row pitches
+ * pitch_a / pitch_b (in halves) and their inverse scales (device pointers). */
+int frnnt_pair_matmul_nt(const void *a_hi, const void *a_lo, const void *b_hi, const void *b_lo,
+                         const float *inv_scale_a, const float *inv_scale_b, const float *bias,
+                         float *d, int M, int N, int K, long long pitch_a, long long pitch_b,
+                         void *stream);
+
+/* D[M][N] = A[R][M]^T * B[R][N]; the reduction over R is split over
+ * frnnt_pair_matmul_tn_splits(M, N, R) work items per output tile, `partials` is scratch of
+ * splits*M*N floats (may be NULL when splits == 1); partial sums are added in order. */
+int frnnt_pair_matmul_tn_splits(int M, int N, long long R);
+int frnnt_pair_matmul_tn(const void *a_hi, const void *a_lo, const void *b_hi, const void *b_lo,
+                         const float *inv_scale_a, const float *inv_scale_b, float *d, float *partials,
+                         int M, int N, long long R, long long pitch_a, long long pitch_b, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

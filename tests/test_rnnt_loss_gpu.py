@@ -369,7 +369,9 @@ def assert_as_close_as_the_reference(ours, g, key, atol):
         r64 = g[key + "_f64_sample"]
         fin = torch.isfinite(r64)
         noise = float((ref.double()[fin] - r64[fin]).abs().max())
-    assert_close(samp(ours), ref, 0, atol + 2 * noise, key)
+    # ... plus float32 rounding of long sums in another order: 2e-6 of the largest entry
+    scale = float(ref[torch.isfinite(ref)].abs().max())
+    assert_close(samp(ours), ref, 0, atol + 2 * noise + 2e-6 * scale, key)
     return noise
 
 
