@@ -204,7 +204,6 @@ pruned_tanh_pairs_kernel(const float *__restrict__ enc, const float *__restrict_
 // ---- epilogues of the three products ----------------------------------------------------------
 // logits = acc * (1/scales) + bias, and per row and tile (max, sum exp(logit - max))
 struct PjlFwdExt {
-  float *out;
   const float *bias;
   float2 *stats;
   const float *scales;
@@ -217,8 +216,8 @@ struct PjlFwdExt {
     r.mx = -INFINITY;
     r.sum = 0.f;
   }
-  __device__ float *out_row(int, int m) const { return out + (size_t)m * N; }
-  __device__ void finish(Row &r, int, int, int n, float (&v)[16]) const {
+  __device__ void prefetch(Row &, int, int, int) const {}
+  __device__ void finish(Row &r, int, int, int n, float (&v)[16], int) const {
     float cm = -INFINITY;
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
@@ -242,29 +241,37 @@ struct PjlFwdExt {
 
 // gz = acc * (1/scales) * (1 - act^2): the gradient with respect to enc + dec
 struct PjlGradInExt {
-  float *out;
   const __half *act_hi, *act_lo;
   const float *scales;
   int N;  // = D
   struct Row {
     float sc;
+    uint4 h[4], l[4];  // the 32 activations (two planes) of the columns that come next
   };
   __device__ void row_begin(Row &r, int, int, int) const { r.sc = scales[kScaleG] * scales[kScaleW]; }
-  __device__ float *out_row(int, int m) const { return out + (size_t)m * N; }
-  __device__ void finish(Row &r, int, int m, int n, float (&v)[16]) const {
-    const __half *h = act_hi + (size_t)m * N + n, *l = act_lo + (size_t)m * N + n;
-    if (n + 16 <= N) {
+  __device__ void prefetch(Row &r, int, int m, int n) const {
+    if (n + 32 <= N) {
+      const uint4 *h = reinterpret_cast<const uint4 *>(act_hi + (size_t)m * N + n);
+      const uint4 *l = reinterpret_cast<const uint4 *>(act_lo + (size_t)m * N + n);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) r.h[i] = h[i], r.l[i] = l[i];
+    }
+  }
+  __device__ void finish(Row &r, int, int m, int n, float (&v)[16], int half) const {
+    const int n32 = n - 16 * half;
+    if (n32 + 32 <= N) {
       __align__(16) __half hh[16], ll[16];
-      *reinterpret_cast<uint4 *>(hh) = *reinterpret_cast<const uint4 *>(h);
-      *reinterpret_cast<uint4 *>(hh + 8) = *reinterpret_cast<const uint4 *>(h + 8);
-      *reinterpret_cast<uint4 *>(ll) = *reinterpret_cast<const uint4 *>(l);
-      *reinterpret_cast<uint4 *>(ll + 8) = *reinterpret_cast<const uint4 *>(l + 8);
+      *reinterpret_cast<uint4 *>(hh) = r.h[2 * half];
+      *reinterpret_cast<uint4 *>(hh + 8) = r.h[2 * half + 1];
+      *reinterpret_cast<uint4 *>(ll) = r.l[2 * half];
+      *reinterpret_cast<uint4 *>(ll + 8) = r.l[2 * half + 1];
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
         const float a = (__half2float(hh[i]) + __half2float(ll[i])) * (1.f / kActScale);
         v[i] = v[i] * r.sc * (1.f - a * a);
       }
     } else {
+      const __half *h = act_hi + (size_t)m * N + n, *l = act_lo + (size_t)m * N + n;
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
         if (n + i < N) {
@@ -279,15 +286,13 @@ struct PjlGradInExt {
 
 // W_grad partial sums: acc * (1/scales)
 struct PjlGradWExt {
-  float *out;  // [splits][M][N]
   const float *scales;
-  int M, N;
   struct Row {
     float sc;
   };
   __device__ void row_begin(Row &r, int, int, int) const { r.sc = scales[kScaleG] * scales[kScaleAct]; }
-  __device__ float *out_row(int z, int m) const { return out + ((size_t)z * M + m) * N; }
-  __device__ void finish(Row &r, int, int, int, float (&v)[16]) const {
+  __device__ void prefetch(Row &, int, int, int) const {}
+  __device__ void finish(Row &r, int, int, int, float (&v)[16], int) const {
 #pragma unroll
     for (int i = 0; i < 16; ++i) v[i] *= r.sc;
   }
@@ -302,6 +307,27 @@ __global__ void ordered_sum_kernel(const float *__restrict__ partial, float *__r
   float acc = 0;
   for (int z = 0; z < parts; ++z) acc += partial[(size_t)z * n + i];
   out[i] = acc;
+}
+
+// the same for many parts of a short vector (column sums per CTA -> bias gradient): 32
+// columns per CTA, eight warps take the parts z = w, w + 8, ... and their sums are added
+// in warp order -- a fixed order, with eight loads in flight per column instead of one
+__global__ void __launch_bounds__(256)
+ordered_sum_tall_kernel(const float *__restrict__ partial, float *__restrict__ out, int n, int parts) {
+  __shared__ float s[8][33];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int i = blockIdx.x * 32 + lane;
+  float acc = 0.f;
+  if (i < n)
+    for (int z = w; z < parts; z += 8) acc += partial[(size_t)z * n + i];
+  s[w][lane] = acc;
+  __syncthreads();
+  if (w == 0 && i < n) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += s[k][lane];
+    out[i] = t;
+  }
 }
 
 // ---- bands ------------------------------------------------------------------------------------
@@ -369,9 +395,11 @@ band_grad_kernel(const float *__restrict__ g_px, const float *__restrict__ g_py,
 
 // g[row][c] = -(gx + gy) * exp(logit - lse) + gx * [c == symbol] + gy * [c == blank], written
 // as planes (|g| <= |gx| + |gy|, whose maximum sets the scale); one warp per row.  Column
-// sums of g (the bias gradient): every warp adds its rows into its own row of a shared
-// array, lane <-> fixed columns, the warps' rows are added in order at the end -> one
-// partial per CTA, no atomics.
+// sums of g (the bias gradient): lane <-> fixed columns, so every warp sums its rows
+// privately -- in registers when a lane owns at most four 4-column vectors (C <= 512),
+// else in its own row of a shared array -- and the warps' sums are added in order at the
+// end -> one partial per CTA, no atomics.
+template <bool REG_SUMS>
 __global__ void __launch_bounds__(32 * kRowWarps)
 lsm_backward_pairs_kernel(const float *__restrict__ logits, const int64_t *__restrict__ symbols,
                           const int64_t *__restrict__ ranges, const float *__restrict__ lse,
@@ -385,13 +413,18 @@ lsm_backward_pairs_kernel(const float *__restrict__ logits, const int64_t *__res
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const float scale = fp16_pair_scale(block_max_of_partials(gmax_part, nparts, &slot));
   if (blockIdx.x == 0 && threadIdx.x == 0) scales[kScaleG] = 1.f / scale;
-  for (int i = threadIdx.x; i < warps_used * C; i += blockDim.x) cs[i] = 0.f;
-  __syncthreads();
+  if (!REG_SUMS) {
+    for (int i = threadIdx.x; i < warps_used * C; i += blockDim.x) cs[i] = 0.f;
+    __syncthreads();
+  }
+  const int nvec = C / 4;
+  float4 racc[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) racc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
   if (warp < warps_used) {
     float4 *mine = reinterpret_cast<float4 *>(cs + (size_t)warp * C);
     const long long warp0 = (long long)blockIdx.x * warps_used + warp;
     const long long nwarps = (long long)gridDim.x * warps_used;
-    const int nvec = C / 4;
     for (long long row = warp0; row < rows; row += nwarps) {
       const long long bt = row / R;
       const int k = (int)(row % R), b = (int)(bt / T);
@@ -402,7 +435,7 @@ lsm_backward_pairs_kernel(const float *__restrict__ logits, const int64_t *__res
       const float4 *src = reinterpret_cast<const float4 *>(logits + (size_t)row * C);
       uint2 *dh = reinterpret_cast<uint2 *>(g_hi + (size_t)row * Cp);
       uint2 *dl = reinterpret_cast<uint2 *>(g_lo + (size_t)row * Cp);
-      for (int v = lane; v < nvec; v += 32) {
+      auto one = [&](int v, float4 &sum) {
         const float4 q = src[v];
         const float x[4] = {q.x, q.y, q.z, q.w};
         float g[4];
@@ -418,9 +451,27 @@ lsm_backward_pairs_kernel(const float *__restrict__ logits, const int64_t *__res
         }
         dh[v] = *reinterpret_cast<const uint2 *>(hi);
         dl[v] = *reinterpret_cast<const uint2 *>(lo);
-        float4 a = mine[v];
-        a.x += g[0], a.y += g[1], a.z += g[2], a.w += g[3];
-        mine[v] = a;
+        sum.x += g[0], sum.y += g[1], sum.z += g[2], sum.w += g[3];
+      };
+      if (REG_SUMS) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int v = lane + 32 * j;
+          if (v < nvec) one(v, racc[j]);
+        }
+      } else {
+        for (int v = lane; v < nvec; v += 32) {
+          float4 a = mine[v];
+          one(v, a);
+          mine[v] = a;
+        }
+      }
+    }
+    if (REG_SUMS) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int v = lane + 32 * j;
+        if (v < nvec) mine[v] = racc[j];
       }
     }
   }
@@ -435,15 +486,14 @@ lsm_backward_pairs_kernel(const float *__restrict__ logits, const int64_t *__res
 // ---- plain products on planes (the engine without the joiner around it) -------------------------
 // D = acc * inv_scale_a * inv_scale_b (+ bias[n])
 struct PlainPairExt {
-  float *out;  // [splits][M][N]
   const float *bias, *inv_a, *inv_b;
-  int M, N;
+  int N;
   struct Row {
     float sc;
   };
   __device__ void row_begin(Row &r, int, int, int) const { r.sc = *inv_a * *inv_b; }
-  __device__ float *out_row(int z, int m) const { return out + ((size_t)z * M + m) * N; }
-  __device__ void finish(Row &r, int, int, int n, float (&v)[16]) const {
+  __device__ void prefetch(Row &, int, int, int) const {}
+  __device__ void finish(Row &r, int, int, int n, float (&v)[16], int) const {
 #pragma unroll
     for (int i = 0; i < 16; ++i) v[i] = v[i] * r.sc + ((bias != nullptr && n + i < N) ? bias[n + i] : 0.f);
   }
@@ -555,8 +605,8 @@ extern "C" int frnnt_pruned_joiner_logprobs_forward(const float *enc, const floa
   FRNNT_CUDA(cudaGetLastError());
   const int mt = (M + kPairTile - 1) / kPairTile;
   const LinShape shape{M, C, D, ((D + kPairBK - 1) / kPairBK) * kPairBK, mt, L.tiles_n, 1};
-  rc = launch_pair_umma<false, false>(mah, mal, mbh, mbl, shape,
-                                      PjlFwdExt{logits, bias, stats, scales, C, L.tiles_n}, st);
+  rc = launch_pair_umma<false, false>(mah, mal, mbh, mbl, logits, shape,
+                                      PjlFwdExt{bias, stats, scales, C, L.tiles_n}, st);
   if (rc != FRNNT_OK) return rc;
   FRNNT_KERNEL(joiner_band_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(
       logits, stats, symbols, ranges, lse, pxb, pyb, rows, T, R, S, C, blank, L.tiles_n));
@@ -619,7 +669,7 @@ extern "C" int frnnt_pruned_joiner_logprobs_backward(const float *px_grad, const
     while (warps_used > 1 && (size_t)warps_used * C * 4 > 160 * 1024) --warps_used;
     FRNNT_REQUIRE((size_t)warps_used * C * 4 <= 200 * 1024, FRNNT_EUNSUPPORTED, "C=%d too large", C);
     const size_t smem = (size_t)warps_used * C * 4;
-    auto kern = lsm_backward_pairs_kernel;
+    auto kern = C <= 512 ? lsm_backward_pairs_kernel<true> : lsm_backward_pairs_kernel<false>;
     FRNNT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     FRNNT_KERNEL(kern<<<L.cs_ctas, 32 * kRowWarps, smem, st>>>(logits, symbols, ranges, lse, gxb, gyb, gmax, gparts,
                                                              g_hi, g_lo, cs_part, scales, rows, T, R, S, C,
@@ -627,13 +677,13 @@ extern "C" int frnnt_pruned_joiner_logprobs_backward(const float *px_grad, const
   }
   FRNNT_CUDA(cudaGetLastError());
   if (bias_grad != nullptr) {
-    FRNNT_KERNEL(ordered_sum_kernel<<<(unsigned)((C + 255) / 256), 256, 0, st>>>(cs_part, bias_grad, C, L.cs_ctas));
+    FRNNT_KERNEL(ordered_sum_tall_kernel<<<(unsigned)((C + 31) / 32), 256, 0, st>>>(cs_part, bias_grad, C, L.cs_ctas));
     FRNNT_CUDA(cudaGetLastError());
   }
   const int mt = (M + kPairTile - 1) / kPairTile;
   if (enc_grad != nullptr) {
     const LinShape shape{M, D, C, ((C + kPairBK - 1) / kPairBK) * kPairBK, mt, (D + kPairTile - 1) / kPairTile, 1};
-    rc = launch_pair_umma<false, false>(gih, gil, wth, wtl, shape, PjlGradInExt{gz, act_hi, act_lo, scales, D}, st);
+    rc = launch_pair_umma<false, false>(gih, gil, wth, wtl, gz, shape, PjlGradInExt{act_hi, act_lo, scales, D}, st);
     if (rc != FRNNT_OK) return rc;
     if (D % 4 == 0 && D <= 3200) {
       rc = frnnt_joiner_input_grads(gz, ranges, enc_grad, dec_grad, sc + L.jg, B, S + 1, T, R, D, stream);
@@ -651,7 +701,7 @@ extern "C" int frnnt_pruned_joiner_logprobs_backward(const float *px_grad, const
     const LinShape shape{C, D, M, k_per_split, (C + kPairTile - 1) / kPairTile, (D + kPairTile - 1) / kPairTile,
                          splits};
     float *out = splits == 1 ? weight_grad : dw_part;
-    rc = launch_pair_umma<true, true>(gwh, gwl, ach, acl, shape, PjlGradWExt{out, scales, C, D}, st);
+    rc = launch_pair_umma<true, true>(gwh, gwl, ach, acl, out, shape, PjlGradWExt{scales}, st);
     if (rc != FRNNT_OK) return rc;
     if (splits > 1) {
       const long long n = (long long)C * D;
@@ -698,9 +748,8 @@ extern "C" int frnnt_pair_matmul_nt(const void *a_hi, const void *a_lo, const vo
   if (rc != FRNNT_OK) return rc;
   const LinShape shape{M, N, K, ((K + kPairBK - 1) / kPairBK) * kPairBK, (M + kPairTile - 1) / kPairTile,
                        (N + kPairTile - 1) / kPairTile, 1};
-  return launch_pair_umma<false, false>(mah, mal, mbh, mbl, shape,
-                                        PlainPairExt{d, bias, inv_scale_a, inv_scale_b, M, N},
-                                        (cudaStream_t)stream);
+  return launch_pair_umma<false, false>(mah, mal, mbh, mbl, d, shape,
+                                        PlainPairExt{bias, inv_scale_a, inv_scale_b, N}, (cudaStream_t)stream);
 }
 
 extern "C" int frnnt_pair_matmul_tn_splits(int M, int N, long long R) { return pair_tn_splits(M, N, R); }
@@ -729,8 +778,8 @@ extern "C" int frnnt_pair_matmul_tn(const void *a_hi, const void *a_lo, const vo
                        (N + kPairTile - 1) / kPairTile, splits};
   cudaStream_t st = (cudaStream_t)stream;
   float *out = splits == 1 ? d : partials;
-  rc = launch_pair_umma<true, true>(mah, mal, mbh, mbl, shape,
-                                    PlainPairExt{out, nullptr, inv_scale_a, inv_scale_b, M, N}, st);
+  rc = launch_pair_umma<true, true>(mah, mal, mbh, mbl, out, shape,
+                                    PlainPairExt{nullptr, inv_scale_a, inv_scale_b, N}, st);
   if (rc != FRNNT_OK) return rc;
   if (splits > 1) {
     const long long n = (long long)M * N;

@@ -13,7 +13,7 @@
 // 2^-18 of the largest keep all 22 bits, smaller ones an absolute error of 2^-40 of the
 // largest (see fp16_pair()).  The scales are undone in the epilogue (exactly).
 //
-// Kernel structure (one 128x128 output tile per work item, 6 warps, one persistent CTA
+// Kernel structure (one 128x128 output tile per work item, 10 warps, one persistent CTA
 // per SM):
 //   warp 0   : TMA producer.  Per 64-wide K slice four 16 KB boxes (A hi, A lo, B hi, B lo)
 //              land in 128-byte-swizzled tiles; 3-stage ring; rows / columns outside the
@@ -22,19 +22,29 @@
 //              index): two boxes of 64 values x 64 k rows.
 //   warp 1   : one thread issues, per K = 16 step, hi*hi, hi*lo, lo*hi into a 128x128 fp32
 //              accumulator in tensor memory.  The tensor core adds into its accumulator
-//              with truncation, so every 128-wide K group gets a fresh accumulator and
-//   warps 2-5 fold finished groups into a running sum with round-to-nearest adds
-//              (tcgen05.ld / add / tcgen05.st), one group behind the MMAs, and run the
-//              epilogue while the other warps are already on the next item.
+//              with truncation, so every 128-wide K group gets a fresh accumulator (two
+//              alternate) and
+//   warps 2-9: two sets of four fold / epilogue warps, one set per tile in turn.  A set
+//              folds the finished groups of its tile into its own running sum in tensor
+//              memory with round-to-nearest adds (tcgen05.ld / add / tcgen05.st), which
+//              frees the accumulator at once, and then runs the epilogue from the running
+//              sum -- policy, 32x32 boxes staged in shared memory, TMA stores -- while the
+//              other set already folds the next tile: the epilogue has a whole tile's
+//              time and never holds an accumulator.
 // No multicast, no clusters.  Every wait is bounded; a timeout poisons the tile with NaN.
 //
 // Policy ("Ext") interface, all __device__:
 //   struct Row;                                    per-row state across one tile's columns
 //   void row_begin(Row &, int z, int m, int n0) const;
-//   void finish(Row &, int z, int m, int n, float (&v)[16]) const;   columns n..n+15 of
-//                                                  row m, in place; only columns < N count
+//   void prefetch(Row &, int z, int m, int n) const;      columns n..n+31 come next: loads
+//                                                  the policy needs for them may start
+//   void finish(Row &, int z, int m, int n, float (&v)[16], int half) const;   columns
+//                                                  n..n+15 of row m (half = 0 / 1 of the
+//                                                  prefetched 32), in place; only columns
+//                                                  below N count
 //   void row_end(Row &, int z, int m, int n0) const;
-//   float *out_row(int z, int m) const;            where row m of the result goes
+// The result goes out through a tensor map of the output (rows beyond M and columns
+// beyond N are clipped by the TMA store).
 #pragma once
 #include <cuda_fp16.h>
 
@@ -42,16 +52,17 @@
 
 namespace frnnt {
 
-constexpr int kPairThreads = 192;  // TMA warp, MMA warp, 4 fold / epilogue warps
-constexpr int kPairFolders = 4;
+constexpr int kPairThreads = 320;  // TMA warp, MMA warp, 2 x 4 fold / epilogue warps
+constexpr int kPairFolders = 4;    // warps of one set
 constexpr int kPairTile = 128;
 constexpr int kPairBK = 64;        // K slice: 128 bytes of fp16 per row
 constexpr int kPairStages = 3;
 constexpr int kPairGroup = 2;      // K slices per accumulator group (128 values of K)
 constexpr uint32_t kPairOpBytes = kPairTile * 128;       // one plane of one operand tile
 constexpr uint32_t kPairStageBytes = 4 * kPairOpBytes;   // A hi, A lo, B hi, B lo
-constexpr size_t kPairSmemBytes = (size_t)kPairStages * kPairStageBytes + 1024;
-// tensor-memory columns: two group accumulators and the running sum
+constexpr uint32_t kPairBoxBytes = 32 * 128;             // a 32 x 32 float box of the output
+constexpr size_t kPairSmemBytes = (size_t)kPairStages * kPairStageBytes + 8 * kPairBoxBytes + 1024;
+// tensor-memory columns: two group accumulators, one running sum per fold set
 constexpr uint32_t kPairCols = 512, kPairAcc1 = 128, kPairRun = 256;
 
 // x * scale as a pair of fp16 values.  |x * scale| must stay below 65504.  hi has 11
@@ -95,6 +106,28 @@ __device__ __forceinline__ void mma_f16_ss(uint32_t tmem_d, uint64_t adesc, uint
       : "memory");
 }
 
+// box in shared memory -> global, clipped at the tensor's edges; completion is tracked
+// by the issuing thread's bulk groups
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, uint32_t smem_src, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"((uint64_t)map), "r"(smem_src), "r"(x), "r"(y), "r"(z)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// until the stores issued by this thread have READ their shared memory
+__device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+
+// mbar_wait that also gives up as soon as another role of the CTA has given up
+__device__ __forceinline__ bool mbar_wait_watch(uint64_t *bar, uint32_t parity, volatile int *failed) {
+  for (int it = 0; it < kWaitLimit; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 63) == 63 && *failed) return false;
+  }
+  return false;
+}
+
 struct PairTile {
   int m0, n0, z, KB, k_begin;
 };
@@ -117,11 +150,14 @@ template <bool A_MN, bool B_MN, class Ext>
 __global__ void __launch_bounds__(kPairThreads, 1)
 pair_umma_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constant__ CUtensorMap map_alo,
                  const __grid_constant__ CUtensorMap map_bhi, const __grid_constant__ CUtensorMap map_blo,
-                 LinShape p, Ext ext) {
+                 const __grid_constant__ CUtensorMap map_out, LinShape p, Ext ext) {
   extern __shared__ uint8_t smem_dyn[];
   __shared__ __align__(8) uint64_t bar_full[kPairStages];   // TMA bytes have landed
   __shared__ __align__(8) uint64_t bar_empty[kPairStages];  // the MMAs are done with the stage
-  __shared__ __align__(8) uint64_t bar_grp[2];              // a group's accumulator is complete
+  // a group's accumulator is complete: one barrier per (fold set, accumulator), because a
+  // parity wait can only tell the current phase from the one before it -- a set must find
+  // nothing but its own tiles' groups on the barriers it waits on
+  __shared__ __align__(8) uint64_t bar_grp[2][2];
   __shared__ __align__(8) uint64_t bar_fold[2];             // ... and has been folded away
   __shared__ uint32_t tmem_slot;
   __shared__ int failed;
@@ -136,7 +172,8 @@ pair_umma_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_const
       mbar_init(&bar_empty[s], 1);
     }
     for (int r = 0; r < 2; ++r) {
-      mbar_init(&bar_grp[r], 1);
+      mbar_init(&bar_grp[0][r], 1);
+      mbar_init(&bar_grp[1][r], 1);
       mbar_init(&bar_fold[r], kPairFolders);
     }
     failed = 0;
@@ -156,7 +193,7 @@ pair_umma_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_const
         const PairTile t = pair_tile(p, w);
         for (int kb = 0; kb < t.KB && !*vfailed; ++kb, ++it) {
           const int s = it % kPairStages;
-          if (it >= kPairStages && !mbar_wait(&bar_empty[s], (uint32_t)((it / kPairStages - 1) & 1))) {
+          if (it >= kPairStages && !mbar_wait_watch(&bar_empty[s], (uint32_t)((it / kPairStages - 1) & 1), vfailed)) {
             *vfailed = 1;
             break;
           }
@@ -194,18 +231,18 @@ pair_umma_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_const
       // M / N values (only the latter layout uses it), SBO = next group of 8 rows
       constexpr uint32_t a_step = A_MN ? 2048u : 32u, b_step = B_MN ? 2048u : 32u;
       constexpr uint32_t a_lbo = A_MN ? 8192u : 16u, b_lbo = B_MN ? 8192u : 16u;
-      int it = 0, gg = 0;  // K slices and accumulator groups so far, over all items
-      for (int w = blockIdx.x; w < n_items && !*vfailed; w += gridDim.x) {
+      int it = 0, gg = 0, item = 0;  // K slices, accumulator groups and items so far
+      for (int w = blockIdx.x; w < n_items && !*vfailed; w += gridDim.x, ++item) {
         const PairTile t = pair_tile(p, w);
         for (int kb = 0; kb < t.KB && !*vfailed; ++kb, ++it) {
           const int s = it % kPairStages;
           const bool group_start = kb % kPairGroup == 0;
           // this accumulator was last used two groups ago: it must have been folded away
-          if (group_start && gg >= 2 && !mbar_wait(&bar_fold[gg & 1], (uint32_t)(((gg - 2) >> 1) & 1))) {
+          if (group_start && gg >= 2 && !mbar_wait_watch(&bar_fold[gg & 1], (uint32_t)(((gg - 2) >> 1) & 1), vfailed)) {
             *vfailed = 1;
             break;
           }
-          if (!mbar_wait(&bar_full[s], (uint32_t)((it / kPairStages) & 1))) {
+          if (!mbar_wait_watch(&bar_full[s], (uint32_t)((it / kPairStages) & 1), vfailed)) {
             *vfailed = 1;
             break;
           }
@@ -224,111 +261,107 @@ pair_umma_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_const
           }
           mma_commit(&bar_empty[s]);
           if (kb % kPairGroup == kPairGroup - 1 || kb == t.KB - 1) {
-            mma_commit(&bar_grp[gg & 1]);
+            mma_commit(&bar_grp[item & 1][gg & 1]);
             ++gg;
           }
         }
       }
     }
   } else {
-    // ---- fold finished groups into the running sum, then the epilogue -------------------------
-    const int quarter = warp & 3;  // tensor-memory lanes 32*quarter..
+    // ---- fold finished groups into the set's running sum, then the epilogue --------------------
+    const int set = (warp - 2) >> 2;  // which of the two sets; tiles alternate between them
+    const int quarter = warp & 3;     // tensor-memory lanes 32*quarter..
     const uint32_t lane_base = (uint32_t)(32 * quarter) << 16;
-    const uint32_t run = tmem_d + lane_base + kPairRun;
-    const bool vec = (p.N % 4) == 0;
+    const uint32_t run = tmem_d + lane_base + kPairRun + 128u * (uint32_t)set;
+    const uint32_t box = tiles + (uint32_t)kPairStages * kPairStageBytes + (uint32_t)(warp - 2) * kPairBoxBytes;
+    uint8_t *box_ptr = smem_dyn + (box - smem_u32(smem_dyn));
     bool ok = true;
-    int gg = 0;
-    for (int w = blockIdx.x; w < n_items; w += gridDim.x) {
+    int gg = 0, item = 0;
+    int seen[2] = {0, 0};  // phases this set has consumed on its two barriers
+    for (int w = blockIdx.x; w < n_items; w += gridDim.x, ++item) {
       const PairTile t = pair_tile(p, w);
       const int NG = (t.KB + kPairGroup - 1) / kPairGroup;
+      if ((item & 1) != set) {  // the other set's tile
+        gg += NG;
+        continue;
+      }
       const int m = t.m0 + 32 * quarter + lane;
       const bool row_ok = m < p.M;
-      float *out = row_ok ? ext.out_row(t.z, m) : nullptr;
       typename Ext::Row rs;
-      if (row_ok) ext.row_begin(rs, t.z, m, t.n0);
+      if (row_ok) {
+        ext.row_begin(rs, t.z, m, t.n0);
+        ext.prefetch(rs, t.z, m, t.n0);
+      }
       for (int g = 0; g < NG && ok; ++g, ++gg) {
-        if (!mbar_wait(&bar_grp[gg & 1], (uint32_t)((gg >> 1) & 1))) {
+        bool got = mbar_wait_watch(&bar_grp[set][gg & 1], (uint32_t)(seen[gg & 1] & 1), vfailed);
+        ++seen[gg & 1];
+        got = __all_sync(0xffffffffu, got);
+        if (!got) {
           ok = false;
           break;
         }
         tc_fence_after_sync();
         const uint32_t acc = tmem_d + lane_base + ((gg & 1) ? kPairAcc1 : 0u);
-        if (g + 1 < NG) {
-          // 32 columns at a time: both loads in flight, one wait; the stores drain behind
-          for (int c = 0; c < kPairTile; c += 32) {
-            float pv[32], rv[32];
-            tmem_ld32_nowait(acc + c, pv);
-            if (g > 0) tmem_ld32_nowait(run + c, rv);
-            tmem_ld_wait();
-            if (g > 0) {
+        // 32 columns at a time: both loads in flight, one wait; the stores drain behind
+        for (int c = 0; c < kPairTile; c += 32) {
+          float pv[32], rv[32];
+          tmem_ld32_nowait(acc + c, pv);
+          if (g > 0) tmem_ld32_nowait(run + c, rv);
+          tmem_ld_wait();
+          if (g > 0) {
 #pragma unroll
-              for (int i = 0; i < 32; ++i) pv[i] = rv[i] + pv[i];
-            }
-            tmem_st32_nowait(run + c, pv);
+            for (int i = 0; i < 32; ++i) pv[i] = rv[i] + pv[i];
           }
-          tmem_st_wait();
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&bar_fold[gg & 1]);
-        } else {
-          // the last group is added on its way out: running sum + accumulator -> epilogue
-          ok = __all_sync(0xffffffffu, ok) && !*vfailed;
-          for (int c0 = 0; c0 < kPairTile; c0 += 32) {
-            float pv[32], rv[32];
-            tmem_ld32_nowait(acc + c0, pv);
-            if (g > 0) tmem_ld32_nowait(run + c0, rv);
-            tmem_ld_wait();
-            if (g > 0) {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) pv[i] = rv[i] + pv[i];
-            }
-#pragma unroll
-            for (int cc = 0; cc < 2; ++cc) {
-              const int n = t.n0 + c0 + 16 * cc;
-              if (row_ok && n < p.N) {
-                float v[16];
-#pragma unroll
-                for (int i = 0; i < 16; ++i) v[i] = pv[16 * cc + i];
-                ext.finish(rs, t.z, m, n, v);
-                if (!ok) {
-#pragma unroll
-                  for (int i = 0; i < 16; ++i) v[i] = NAN;
-                }
-                float *dst = out + n;
-                if (vec && n + 16 <= p.N) {
-#pragma unroll
-                  for (int i = 0; i < 16; i += 4)
-                    *reinterpret_cast<float4 *>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-                } else {
-#pragma unroll
-                  for (int i = 0; i < 16; ++i)
-                    if (n + i < p.N) dst[i] = v[i];
-                }
-              }
-            }
-          }
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&bar_fold[gg & 1]);
+          tmem_st32_nowait(run + c, pv);
         }
+        tmem_st_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar_fold[gg & 1]);
       }
       ok = __all_sync(0xffffffffu, ok) && !*vfailed;
       if (!ok) *vfailed = 1;
-      if (t.KB == 0 || !ok) {
-        // nothing was accumulated (an empty reduction), or a wait ran out: zeros / NaN
-        for (int n = t.n0; n < t.n0 + kPairTile && n < p.N; n += 16) {
-          if (!row_ok) break;
-          float v[16];
+      // epilogue from the running sum: 32 columns -> policy -> swizzled 32 x 32 box -> TMA store
+      for (int c0 = 0; c0 < kPairTile && t.n0 + c0 < p.N; c0 += 32) {
+        float pv[32];
+        if (ok && t.KB > 0) {
+          tmem_ld32_nowait(run + c0, pv);
+          tmem_ld_wait();
+        } else {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) v[i] = 0.f;
-          if (ok) ext.finish(rs, t.z, m, n, v);
-#pragma unroll
-          for (int i = 0; i < 16; ++i)
-            if (n + i < p.N) out[n + i] = ok ? v[i] : NAN;
+          for (int i = 0; i < 32; ++i) pv[i] = 0.f;
         }
+        const int n = t.n0 + c0;
+        float v0[16], v1[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v0[i] = pv[i], v1[i] = pv[16 + i];
+        if (row_ok) {
+          ext.finish(rs, t.z, m, n, v0, 0);
+          if (n + 16 < p.N) ext.finish(rs, t.z, m, n + 16, v1, 1);
+          if (c0 + 32 < kPairTile && n + 32 < p.N) ext.prefetch(rs, t.z, m, n + 32);
+        }
+        if (!ok) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v0[i] = v1[i] = NAN;
+        }
+        // the store of the previous box must have read the staging buffer
+        if (lane == 0) tma_store_wait_read();
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          *reinterpret_cast<float4 *>(box_ptr + sw128_offset(lane, j)) =
+              make_float4(v0[4 * j], v0[4 * j + 1], v0[4 * j + 2], v0[4 * j + 3]);
+          *reinterpret_cast<float4 *>(box_ptr + sw128_offset(lane, 4 + j)) =
+              make_float4(v1[4 * j], v1[4 * j + 1], v1[4 * j + 2], v1[4 * j + 3]);
+        }
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) tma_store_3d(&map_out, box, n, t.m0 + 32 * quarter, t.z);
       }
       if (row_ok) ext.row_end(rs, t.z, m, t.n0);
+      tc_fence_before_sync();
     }
+    if (lane == 0) tma_store_wait_read();
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -362,16 +395,39 @@ inline int make_pair_map(CUtensorMap *map, const void *base, int rows, int cols,
                   : make_map_f16(map, base, rows, cols, pitch, kPairBK, kPairTile);
 }
 
+// map of the float32 output [nz][M][N] (row pitch N floats): boxes of 32 x 32, stored from
+// a 128-byte-swizzled staging buffer
+inline int make_out_map(CUtensorMap *map, const float *base, int nz, int M, int N) {
+  auto enc = tensor_map_encoder();
+  FRNNT_REQUIRE(enc != nullptr, FRNNT_ECUDA, "cuTensorMapEncodeTiled is not available");
+  FRNNT_REQUIRE((uintptr_t)base % 16 == 0 && N % 4 == 0, FRNNT_EUNSUPPORTED,
+                "the output needs a 16-byte aligned base and a row length that is a multiple of 4 floats");
+  cuuint64_t dims[3] = {(cuuint64_t)N, (cuuint64_t)M, (cuuint64_t)(nz > 0 ? nz : 1)};
+  cuuint64_t strides[2] = {(cuuint64_t)N * 4, (cuuint64_t)N * 4 * (cuuint64_t)M};
+  cuuint32_t box[3] = {32, 32, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(base), dims, strides, box,
+                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  FRNNT_REQUIRE(r == CUDA_SUCCESS, FRNNT_ECUDA, "cuTensorMapEncodeTiled (output) failed with %d", (int)r);
+  return FRNNT_OK;
+}
+
+// out = [shape.nz][shape.M][shape.N] floats
 template <bool A_MN, bool B_MN, class Ext>
 int launch_pair_umma(const CUtensorMap &mah, const CUtensorMap &mal, const CUtensorMap &mbh,
-                     const CUtensorMap &mbl, const LinShape &shape, const Ext &ext, cudaStream_t st) {
+                     const CUtensorMap &mbl, float *out, const LinShape &shape, const Ext &ext,
+                     cudaStream_t st) {
+  CUtensorMap mo;
+  int rc = make_out_map(&mo, out, shape.nz, shape.M, shape.N);
+  if (rc != FRNNT_OK) return rc;
   auto kern = pair_umma_kernel<A_MN, B_MN, Ext>;
   FRNNT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPairSmemBytes));
   int ctas = 0;
-  const int rc = lin_grid((long long)shape.tiles_m * shape.tiles_n * shape.nz, &ctas);
+  rc = lin_grid((long long)shape.tiles_m * shape.tiles_n * shape.nz, &ctas);
   if (rc != FRNNT_OK) return rc;
   if (ctas == 0) return FRNNT_OK;
-  FRNNT_KERNEL(kern<<<ctas, kPairThreads, kPairSmemBytes, st>>>(mah, mal, mbh, mbl, shape, ext));
+  FRNNT_KERNEL(kern<<<ctas, kPairThreads, kPairSmemBytes, st>>>(mah, mal, mbh, mbl, mo, shape, ext));
   FRNNT_CUDA(cudaGetLastError());
   return FRNNT_OK;
 }

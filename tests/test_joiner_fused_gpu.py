@@ -60,6 +60,11 @@ CASES = [
     (1, 40, 9, 3, 72, 1032),       # more than eight column tiles, D not a multiple of the K slice
     (2, 21, 14, 9, 8, 12),         # the narrowest activations, more rows per frame than registers hold
     (2, 150, 20, 2, 40, 4),        # the smallest vocabulary
+    # several tiles per persistent CTA (the two fold sets take turns), with one, three and
+    # five K slices per tile (odd group counts walk through both accumulators)
+    (16, 500, 50, 5, 64, 200),
+    (12, 400, 40, 5, 192, 264),
+    (10, 300, 30, 5, 320, 136),
 ]
 
 
