@@ -430,7 +430,7 @@ def stage_table(fr, wl, dev, flush, hbm_gbs):
                   _lib.ptr(sym), _lib.ptr(bnd), _lib.ptr(pj_saved), _lib.ptr(pj_bs), _lib.ptr(enc_g),
                   _lib.ptr(dec_g), _lib.ptr(w_g), _lib.ptr(b_g), B, T, R, S, C, D, 0, 0, sp)
 
-    Cp = (C + 7) // 8 * 8
+    Cp = (C + 63) // 64 * 64
     half = lambda *shape: torch.empty(*shape, dtype=torch.float16, device=dev)  # noqa: E731
     pscr = torch.empty(lib.frnnt_pairs_scratch_floats(), device=dev)
     inv = torch.empty(4, device=dev)

@@ -76,7 +76,9 @@ struct PjlLayout {
 static PjlLayout pjl_layout(int B, int T, int R, int S1, int C, int D) {
   PjlLayout L;
   const size_t M = (size_t)B * T * R;
-  const size_t Cp = (size_t)(C + 7) / 8 * 8;
+  // row pitch of the planes whose rows have C entries: whole 128-byte lines, so that the
+  // 128-byte row segments TMA fetches never straddle one more 32-byte sector
+  const size_t Cp = (size_t)(C + 63) / 64 * 64;
   L.M = M;
   L.Cp = Cp;
   L.tiles_n = (C + kPairTile - 1) / kPairTile;
