@@ -46,6 +46,12 @@ C5_GLOBAL_LOSS = None
 # the roofline lines name, workload c3, from the ncu captures summarised under profiles/
 # (one small capture per kernel; the file names the command).  None: not captured.
 NCU_TRAFFIC_C3 = {
+    # profiles/kernels_c3_half_batch_ncu_full.txt: captured at half batch, doubled (every kernel
+    # streams its operands once, so its traffic grows with the number of rows)
+    "pair_linear_fwd": 2 * 277.0e6, "pair_linear_grad_input": 2 * 461.8e6,
+    "pair_linear_grad_weight": 2 * 331.5e6,
+    "mi_forward": 2 * 8.3e6, "mi_backward": 2 * 5.9e6, "mi_forward_pruned": 2 * 8.3e6,
+    "mi_backward_pruned": 2 * 5.9e6,
 }
 
 
