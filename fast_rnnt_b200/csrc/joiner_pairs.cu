@@ -206,6 +206,9 @@ pruned_tanh_pairs_kernel(const float *__restrict__ enc, const float *__restrict_
 // ---- epilogues of the three products ----------------------------------------------------------
 // logits = acc * (1/scales) + bias, and per row and tile (max, sum exp(logit - max))
 struct PjlFwdExt {
+  static constexpr bool kBatched = false, kCustomStore = false;
+  template <class R> __device__ void store_box(R &, int, int, int, int, float (&)[16], float (&)[16], const uint8_t *) const {}
+  __device__ void tile_begin(int, int, uint8_t *, int) const {}
   const float *bias;
   float2 *stats;
   const float *scales;
@@ -243,6 +246,9 @@ struct PjlFwdExt {
 
 // gz = acc * (1/scales) * (1 - act^2): the gradient with respect to enc + dec
 struct PjlGradInExt {
+  static constexpr bool kBatched = false, kCustomStore = false;
+  template <class R> __device__ void store_box(R &, int, int, int, int, float (&)[16], float (&)[16], const uint8_t *) const {}
+  __device__ void tile_begin(int, int, uint8_t *, int) const {}
   const __half *act_hi, *act_lo;
   const float *scales;
   int N;  // = D
@@ -288,6 +294,9 @@ struct PjlGradInExt {
 
 // W_grad partial sums: acc * (1/scales)
 struct PjlGradWExt {
+  static constexpr bool kBatched = false, kCustomStore = false;
+  template <class R> __device__ void store_box(R &, int, int, int, int, float (&)[16], float (&)[16], const uint8_t *) const {}
+  __device__ void tile_begin(int, int, uint8_t *, int) const {}
   const float *scales;
   struct Row {
     float sc;
@@ -488,6 +497,9 @@ lsm_backward_pairs_kernel(const float *__restrict__ logits, const int64_t *__res
 // ---- plain products on planes (the engine without the joiner around it) -------------------------
 // D = acc * inv_scale_a * inv_scale_b (+ bias[n])
 struct PlainPairExt {
+  static constexpr bool kBatched = false, kCustomStore = false;
+  template <class R> __device__ void store_box(R &, int, int, int, int, float (&)[16], float (&)[16], const uint8_t *) const {}
+  __device__ void tile_begin(int, int, uint8_t *, int) const {}
   const float *bias, *inv_a, *inv_b;
   int N;
   struct Row {

@@ -23,6 +23,7 @@
 #include <string.h>
 
 #include "common.cuh"
+#include "simple_pairs.cuh"
 
 namespace frnnt {
 
@@ -632,6 +633,15 @@ static bool use_tensor_cores(const void *lm, const void *am, int S1, int T, int 
   return norm_umma_supported(lm, am, S1, T, C);
 }
 
+// the fp16-pair engine (FRNNT_CONTRACTION=tf32 keeps the 3xTF32 kernels, =simt the FMA pipe)
+template <typename real>
+static bool use_pairs(const void *lm, const void *am, int S1, int T, int C, int rnnt_type) {
+  if (sizeof(real) != 4) return false;
+  const char *mode = getenv("FRNNT_CONTRACTION");
+  if (mode != nullptr && (strcmp(mode, "simt") == 0 || strcmp(mode, "tf32") == 0)) return false;
+  return simple_pairs_supported(lm, am, S1, T, C, rnnt_type);
+}
+
 static int simple_check(int dtype, int B, int S, int T, int C, int blank, int rnnt_type) {
   FRNNT_REQUIRE(check_dtype(dtype), FRNNT_EINVAL, "dtype must be FRNNT_F32 or FRNNT_F64");
   FRNNT_REQUIRE(B >= 0 && S >= 0 && T >= 0 && C >= 1, FRNNT_EINVAL,
@@ -680,8 +690,17 @@ static int simple_forward_impl(const void *lm_, const void *am_, const int64_t *
   real *loguni = (real *)(svb + sv.loguni), *partial = (real *)(scb + sc.partial);
   const long long lm_rows = (long long)B * S1, am_rows = (long long)B * T;
 
-  FRNNT_KERNEL(row_stats_kernel<real><<<warps_grid(lm_rows), 256, 0, st>>>(lm, lmmax, lmsum, lm_rows, C));
-  {
+  const bool pairs = use_pairs<real>(lm, am, S1, T, C, rnnt_type);
+  void *pairs_saved = svb + sv.total;
+  if (pairs) {
+    int rc0 = launch_simple_forward_pairs((const float *)lm, (const float *)am, symbols, boundary, blank,
+                                          rnnt_type, cfg.smoothed, cfg.am_only_off, (float)cfg.both,
+                                          (float)cfg.ls, (float)cfg.as, (float *)px, (float *)py, (float *)norm,
+                                          (float *)lmmax, (float *)lmsum, (float *)ammax, (const float *)amonly,
+                                          (const float *)loguni, pairs_saved, B, S, T, C, 0, st);
+    if (rc0 != FRNNT_OK) return rc0;
+  } else {
+    FRNNT_KERNEL(row_stats_kernel<real><<<warps_grid(lm_rows), 256, 0, st>>>(lm, lmmax, lmsum, lm_rows, C));
     constexpr int VW = 16 / sizeof(real);
     const int vec_ok = C % VW == 0 && (uintptr_t)am % 16 == 0;
     FRNNT_KERNEL(row_max_kernel<real><<<warps_grid(am_rows), 256, 0, st>>>(am, ammax, am_rows, C, vec_ok));
@@ -696,6 +715,12 @@ static int simple_forward_impl(const void *lm_, const void *am_, const int64_t *
     FRNNT_CUDA(cudaGetLastError());
   }
   int rc;
+  if (pairs)
+    return launch_simple_forward_pairs((const float *)lm, (const float *)am, symbols, boundary, blank,
+                                       rnnt_type, cfg.smoothed, cfg.am_only_off, (float)cfg.both,
+                                       (float)cfg.ls, (float)cfg.as, (float *)px, (float *)py, (float *)norm,
+                                       (float *)lmmax, (float *)lmsum, (float *)ammax, (const float *)amonly,
+                                       (const float *)loguni, pairs_saved, B, S, T, C, 1, st);
   if (use_tensor_cores<real>(lm, am, S1, T, C)) {
     rc = launch_norm_umma((const float *)lm, (const float *)am, (const float *)lmmax,
                           (const float *)ammax, (float *)norm, B, S1, T, C, st);
@@ -771,7 +796,14 @@ static int simple_backward_impl(const void *lm_, const void *am_, const int64_t 
   }
 
   int rc;
-  if (use_tensor_cores<real>(lm, am, S1, T, C)) {
+  if (use_pairs<real>(lm, am, S1, T, C, rnnt_type) && T > 0) {
+    rc = launch_simple_grads_pairs((const float *)rw, (const float *)lmsum, (const float *)ammax,
+                                   (const float *)amonly, (const float *)uni, (const float *)gl_p,
+                                   (const float *)h_p, (const float *)dp_p, (const float *)rowdot_p,
+                                   (float *)lm_grad, (float *)am_grad, svb + sv.total, scb + sc.total, B, S, T,
+                                   C, Tp, st);
+    if (rc != FRNNT_OK) return rc;
+  } else if (use_tensor_cores<real>(lm, am, S1, T, C)) {
     rc = launch_simple_grads_umma((const float *)lm, (const float *)am, (const float *)lmmax,
                                   (const float *)lmsum, (const float *)ammax, (const float *)amonly,
                                   (const float *)uni, (const float *)rw, (const float *)gl_p,
@@ -801,14 +833,17 @@ static int simple_backward_impl(const void *lm_, const void *am_, const int64_t 
 
 using namespace frnnt;
 
+// float32 calls may take the tensor-core path, whose planes and tables follow the regular areas
 extern "C" size_t frnnt_simple_saved_bytes(int dtype, int B, int S, int T, int C) {
   if (!check_dtype(dtype) || B < 0 || S < 0 || T < 0 || C < 0) return 0;
-  return SavedLayout(dtype_size(dtype), B, S, T, C).total;
+  return SavedLayout(dtype_size(dtype), B, S, T, C).total +
+         (dtype == FRNNT_F32 ? SimplePairsLayout(B, S, T, C).saved_bytes : 0);
 }
 
 extern "C" size_t frnnt_simple_scratch_bytes(int dtype, int B, int S, int T, int C) {
   if (!check_dtype(dtype) || B < 0 || S < 0 || T < 0 || C < 0) return 0;
-  return ScratchLayout(dtype_size(dtype), B, S, T, C).total;
+  return ScratchLayout(dtype_size(dtype), B, S, T, C).total +
+         (dtype == FRNNT_F32 ? SimplePairsLayout(B, S, T, C).scratch_bytes : 0);
 }
 
 extern "C" int frnnt_simple_logprobs_forward(int dtype, const void *lm, const void *am,

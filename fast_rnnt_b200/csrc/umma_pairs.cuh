@@ -34,6 +34,13 @@
 // No multicast, no clusters.  Every wait is bounded; a timeout poisons the tile with NaN.
 //
 // Policy ("Ext") interface, all __device__:
+//   static constexpr bool kBatched;                the work-item index z is a batch index (the
+//                                                  outer coordinate of every tensor map) instead
+//                                                  of a split of the reduction
+//   static constexpr bool kCustomStore;            the policy writes the result itself:
+//                                                  store_box() is called instead of finish(),
+//                                                  staging and the TMA store, for the 32-column
+//                                                  boxes of a tile from the last to the first
 //   struct Row;                                    per-row state across one tile's columns
 //   void row_begin(Row &, int z, int m, int n0) const;
 //   void prefetch(Row &, int z, int m, int n) const;      columns n..n+31 come next: loads
@@ -43,6 +50,12 @@
 //                                                  prefetched 32), in place; only columns
 //                                                  below N count
 //   void row_end(Row &, int z, int m, int n0) const;
+//   void tile_begin(int z, int n0, uint8_t *box, int lane) const;   (kCustomStore) called by
+//                                                  all lanes of a fold warp when it takes a
+//                                                  tile: 4 KB of shared memory per warp for
+//                                                  per-column data
+//   void store_box(Row &, int z, int m, int n0, int c0, float (&v0)[16], float (&v1)[16],
+//                  const uint8_t *box) const;      (kCustomStore) columns n0+c0..n0+c0+31 of row m < M
 // The result goes out through a tensor map of the output (rows beyond M and columns
 // beyond N are clipped by the TMA store).
 #pragma once
@@ -133,6 +146,7 @@ struct PairTile {
 };
 // work item w -> (z, m tile, n tile); the n tiles of one m tile are neighbours, so the
 // CTAs that run at the same time share their A rows in L2
+template <bool BATCHED>
 __device__ __forceinline__ PairTile pair_tile(const LinShape &p, int w) {
   PairTile t;
   const int per_z = p.tiles_m * p.tiles_n;
@@ -140,8 +154,8 @@ __device__ __forceinline__ PairTile pair_tile(const LinShape &p, int w) {
   const int r = w - t.z * per_z;
   t.m0 = (r / p.tiles_n) * kPairTile;
   t.n0 = (r % p.tiles_n) * kPairTile;
-  t.k_begin = t.z * p.k_per_split;
-  const int k_end = min(p.K, t.k_begin + p.k_per_split);
+  t.k_begin = BATCHED ? 0 : t.z * p.k_per_split;
+  const int k_end = BATCHED ? p.K : min(p.K, t.k_begin + p.k_per_split);
   t.KB = k_end > t.k_begin ? (k_end - t.k_begin + kPairBK - 1) / kPairBK : 0;
   return t;
 }
@@ -190,7 +204,7 @@ pair_umma_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_const
     if (lane == 0) {
       int it = 0;  // K slices issued so far, over all items
       for (int w = blockIdx.x; w < n_items && !*vfailed; w += gridDim.x) {
-        const PairTile t = pair_tile(p, w);
+        const PairTile t = pair_tile<Ext::kBatched>(p, w);
         for (int kb = 0; kb < t.KB && !*vfailed; ++kb, ++it) {
           const int s = it % kPairStages;
           if (it >= kPairStages && !mbar_wait_watch(&bar_empty[s], (uint32_t)((it / kPairStages - 1) & 1), vfailed)) {
@@ -200,25 +214,26 @@ pair_umma_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_const
           const int k0 = t.k_begin + kb * kPairBK;
           const uint32_t st = tiles + (uint32_t)s * kPairStageBytes;
           mbar_expect_tx(&bar_full[s], kPairStageBytes);
+          const int zc = Ext::kBatched ? t.z : 0;  // outer coordinate of the operand maps
           if (A_MN) {
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
-              tma_load_2d(st + j * 8192, &map_ahi, t.m0 + 64 * j, k0, &bar_full[s]);
-              tma_load_2d(st + kPairOpBytes + j * 8192, &map_alo, t.m0 + 64 * j, k0, &bar_full[s]);
+              tma_load_3d(st + j * 8192, &map_ahi, t.m0 + 64 * j, k0, zc, &bar_full[s]);
+              tma_load_3d(st + kPairOpBytes + j * 8192, &map_alo, t.m0 + 64 * j, k0, zc, &bar_full[s]);
             }
           } else {
-            tma_load_2d(st, &map_ahi, k0, t.m0, &bar_full[s]);
-            tma_load_2d(st + kPairOpBytes, &map_alo, k0, t.m0, &bar_full[s]);
+            tma_load_3d(st, &map_ahi, k0, t.m0, zc, &bar_full[s]);
+            tma_load_3d(st + kPairOpBytes, &map_alo, k0, t.m0, zc, &bar_full[s]);
           }
           if (B_MN) {
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
-              tma_load_2d(st + 2 * kPairOpBytes + j * 8192, &map_bhi, t.n0 + 64 * j, k0, &bar_full[s]);
-              tma_load_2d(st + 3 * kPairOpBytes + j * 8192, &map_blo, t.n0 + 64 * j, k0, &bar_full[s]);
+              tma_load_3d(st + 2 * kPairOpBytes + j * 8192, &map_bhi, t.n0 + 64 * j, k0, zc, &bar_full[s]);
+              tma_load_3d(st + 3 * kPairOpBytes + j * 8192, &map_blo, t.n0 + 64 * j, k0, zc, &bar_full[s]);
             }
           } else {
-            tma_load_2d(st + 2 * kPairOpBytes, &map_bhi, k0, t.n0, &bar_full[s]);
-            tma_load_2d(st + 3 * kPairOpBytes, &map_blo, k0, t.n0, &bar_full[s]);
+            tma_load_3d(st + 2 * kPairOpBytes, &map_bhi, k0, t.n0, zc, &bar_full[s]);
+            tma_load_3d(st + 3 * kPairOpBytes, &map_blo, k0, t.n0, zc, &bar_full[s]);
           }
         }
       }
@@ -233,7 +248,7 @@ pair_umma_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_const
       constexpr uint32_t a_lbo = A_MN ? 8192u : 16u, b_lbo = B_MN ? 8192u : 16u;
       int it = 0, gg = 0, item = 0;  // K slices, accumulator groups and items so far
       for (int w = blockIdx.x; w < n_items && !*vfailed; w += gridDim.x, ++item) {
-        const PairTile t = pair_tile(p, w);
+        const PairTile t = pair_tile<Ext::kBatched>(p, w);
         for (int kb = 0; kb < t.KB && !*vfailed; ++kb, ++it) {
           const int s = it % kPairStages;
           const bool group_start = kb % kPairGroup == 0;
@@ -279,7 +294,7 @@ pair_umma_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_const
     int gg = 0, item = 0;
     int seen[2] = {0, 0};  // phases this set has consumed on its two barriers
     for (int w = blockIdx.x; w < n_items; w += gridDim.x, ++item) {
-      const PairTile t = pair_tile(p, w);
+      const PairTile t = pair_tile<Ext::kBatched>(p, w);
       const int NG = (t.KB + kPairGroup - 1) / kPairGroup;
       if ((item & 1) != set) {  // the other set's tile
         gg += NG;
@@ -288,6 +303,11 @@ pair_umma_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_const
       const int m = t.m0 + 32 * quarter + lane;
       const bool row_ok = m < p.M;
       typename Ext::Row rs;
+      if (Ext::kCustomStore) {
+        // whole warp: per-column data of the tile into the warp's (otherwise unused) box
+        ext.tile_begin(t.z, t.n0, box_ptr, lane);
+        __syncwarp();
+      }
       if (row_ok) {
         ext.row_begin(rs, t.z, m, t.n0);
         ext.prefetch(rs, t.z, m, t.n0);
@@ -321,6 +341,24 @@ pair_umma_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_const
       }
       ok = __all_sync(0xffffffffu, ok) && !*vfailed;
       if (!ok) *vfailed = 1;
+      if (Ext::kCustomStore) {
+        // the policy stores the tile itself, boxes from the last to the first
+        for (int c0 = kPairTile - 32; c0 >= 0; c0 -= 32) {
+          if (t.n0 + c0 >= p.N) continue;
+          float pv[32];
+          if (ok && t.KB > 0) {
+            tmem_ld32_nowait(run + c0, pv);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) pv[i] = ok ? 0.f : NAN;
+          }
+          float v0[16], v1[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v0[i] = pv[i], v1[i] = pv[16 + i];
+          if (row_ok) ext.store_box(rs, t.z, m, t.n0, c0, v0, v1, box_ptr);
+        }
+      } else {
       // epilogue from the running sum: 32 columns -> policy -> swizzled 32 x 32 box -> TMA store
       for (int c0 = 0; c0 < kPairTile && t.n0 + c0 < p.N; c0 += 32) {
         float pv[32];
@@ -358,6 +396,7 @@ pair_umma_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_const
         __syncwarp();
         if (lane == 0) tma_store_3d(&map_out, box, n, t.m0 + 32 * quarter, t.z);
       }
+      }
       if (row_ok) ext.row_end(rs, t.z, m, t.n0);
       tc_fence_before_sync();
     }
@@ -369,19 +408,24 @@ pair_umma_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_const
 }
 
 // ---- host -----------------------------------------------------------------------------------
-// map of a row-major fp16 matrix [rows][cols] whose rows are `pitch` halves apart; box =
-// box_cols x box_rows, 128-byte swizzle.  Elements outside [rows][cols] read as zeros.
-inline int make_map_f16(CUtensorMap *map, const void *base, int rows, int cols, long long pitch,
-                        int box_cols, int box_rows) {
+// map of `batch` row-major fp16 matrices [rows][cols] whose rows are `pitch` halves apart and
+// which follow each other every `batch_stride` halves (batch <= 1: one matrix); box =
+// box_cols x box_rows x 1, 128-byte swizzle.  Elements outside [rows][cols] read as zeros.
+inline int make_map_f16(CUtensorMap *map, const void *base, int rows, int cols, long long pitch, int batch,
+                        long long batch_stride, int box_cols, int box_rows) {
   auto enc = tensor_map_encoder();
   FRNNT_REQUIRE(enc != nullptr, FRNNT_ECUDA, "cuTensorMapEncodeTiled is not available");
-  FRNNT_REQUIRE((uintptr_t)base % 16 == 0 && pitch % 8 == 0, FRNNT_EUNSUPPORTED,
-                "TMA needs a 16-byte aligned base and a row pitch that is a multiple of 8 halves");
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)pitch * 2};
-  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(base), dims, strides, box,
+  if (batch <= 1) {
+    batch = 1;
+    batch_stride = (long long)rows * pitch;
+  }
+  FRNNT_REQUIRE((uintptr_t)base % 16 == 0 && pitch % 8 == 0 && batch_stride % 8 == 0, FRNNT_EUNSUPPORTED,
+                "TMA needs a 16-byte aligned base and row / matrix strides that are multiples of 8 halves");
+  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batch};
+  cuuint64_t strides[2] = {(cuuint64_t)pitch * 2, (cuuint64_t)batch_stride * 2};
+  cuuint32_t box[3] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(base), dims, strides, box,
                    estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   FRNNT_REQUIRE(r == CUDA_SUCCESS, FRNNT_ECUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
@@ -390,9 +434,9 @@ inline int make_map_f16(CUtensorMap *map, const void *base, int rows, int cols, 
 // operand plane for the engine: K-major ([M or N rows][K cols], box 64 k x 128 rows) or
 // contiguous along M / N ([K rows][M or N cols], boxes of 64 values x 64 k rows)
 inline int make_pair_map(CUtensorMap *map, const void *base, int rows, int cols, long long pitch,
-                         bool mn_major) {
-  return mn_major ? make_map_f16(map, base, rows, cols, pitch, 64, kPairBK)
-                  : make_map_f16(map, base, rows, cols, pitch, kPairBK, kPairTile);
+                         bool mn_major, int batch = 0, long long batch_stride = 0) {
+  return mn_major ? make_map_f16(map, base, rows, cols, pitch, batch, batch_stride, 64, kPairBK)
+                  : make_map_f16(map, base, rows, cols, pitch, batch, batch_stride, kPairBK, kPairTile);
 }
 
 // map of the float32 output [nz][M][N] (row pitch N floats): boxes of 32 x 32, stored from
@@ -419,7 +463,8 @@ int launch_pair_umma(const CUtensorMap &mah, const CUtensorMap &mal, const CUten
                      const CUtensorMap &mbl, float *out, const LinShape &shape, const Ext &ext,
                      cudaStream_t st) {
   CUtensorMap mo;
-  int rc = make_out_map(&mo, out, shape.nz, shape.M, shape.N);
+  // a policy that stores the result itself never uses the map, which still has to be valid
+  int rc = Ext::kCustomStore ? make_out_map(&mo, out, 1, 4, 4) : make_out_map(&mo, out, shape.nz, shape.M, shape.N);
   if (rc != FRNNT_OK) return rc;
   auto kern = pair_umma_kernel<A_MN, B_MN, Ext>;
   FRNNT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPairSmemBytes));
