@@ -57,10 +57,20 @@ static int pair_tn_splits(int M, int N, long long R) {
   return best;
 }
 
-static int colsum_ctas(long long rows) {
-  long long want = (rows + kRowWarps - 1) / kRowWarps;
-  const long long cap = (long long)sm_count() * 8;
-  return (int)(want < 1 ? 1 : (want < cap ? want : cap));
+// row groups of the log-softmax backward: each CTA streams a contiguous group of rows for
+// one chunk of 1024 columns; about eight CTAs per SM over all chunks
+// threads per CTA of that kernel: one per 4-column vector, whole warps, at most 256
+static int lsm_threads(int C) {
+  const int nvec = C / 4;
+  return nvec >= 256 ? 256 : ((nvec + 31) / 32) * 32;
+}
+static int colsum_groups(long long rows, int C) {
+  const int th = lsm_threads(C);
+  const long long chunks = ((long long)C / 4 + th - 1) / th;
+  long long want = ((long long)sm_count() * 8 + chunks - 1) / chunks;
+  const long long cap = (rows + 3) / 4;  // at least four rows per group
+  want = want < cap ? want : cap;
+  return (int)(want < 1 ? 1 : want);
 }
 
 // Offsets (bytes) of everything the operator keeps: `saved` lives from forward to
@@ -70,7 +80,7 @@ struct PjlLayout {
   int tiles_n, splits, cs_ctas;
   size_t act_hi, act_lo, logits, lse, wt_hi, wt_lo, scales, saved_bytes;
   size_t w_hi, w_lo, stats, pxb, pyb, amax_part, fwd_bytes;
-  size_t g_hi, g_lo, gz, gxb, gyb, gmax_part, dw_part, cs_part, jg, bwd_bytes;
+  size_t g_hi, g_lo, gz, rowinfo, gmax_part, dw_part, cs_part, jg, bwd_bytes;
 };
 
 static PjlLayout pjl_layout(int B, int T, int R, int S1, int C, int D) {
@@ -83,7 +93,7 @@ static PjlLayout pjl_layout(int B, int T, int R, int S1, int C, int D) {
   L.Cp = Cp;
   L.tiles_n = (C + kPairTile - 1) / kPairTile;
   L.splits = pair_tn_splits(C, D, (long long)M);
-  L.cs_ctas = colsum_ctas((long long)M);
+  L.cs_ctas = colsum_groups((long long)M, C);
   size_t o = 0;
   auto take = [&](size_t bytes) {
     const size_t r = o;
@@ -110,8 +120,7 @@ static PjlLayout pjl_layout(int B, int T, int R, int S1, int C, int D) {
   L.g_hi = take(M * Cp * 2);
   L.g_lo = take(M * Cp * 2);
   L.gz = take(M * D * 4);
-  L.gxb = take(M * 4);
-  L.gyb = take(M * 4);
+  L.rowinfo = take(M * 16);
   L.gmax_part = take(kMaxParts * 4);
   L.dw_part = take(L.splits > 1 ? (size_t)L.splits * C * D * 4 : 0);
   L.cs_part = take((size_t)L.cs_ctas * C * 4);
@@ -370,13 +379,16 @@ joiner_band_kernel(const float *__restrict__ logits, const float2 *__restrict__ 
   pyb[row] = x[blank] - l;
 }
 
-// per row (b, t, k): the gradients that reach its two band entries from the lattices
-// (the inverse of band_to_lattice_kernel), and the largest |gx| + |gy| of each CTA's rows
+// per row (b, t, k): what the log-softmax backward needs of it in one 16-byte entry -- the
+// gradients that reach its two band entries from the lattices (the inverse of
+// band_to_lattice_kernel), its log-sum-exp and its symbol -- and the largest |gx| + |gy|
+// of each CTA's rows
 __global__ void __launch_bounds__(256)
 band_grad_kernel(const float *__restrict__ g_px, const float *__restrict__ g_py,
-                 const int64_t *__restrict__ ranges, const int64_t *__restrict__ boundary,
-                 float *__restrict__ gxb, float *__restrict__ gyb, float *__restrict__ part,
-                 long long rows, int T, int R, int S, int rnnt_type) {
+                 const int64_t *__restrict__ symbols, const int64_t *__restrict__ ranges,
+                 const int64_t *__restrict__ boundary, const float *__restrict__ lse,
+                 float4 *__restrict__ rowinfo, float *__restrict__ part, long long rows, int T, int R,
+                 int S, int C, int blank, int rnnt_type) {
   __shared__ float sm[8];
   const int S1 = S + 1;
   const int T1 = (rnnt_type == FRNNT_REGULAR) ? T + 1 : T;
@@ -391,8 +403,8 @@ band_grad_kernel(const float *__restrict__ g_px, const float *__restrict__ g_py,
                         (long long)t == (long long)boundary[4 * b + 3];
     if (s < S && !masked) gx = g_px[((size_t)b * S + s) * T1 + t];
     if (rnnt_type == FRNNT_CONSTRAINED && s >= 1) gy += g_px[((size_t)b * S + s - 1) * T1 + t];
-    gxb[row] = gx;
-    gyb[row] = gy;
+    const int y = band_symbol(symbols, ranges, b, (size_t)row, k, S, blank, C);
+    rowinfo[row] = make_float4(gx, gy, lse[row], __int_as_float(y));
     mx = fmaxf(mx, fabsf(gx) + fabsf(gy));
   }
   mx = warp_max(mx);
@@ -405,93 +417,58 @@ band_grad_kernel(const float *__restrict__ g_px, const float *__restrict__ g_py,
 }
 
 // g[row][c] = -(gx + gy) * exp(logit - lse) + gx * [c == symbol] + gy * [c == blank], written
-// as planes (|g| <= |gx| + |gy|, whose maximum sets the scale); one warp per row.  Column
-// sums of g (the bias gradient): lane <-> fixed columns, so every warp sums its rows
-// privately -- in registers when a lane owns at most four 4-column vectors (C <= 512),
-// else in its own row of a shared array -- and the warps' sums are added in order at the
-// end -> one partial per CTA, no atomics.
-template <bool REG_SUMS>
-__global__ void __launch_bounds__(32 * kRowWarps)
-lsm_backward_pairs_kernel(const float *__restrict__ logits, const int64_t *__restrict__ symbols,
-                          const int64_t *__restrict__ ranges, const float *__restrict__ lse,
-                          const float *__restrict__ gxb, const float *__restrict__ gyb,
+// as planes (|g| <= |gx| + |gy|, whose maximum sets the scale).  Thread <-> four columns,
+// CTA <-> a contiguous group of rows x a chunk of up to 1024 columns: the loads of four rows are
+// in flight together, and the column sums of g (the bias gradient) stay in registers across
+// the whole group -> one partial per group, added in order afterwards (no atomics).
+constexpr int kLsmRowsInFlight = 4;
+__global__ void __launch_bounds__(256)
+lsm_backward_pairs_kernel(const float *__restrict__ logits, const float4 *__restrict__ rowinfo,
                           const float *__restrict__ gmax_part, int nparts, __half *__restrict__ g_hi,
                           __half *__restrict__ g_lo, float *__restrict__ cs_part,
-                          float *__restrict__ scales, long long rows, int T, int R, int S, int C,
-                          int Cp, int blank, int warps_used) {
-  extern __shared__ __align__(16) float cs[];  // [warps_used][C]   (C is a multiple of 4)
+                          float *__restrict__ scales, long long rows, int C, int Cp, int blank, int groups) {
   __shared__ float slot;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const float scale = fp16_pair_scale(block_max_of_partials(gmax_part, nparts, &slot));
-  if (blockIdx.x == 0 && threadIdx.x == 0) scales[kScaleG] = 1.f / scale;
-  if (!REG_SUMS) {
-    for (int i = threadIdx.x; i < warps_used * C; i += blockDim.x) cs[i] = 0.f;
-    __syncthreads();
-  }
-  const int nvec = C / 4;
-  float4 racc[4];
+  if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) scales[kScaleG] = 1.f / scale;
+  const int v = blockIdx.x * blockDim.x + threadIdx.x;  // this thread's 4-column vector
+  const bool col_ok = v < C / 4;
+  const long long per = (rows + groups - 1) / groups;
+  const long long r0 = (long long)blockIdx.y * per;
+  const long long r1 = r0 + per < rows ? r0 + per : rows;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  const int c0 = 4 * v;
+  for (long long row = r0; row < r1; row += kLsmRowsInFlight) {
+    float4 q[kLsmRowsInFlight], info[kLsmRowsInFlight];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) racc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-  if (warp < warps_used) {
-    float4 *mine = reinterpret_cast<float4 *>(cs + (size_t)warp * C);
-    const long long warp0 = (long long)blockIdx.x * warps_used + warp;
-    const long long nwarps = (long long)gridDim.x * warps_used;
-    for (long long row = warp0; row < rows; row += nwarps) {
-      const long long bt = row / R;
-      const int k = (int)(row % R), b = (int)(bt / T);
-      const float gx = gxb[row], gy = gyb[row];
-      const int y = band_symbol(symbols, ranges, b, (size_t)row, k, S, blank, C);
-      const float l = lse[row];
+    for (int u = 0; u < kLsmRowsInFlight; ++u) {
+      const long long r = row + u < r1 ? row + u : r1 - 1;
+      info[u] = rowinfo[r];
+      q[u] = col_ok ? reinterpret_cast<const float4 *>(logits + (size_t)r * C)[v] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (!col_ok) continue;
+#pragma unroll
+    for (int u = 0; u < kLsmRowsInFlight; ++u) {
+      if (row + u >= r1) break;
+      const float gx = info[u].x, gy = info[u].y, l = info[u].z;
+      const int y = __float_as_int(info[u].w);
       const float neg = -(gx + gy);
-      const float4 *src = reinterpret_cast<const float4 *>(logits + (size_t)row * C);
-      uint2 *dh = reinterpret_cast<uint2 *>(g_hi + (size_t)row * Cp);
-      uint2 *dl = reinterpret_cast<uint2 *>(g_lo + (size_t)row * Cp);
-      auto one = [&](int v, float4 &sum) {
-        const float4 q = src[v];
-        const float x[4] = {q.x, q.y, q.z, q.w};
-        float g[4];
-        __align__(8) __half hi[4], lo[4];
+      const float x[4] = {q[u].x, q[u].y, q[u].z, q[u].w};
+      float g[4];
+      __align__(8) __half hi[4], lo[4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int c = v * 4 + e;
-          float gg = neg * __expf(x[e] - l);
-          if (c == y) gg += gx;
-          if (c == blank) gg += gy;
-          g[e] = gg;
-          fp16_pair(gg, scale, hi[e], lo[e]);
-        }
-        dh[v] = *reinterpret_cast<const uint2 *>(hi);
-        dl[v] = *reinterpret_cast<const uint2 *>(lo);
-        sum.x += g[0], sum.y += g[1], sum.z += g[2], sum.w += g[3];
-      };
-      if (REG_SUMS) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int v = lane + 32 * j;
-          if (v < nvec) one(v, racc[j]);
-        }
-      } else {
-        for (int v = lane; v < nvec; v += 32) {
-          float4 a = mine[v];
-          one(v, a);
-          mine[v] = a;
-        }
+      for (int e = 0; e < 4; ++e) {
+        float gg = neg * __expf(x[e] - l);
+        if (c0 + e == y) gg += gx;
+        if (c0 + e == blank) gg += gy;
+        g[e] = gg;
+        fp16_pair(gg, scale, hi[e], lo[e]);
       }
-    }
-    if (REG_SUMS) {
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int v = lane + 32 * j;
-        if (v < nvec) mine[v] = racc[j];
-      }
+      reinterpret_cast<uint2 *>(g_hi + (size_t)(row + u) * Cp)[v] = *reinterpret_cast<const uint2 *>(hi);
+      reinterpret_cast<uint2 *>(g_lo + (size_t)(row + u) * Cp)[v] = *reinterpret_cast<const uint2 *>(lo);
+      acc.x += g[0], acc.y += g[1], acc.z += g[2], acc.w += g[3];
     }
   }
-  __syncthreads();
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
-    float acc = 0.f;
-    for (int w = 0; w < warps_used; ++w) acc += cs[(size_t)w * C + c];
-    cs_part[(size_t)blockIdx.x * C + c] = acc;
-  }
+  if (col_ok) reinterpret_cast<float4 *>(cs_part + (size_t)blockIdx.y * C)[v] = acc;
 }
 
 // ---- plain products on planes (the engine without the joiner around it) -------------------------
@@ -657,7 +634,8 @@ extern "C" int frnnt_pruned_joiner_logprobs_backward(const float *px_grad, const
   const float *logits = (const float *)(sv + L.logits), *lse = (const float *)(sv + L.lse);
   float *scales = (float *)(sv + L.scales);  // slot kScaleG is written here
   __half *g_hi = (__half *)(sc + L.g_hi), *g_lo = (__half *)(sc + L.g_lo);
-  float *gz = (float *)(sc + L.gz), *gxb = (float *)(sc + L.gxb), *gyb = (float *)(sc + L.gyb);
+  float *gz = (float *)(sc + L.gz);
+  float4 *rowinfo = (float4 *)(sc + L.rowinfo);
   float *gmax = (float *)(sc + L.gmax_part), *dw_part = (float *)(sc + L.dw_part);
   float *cs_part = (float *)(sc + L.cs_part);
   const long long rows = (long long)L.M;
@@ -675,19 +653,13 @@ extern "C" int frnnt_pruned_joiner_logprobs_backward(const float *px_grad, const
   if (rc != FRNNT_OK) return rc;
 
   const int gparts = parts_for(rows);
-  FRNNT_KERNEL(band_grad_kernel<<<gparts, 256, 0, st>>>(px_grad, py_grad, ranges, boundary, gxb, gyb, gmax,
-                                                       rows, T, R, S, rnnt_type));
+  FRNNT_KERNEL(band_grad_kernel<<<gparts, 256, 0, st>>>(px_grad, py_grad, symbols, ranges, boundary, lse, rowinfo,
+                                                       gmax, rows, T, R, S, C, blank, rnnt_type));
   {
-    // as many warps per CTA as have room for their column sums in shared memory
-    int warps_used = kRowWarps;
-    while (warps_used > 1 && (size_t)warps_used * C * 4 > 160 * 1024) --warps_used;
-    FRNNT_REQUIRE((size_t)warps_used * C * 4 <= 200 * 1024, FRNNT_EUNSUPPORTED, "C=%d too large", C);
-    const size_t smem = (size_t)warps_used * C * 4;
-    auto kern = C <= 512 ? lsm_backward_pairs_kernel<true> : lsm_backward_pairs_kernel<false>;
-    FRNNT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    FRNNT_KERNEL(kern<<<L.cs_ctas, 32 * kRowWarps, smem, st>>>(logits, symbols, ranges, lse, gxb, gyb, gmax, gparts,
-                                                             g_hi, g_lo, cs_part, scales, rows, T, R, S, C,
-                                                             Cp, blank, warps_used));
+    const int th = lsm_threads(C);
+    dim3 grid((unsigned)((C / 4 + th - 1) / th), (unsigned)L.cs_ctas);
+    FRNNT_KERNEL(lsm_backward_pairs_kernel<<<grid, th, 0, st>>>(logits, rowinfo, gmax, gparts, g_hi, g_lo, cs_part,
+                                                                scales, rows, C, Cp, blank, L.cs_ctas));
   }
   FRNNT_CUDA(cudaGetLastError());
   if (bias_grad != nullptr) {
