@@ -465,6 +465,47 @@ __global__ void grad_weight_kernel(EffGrads<real> eg, const real *__restrict__ n
   rw[o] = (w == 0) ? (real)0 : w * inv;
 }
 
+// The two kernels above and below in one pass, for the tensor-core path: one CTA per lattice
+// row (b, s) writes the row of Rw, the row sums of gx (all T1 columns) and gy, and the
+// row's largest |Rw| (which sets the scale of the fp16 planes Rw is split into).
+template <typename real>
+__global__ void __launch_bounds__(128)
+grad_weight_rows_kernel(EffGrads<real> eg, const real *__restrict__ norm, const real *__restrict__ lmmax,
+                        const real *__restrict__ ammax, real *__restrict__ rw, real *__restrict__ sgx,
+                        real *__restrict__ sgy, float *__restrict__ rowmax, real both, int Tp) {
+  __shared__ real red[3][4];
+  const int row = blockIdx.x, b = row / (eg.S + 1), s = row % (eg.S + 1);
+  const real lmx = lmmax[row];
+  real ax = 0, ay = 0, mx = 0;
+  const int n = max(Tp, eg.T1);
+  for (int t = threadIdx.x; t < n; t += blockDim.x) {
+    const real gx = eg.gx(b, s, t), gy = eg.gy(b, s, t);
+    ax += gx;
+    ay += gy;
+    if (t < Tp) {
+      real v = 0;
+      if (t < eg.T) {
+        const real w = both * (gx + gy);
+        const real inv = exp_r(lmx + ammax[(size_t)b * eg.T + t] - norm[(size_t)row * eg.T + t]);
+        v = (w == 0) ? (real)0 : w * inv;
+      }
+      rw[(size_t)row * Tp + t] = v;
+      mx = max(mx, v < 0 ? -v : v);
+    }
+  }
+  ax = warp_sum(ax);
+  ay = warp_sum(ay);
+  mx = warp_max(mx);
+  const int w = threadIdx.x >> 5;
+  if ((threadIdx.x & 31) == 0) red[0][w] = ax, red[1][w] = ay, red[2][w] = mx;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    sgx[row] = (red[0][0] + red[0][1]) + (red[0][2] + red[0][3]);
+    sgy[row] = (red[1][0] + red[1][1]) + (red[1][2] + red[1][3]);
+    rowmax[row] = (float)max(max(red[2][0], red[2][1]), max(red[2][2], red[2][3]));
+  }
+}
+
 // one warp per (b, s): sums over t of gx (all T1 columns) and gy
 template <typename real>
 __global__ void grad_row_sums_kernel(EffGrads<real> eg, real *__restrict__ sgx,
@@ -763,10 +804,18 @@ static int simple_backward_impl(const void *lm_, const void *am_, const int64_t 
   EffGrads<real> eg{(const real *)px_grad, (const real *)py_grad, boundary, S, T, T1, rnnt_type};
 
   const int Tp = rw_pitch(T);
+  const bool pairs = use_pairs<real>(lm, am, S1, T, C, rnnt_type) && T > 0;
   dim3 g3((unsigned)((Tp + 127) / 128), (unsigned)S1, (unsigned)B);
-  if (T > 0)
-    FRNNT_KERNEL(grad_weight_kernel<real><<<g3, 128, 0, st>>>(eg, norm, lmmax, ammax, rw, (real)cfg.both, Tp));
-  FRNNT_KERNEL(grad_row_sums_kernel<real><<<(int)((lm_rows * 32 + 255) / 256), 256, 0, st>>>(eg, sgx, sgy, B));
+  if (pairs) {
+    // one pass: Rw, the row sums and the row maxima of |Rw| (first floats of the pairs scratch)
+    FRNNT_KERNEL(grad_weight_rows_kernel<real><<<(unsigned)lm_rows, 128, 0, st>>>(
+        eg, norm, lmmax, ammax, rw, sgx, sgy, (float *)(scb + sc.total + simple_pairs_rowmax_offset(B, S, T, C)),
+        (real)cfg.both, Tp));
+  } else {
+    if (T > 0)
+      FRNNT_KERNEL(grad_weight_kernel<real><<<g3, 128, 0, st>>>(eg, norm, lmmax, ammax, rw, (real)cfg.both, Tp));
+    FRNNT_KERNEL(grad_row_sums_kernel<real><<<(int)((lm_rows * 32 + 255) / 256), 256, 0, st>>>(eg, sgx, sgy, B));
+  }
   if (T > 0)
     FRNNT_KERNEL(grad_col_sums_kernel<real><<<dim3((unsigned)((T + 31) / 32), (unsigned)B), 32 * kColSumWarps, 0,
                                               st>>>(eg, cgx, cgy, B));
@@ -796,7 +845,7 @@ static int simple_backward_impl(const void *lm_, const void *am_, const int64_t 
   }
 
   int rc;
-  if (use_pairs<real>(lm, am, S1, T, C, rnnt_type) && T > 0) {
+  if (pairs) {
     rc = launch_simple_grads_pairs((const float *)rw, (const float *)lmsum, (const float *)ammax,
                                    (const float *)amonly, (const float *)uni, (const float *)gl_p,
                                    (const float *)h_p, (const float *)dp_p, (const float *)rowdot_p,

@@ -52,10 +52,12 @@ SimplePairsLayout::SimplePairsLayout(int B, int S, int T, int C) {
   o = 0;
   rw_hi = take((size_t)B * S1 * Tq * 2);
   rw_lo = take((size_t)B * S1 * Tq * 2);
-  parts = take(kSpParts * 4);
+  parts = take(std::max<size_t>(kSpParts, (size_t)B * S1) * 4);
   inv_scale = take(64);
   scratch_bytes = o;
 }
+
+size_t simple_pairs_rowmax_offset(int B, int S, int T, int C) { return SimplePairsLayout(B, S, T, C).parts; }
 
 bool simple_pairs_supported(const void *lm, const void *am, int S1, int T, int C, int rnnt_type) {
   if (C % 4 != 0 || C < 4 || S1 < 1 || T < 1) return false;
@@ -367,22 +369,6 @@ struct AmGradPairExt {
   __device__ void tile_begin(int, int, uint8_t *, int) const {}
 };
 
-// per-CTA maxima of |x| (x >= 0 not assumed)
-__global__ void __launch_bounds__(256)
-sp_absmax_kernel(const float *__restrict__ x, long long n, float *__restrict__ part) {
-  __shared__ float s[8];
-  float m = 0.f;
-  for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < n; i += (long long)gridDim.x * 256)
-    m = fmaxf(m, fabsf(x[i]));
-  m = warp_max(m);
-  if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = m;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    for (int w = 1; w < 8; ++w) m = fmaxf(m, s[w]);
-    part[blockIdx.x] = m;
-  }
-}
-
 // Rw [rows][Tp] float -> planes [rows][Tq], columns Tp..Tq-1 zero (they are inside the
 // tensor maps only as padding up to T, never beyond it, but the backward's second product
 // reads rows as its reduction index and must not meet stale data)
@@ -476,10 +462,8 @@ int launch_simple_grads_pairs(const float *rw, const float *lmsum, const float *
   if (rc == FRNNT_OK) rc = make_pair_map(&b2l, lp_lo, S1, C, Cp, true, B, (long long)S1 * Cp);
   if (rc != FRNNT_OK) return rc;
 
-  const long long n = rows * Tp;
-  long long want = (n + 255) / 256;
-  const int nparts = (int)(want < 1 ? 1 : (want < kSpParts ? want : kSpParts));
-  FRNNT_KERNEL(sp_absmax_kernel<<<nparts, 256, 0, st>>>(rw, n, parts));
+  // the caller left max |rw| per row in `parts`
+  const int nparts = (int)rows;
   const long long nq = rows * Tq;
   const int grid = (int)std::min<long long>((nq + 255) / 256, (long long)sm_count() * 16);
   FRNNT_KERNEL(sp_split_kernel<<<grid, 256, 0, st>>>(rw, rows, Tp, Tq, parts, nparts, rw_hi, rw_lo, inv_rw));

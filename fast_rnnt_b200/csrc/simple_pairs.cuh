@@ -17,6 +17,10 @@ struct SimplePairsLayout {
   SimplePairsLayout(int B, int S, int T, int C);
 };
 
+// offset, inside the pairs scratch, of the per-row maxima of |rw| that the caller fills in
+// (B*(S+1) floats) before launch_simple_grads_pairs
+size_t simple_pairs_rowmax_offset(int B, int S, int T, int C);
+
 bool simple_pairs_supported(const void *lm, const void *am, int S1, int T, int C, int rnnt_type);
 
 // stage 0: row maxima / sums, exp planes, per-row scalars, the -inf column of px;
@@ -28,7 +32,8 @@ int launch_simple_forward_pairs(const float *lm, const float *am, const int64_t 
                                 const float *amonly, const float *loguni, void *pairs_saved, int B, int S,
                                 int T, int C, int stage, cudaStream_t st);
 
-// lm_grad / am_grad without the one-hot terms, from the gradient weights rw [B][S+1][Tp]
+// lm_grad / am_grad without the one-hot terms, from the gradient weights rw [B][S+1][Tp] and
+// the maxima of |rw| per row (see simple_pairs_rowmax_offset)
 int launch_simple_grads_pairs(const float *rw, const float *lmsum, const float *ammax, const float *amonly,
                               const float *uni, const float *gl, const float *h, const float *dp,
                               const float *rowdot, float *lm_grad, float *am_grad, const void *pairs_saved,

@@ -123,10 +123,20 @@ class MutualInformationRecursionFunction(torch.autograd.Function):
         need_grad = return_grad or px.requires_grad or py.requires_grad
         ans, _, lattice = mi_forward(px, py, boundary, want_p=False, want_lattice=need_grad)
         px_grad, py_grad = None, None
-        if need_grad:
+        ctx.deferred = False
+        if return_grad:
+            # the reference's contract: the reverse sweep runs at once with ans_grad = 1, the
+            # occupancies are handed out and rescaled in place when the loss is back-propagated
             ones = torch.ones(B, device=px.device, dtype=px.dtype)
             px_grad, py_grad = mi_backward_from_lattice(px, lattice, boundary, ones, py.shape)
             ctx.save_for_backward(px_grad, py_grad)
+        elif need_grad:
+            # nobody sees the occupancies: the reverse sweep waits for the real ans_grad, which
+            # saves the two rescaling passes over the lattice gradients (same result up to
+            # the rounding of one multiplication per entry)
+            ctx.deferred = True
+            ctx.py_shape = tuple(py.shape)
+            ctx.save_for_backward(px, lattice, boundary)
         assert len(pxy_grads) == 2
         pxy_grads[0] = px_grad
         pxy_grads[1] = py_grad
@@ -134,6 +144,11 @@ class MutualInformationRecursionFunction(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, ans_grad: Tensor) -> Tuple[Tensor, Tensor, None, None, None]:
+        if ctx.deferred:
+            px, lattice, boundary = ctx.saved_tensors
+            px_grad, py_grad = mi_backward_from_lattice(px, lattice, boundary,
+                                                        ans_grad.contiguous().to(px.dtype), ctx.py_shape)
+            return (px_grad, py_grad, None, None, None)
         (px_grad, py_grad) = ctx.saved_tensors
         (B,) = ans_grad.shape
         ans_grad = ans_grad.reshape(B, 1, 1)
