@@ -48,8 +48,8 @@ C5_GLOBAL_LOSS = None
 NCU_TRAFFIC_C3 = {
     # profiles/kernels_c3_half_batch_ncu_full.txt: captured at half batch, doubled (every kernel
     # streams its operands once, so its traffic grows with the number of rows)
-    "pair_linear_fwd": 2 * 277.0e6, "pair_linear_grad_input": 2 * 461.8e6,
-    "pair_linear_grad_weight": 2 * 331.5e6,
+    "fused_fwd_product": 2 * 277.0e6, "fused_bwd_grad_input": 2 * 461.8e6,
+    "fused_bwd_grad_weight": 2 * 331.5e6,
     "mi_forward": 2 * 8.3e6, "mi_backward": 2 * 5.9e6, "mi_forward_pruned": 2 * 8.3e6,
     "mi_backward_pruned": 2 * 5.9e6,
 }
@@ -130,7 +130,7 @@ class ClockSampler:
 # ------------------------------------------------------------------------------
 # the step
 # ------------------------------------------------------------------------------
-def make_step(fr, wl, joiner="torch"):
+def make_step(fr, wl, joiner="torch", overlap=False):
     """Returns step(inputs) -> loss for the pruned pipeline; `fr` is the loss package
     (ours on CUDA, or the CPU oracle / the reference wrapped to the same names).
     joiner: how the caller's network between pruning and the pruned loss runs --
@@ -138,11 +138,27 @@ def make_step(fr, wl, joiner="torch"):
                     reference's documented usage, the only form the reference offers),
       "tensorcore"  this library's pruned_joiner (3xTF32 products) + rnnt_loss_pruned,
       "fused"       this library's rnnt_loss_pruned_joiner: one operator from enc / dec to
-                    the pruned lattices (fp16-pair products, log-sum-exp in the epilogue)."""
+                    the pruned lattices (fp16-pair products, log-sum-exp in the epilogue).
+    overlap: run the simple loss on a second CUDA stream (see inside)."""
     blank, R = wl["blank"], wl["s_range"]
     ls, as_ = wl["lm_only_scale"], wl["am_only_scale"]
+    side = [None]   # CUDA only: the stream the simple loss runs on
 
     def step(t):
+        on_gpu = t["am"].is_cuda
+        if on_gpu and overlap:
+            # The simple loss runs on a second stream.  Forward nothing is gained (the prune
+            # ranges need its occupancies), but autograd runs every backward node on the stream
+            # of its forward: the simple loss's backward (small kernels + short products) then
+            # overlaps with the pruned branch's large products instead of queueing behind them.
+            if side[0] is None:
+                side[0] = torch.cuda.Stream(device=t["am"].device)
+            main = torch.cuda.current_stream(t["am"].device)
+            side[0].wait_stream(main)
+            ctx = torch.cuda.stream(side[0])
+        else:
+            import contextlib
+            main, ctx = None, contextlib.nullcontext()
         am = t["am"].requires_grad_(True)
         lm = t["lm"].requires_grad_(True)
         enc = t["enc"].requires_grad_(True)
@@ -151,9 +167,12 @@ def make_step(fr, wl, joiner="torch"):
         bias = t["joiner_b"].requires_grad_(True)
         for x in (am, lm, enc, dec, W, bias):
             x.grad = None
-        simple, (gx, gy) = fr.rnnt_loss_smoothed(
-            lm=lm, am=am, symbols=t["symbols"], termination_symbol=blank, lm_only_scale=ls,
-            am_only_scale=as_, boundary=t["boundary"], reduction="sum", return_grad=True)
+        with ctx:
+            simple, (gx, gy) = fr.rnnt_loss_smoothed(
+                lm=lm, am=am, symbols=t["symbols"], termination_symbol=blank, lm_only_scale=ls,
+                am_only_scale=as_, boundary=t["boundary"], reduction="sum", return_grad=True)
+        if main is not None:
+            main.wait_stream(side[0])
         ranges = fr.get_rnnt_prune_ranges(px_grad=gx, py_grad=gy, boundary=t["boundary"], s_range=R)
         if joiner == "fused":
             pruned = fr.rnnt_loss_pruned_joiner(
@@ -171,6 +190,8 @@ def make_step(fr, wl, joiner="torch"):
                                          reduction="sum")
         loss = simple + pruned
         loss.backward()
+        if main is not None:
+            main.wait_stream(side[0])   # the step ends when both branches have
         return loss.detach()
 
     return step
@@ -279,7 +300,8 @@ def reference_cuda_run(workload, batch, sample_batch, cpu_grads, dev):
     med = statistics.median(ms)
     out = {"ms_per_step": round(med, 3), "value": round(batch / (med * 1e-3), 1), "unit": "utt/s",
            "what": "the reference's python package on CUDA tensors with its own CUDA kernels, "
-                   "joiner in torch (cuBLAS fp32), same workload, CUDA events, median of 5"}
+                   "joiner in torch (cuBLAS fp32), same workload, CUDA events, median of 5; one "
+                   "stream (its kernels launch on the legacy default stream)"}
     noise = None
     if cpu_grads is not None:
         wl_s = workloads.pipeline_workload(workload, batch=sample_batch)
@@ -437,42 +459,35 @@ def stage_table(fr, wl, dev, flush, hbm_gbs):
                   _lib.ptr(dec_g), _lib.ptr(w_g), _lib.ptr(b_g), B, T, R, S, C, D, 0, 0, sp)
 
     Cp = (C + 63) // 64 * 64
-    half = lambda *shape: torch.empty(*shape, dtype=torch.float16, device=dev)  # noqa: E731
-    pscr = torch.empty(lib.frnnt_pairs_scratch_floats(), device=dev)
-    inv = torch.empty(4, device=dev)
-    a_hi, a_lo, w_hi, w_lo = half(M, D), half(M, D), half(C, D), half(C, D)
-    g_hi, g_lo, wt_hi, wt_lo = half(M, Cp), half(M, Cp), half(D, Cp), half(D, Cp)
 
-    def planes(x, rows, cols, pitch, hi, lo, slot):
-        _lib.call("frnnt_pairs_from_f32", _lib.ptr(x), _lib._c_longlong(rows), cols,
-                  _lib._c_longlong(pitch), _lib.ptr(hi), _lib.ptr(lo), _lib.ptr(inv[slot:]),
-                  _lib.ptr(pscr), sp)
+    def fwd_part(part):
+        return lambda: _lib.call(
+            "frnnt_pruned_joiner_logprobs_forward_part", part, _lib.ptr(t["enc"]), _lib.ptr(t["dec"]),
+            _lib.ptr(ranges), _lib.ptr(W), _lib.ptr(t["joiner_b"]), _lib.ptr(sym), _lib.ptr(bnd),
+            _lib.ptr(ppxd), _lib.ptr(ppyd), _lib.ptr(pj_saved), _lib.ptr(pj_fs), B, T, R, S, C, D, 0, 0, sp)
 
-    planes(act2, M, D, D, a_hi, a_lo, 0)
-    planes(W, C, D, D, w_hi, w_lo, 1)
-    planes(g_logits, M, C, Cp, g_hi, g_lo, 2)
-    planes(Wt, D, C, Cp, wt_hi, wt_lo, 3)
-    out_mc, out_md = torch.empty(M, C, device=dev), torch.empty(M, D, device=dev)
-    tn_parts = torch.empty(max(1, lib.frnnt_pair_matmul_tn_splits(C, D, _lib._c_longlong(M)) * C * D),
-                           device=dev)
-    LL = _lib._c_longlong
+    def bwd_part(part):
+        return lambda: _lib.call(
+            "frnnt_pruned_joiner_logprobs_backward_part", part, _lib.ptr(gpx), _lib.ptr(gpy),
+            _lib.ptr(ranges), _lib.ptr(sym), _lib.ptr(bnd), _lib.ptr(pj_saved), _lib.ptr(pj_bs),
+            _lib.ptr(enc_g), _lib.ptr(dec_g), _lib.ptr(w_g), _lib.ptr(b_g), B, T, R, S, C, D, 0, 0, sp)
+
+    pj_fwd()
+    pj_bwd()   # every buffer the parts below work on is filled
+    planes_bytes = es * (B * (T + S1) * D + M * D + 3 * C * D) + 8 * M
     stages += [
         ("fused_joiner_lattices_fwd", pj_fwd,
          es * (B * (T + S1) * D + 8 * M // 4 + M * D + M * C + C * D) + lat, gemm_flops),
         ("fused_joiner_lattices_bwd", pj_bwd,
          lat + es * (2 * M * C + 2 * M * D + B * (T + S1) * D + 2 * C * D), 2 * gemm_flops),
-        ("pair_linear_fwd", lambda: _lib.call(
-            "frnnt_pair_matmul_nt", _lib.ptr(a_hi), _lib.ptr(a_lo), _lib.ptr(w_hi), _lib.ptr(w_lo),
-            _lib.ptr(inv[0:]), _lib.ptr(inv[1:]), _lib.ptr(t["joiner_b"]), _lib.ptr(out_mc), M, C, D,
-            LL(D), LL(D), sp), es * (M * D + M * C + C * D), gemm_flops),
-        ("pair_linear_grad_input", lambda: _lib.call(
-            "frnnt_pair_matmul_nt", _lib.ptr(g_hi), _lib.ptr(g_lo), _lib.ptr(wt_hi), _lib.ptr(wt_lo),
-            _lib.ptr(inv[2:]), _lib.ptr(inv[3:]), None, _lib.ptr(out_md), M, D, C, LL(Cp), LL(Cp), sp),
-         es * (M * C + M * D + C * D), gemm_flops),
-        ("pair_linear_grad_weight", lambda: _lib.call(
-            "frnnt_pair_matmul_tn", _lib.ptr(g_hi), _lib.ptr(g_lo), _lib.ptr(a_hi), _lib.ptr(a_lo),
-            _lib.ptr(inv[2:]), _lib.ptr(inv[0:]), _lib.ptr(w_g), _lib.ptr(tn_parts), C, D, LL(M),
-            LL(Cp), LL(D), sp), es * (M * C + M * D + C * D), gemm_flops),
+        # the same calls, one part at a time (what a step launches, kernel group by kernel group)
+        ("fused_fwd_planes", fwd_part(0), planes_bytes, None),
+        ("fused_fwd_product", fwd_part(1), es * (M * D + M * C + C * D), gemm_flops),
+        ("fused_fwd_lattices", fwd_part(2), lat + 8 * M * 3 + es * M * (C // 128 + 1) * 2, None),
+        ("fused_bwd_planes", bwd_part(0), lat + es * M * (C + Cp), None),
+        ("fused_bwd_grad_input", bwd_part(1), es * (M * Cp + 2 * M * D + C * D), gemm_flops),
+        ("fused_bwd_input_grads", bwd_part(4), es * (M * D + B * (T + S1) * D), None),
+        ("fused_bwd_grad_weight", bwd_part(3), es * (M * Cp + M * D + C * D), gemm_flops),
     ]
     out = {}
     for name, fn, nbytes, flops in stages:
@@ -489,13 +504,14 @@ COMMON_STAGES = ["simple_logprobs_fwd", "simple_logprobs_bwd", "mi_forward", "mi
                  "mi_forward_pruned", "mi_backward_pruned", "prune_ranges"]
 STEP_STAGES = {
     # stages of the table above that one timed step launches, by --joiner
-    "fused": COMMON_STAGES + ["fused_joiner_lattices_fwd", "fused_joiner_lattices_bwd"],
+    "fused": COMMON_STAGES + ["fused_fwd_planes", "fused_fwd_product", "fused_fwd_lattices", "fused_bwd_planes",
+                              "fused_bwd_grad_input", "fused_bwd_input_grads", "fused_bwd_grad_weight"],
     "tensorcore": COMMON_STAGES + ["joiner_tanh", "joiner_linear_fwd", "lsm_gather_fwd", "lsm_gather_bwd",
                                    "joiner_linear_grad_input", "joiner_linear_grad_weight",
                                    "joiner_input_grads"],
     "torch": COMMON_STAGES + ["prune_gather_fwd", "lsm_gather_fwd", "lsm_gather_bwd", "prune_gather_bwd"],
 }
-PRODUCT_STAGES = {"fused": ["pair_linear_fwd", "pair_linear_grad_input", "pair_linear_grad_weight"],
+PRODUCT_STAGES = {"fused": ["fused_fwd_product", "fused_bwd_grad_input", "fused_bwd_grad_weight"],
                   "tensorcore": ["joiner_linear_fwd", "joiner_linear_grad_input",
                                  "joiner_linear_grad_weight"],
                   "torch": []}
@@ -543,6 +559,9 @@ def main():
                     help="the caller's joiner: this library's fused rnnt_loss_pruned_joiner "
                          "(fp16-pair tcgen05 products), its pruned_joiner (3xTF32 products), or "
                          "torch.nn.functional.linear (cuBLAS fp32)")
+    ap.add_argument("--no-overlap", action="store_true",
+                    help="keep the simple loss on the main stream (its backward then queues behind "
+                         "the pruned branch's instead of overlapping with it)")
     ap.add_argument("--no-stages", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -619,7 +638,7 @@ def main():
         wl = workloads.pipeline_workload(args.workload, batch=batch, seed=rank)
     host = {k: wl[k].pin_memory() for k in TENSOR_KEYS}
     resident = {k: v.to(dev) for k, v in host.items()}
-    inner = make_step(fr, wl, args.joiner)
+    inner = make_step(fr, wl, args.joiner, overlap=not args.no_overlap)
 
     from fast_rnnt_b200 import sharding
 
@@ -754,7 +773,11 @@ def main():
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": cfg,
-            "joiner_impl": joiner_impl[args.joiner], "clocks": clocks.summary(),
+            "joiner_impl": joiner_impl[args.joiner],
+            "streams": ("one" if args.no_overlap else
+                        "two: the simple loss (forward, hence its backward) on a second stream, "
+                        "so that its backward overlaps with the pruned branch's"),
+            "clocks": clocks.summary(),
             "e2e": {"value": round(e2e_value, 1), "unit": "utt/s", "h2d_bytes_per_step": int(h2d),
                     "d2h_bytes_per_step": 4, "ms_per_step": round(e2e_ms, 4),
                     "note": "uploads every input of the step, reads back the loss; the input "
@@ -779,7 +802,8 @@ def main():
         line["step_stages"] = {"launched_by_the_timed_step": in_step,
                                "sum_ms": round(step_sum, 4),
                                "note": "each stage timed alone with a flushed L2; their sum is not "
-                                       "the step time (ms_per_step is), it shows where it goes"}
+                                       "the step time (ms_per_step is: stages overlap there), it "
+                                       "shows where the time goes"}
         line["loss_path"] = {"ms_per_step": round(step_sum - prod_sum, 4),
                              "value": round(batch / ((step_sum - prod_sum) * 1e-3), 1), "unit": "utt/s",
                              "note": "the stages the timed step launches minus the joiner's three "
@@ -793,7 +817,7 @@ def main():
             top = max(products, key=lambda k: stages[k]["ms"])
             pairs = args.joiner == "fused"
             line["roofline"] = {
-                "kernel": top + (" (pair_umma_kernel, fp16-pair tcgen05)" if pairs else
+                "kernel": top + (" (pair_umma_kernel / pair_umma256_kernel, fp16-pair tcgen05)" if pairs else
                                  " (linear_umma_kernel, 3xTF32 tcgen05)"),
                 "bound": "tensor", "achieved": stages[top]["tflops"], "peak": tf_peak, "unit": "TFLOP/s",
                 "frac": round(stages[top]["tflops"] / tf_peak, 4),

@@ -24,10 +24,12 @@
 //              enc_grad / dec_grad from one pass over gz;  W_grad = g^T * act, split-K.
 #include <cuda_fp16.h>
 
+#include <stdlib.h>
+
 #include <algorithm>
 
 #include "lsm_band.cuh"
-#include "umma_pairs.cuh"
+#include "umma_pairs256.cuh"
 
 namespace frnnt {
 
@@ -39,9 +41,34 @@ enum { kScaleAct = 0, kScaleW = 1, kScaleG = 2 };  // slots of the inverse scale
 
 static inline size_t up256(size_t x) { return (x + 255) & ~(size_t)255; }
 
+// rows of an output tile.  The 256 x 128 kernel (umma_pairs256.cuh) moves a quarter fewer
+// bytes per flop, but its eight warps do both folding and epilogue; measured at C3 it wins
+// where the epilogue is trivial and the reduction long (grad-weight, plain products:
+// 0.235 -> 0.21 ms) and loses where the epilogue carries the log-sum-exp partials or the
+// tanh' activations (fused forward 0.41 -> 0.43 ms, backward 0.78 -> 0.88 ms), so only the
+// former use it.  FRNNT_PAIR_TILE=128 forces the 128 x 128 kernel everywhere.
+static int pair_tile_m(int M, bool light_epilogue) {
+  static int forced = -1;
+  if (forced < 0) {
+    const char *e = getenv("FRNNT_PAIR_TILE");
+    forced = (e != nullptr && atoi(e) == 128) ? 128 : 0;
+  }
+  return (forced == 128 || !light_epilogue || M <= kPairTile) ? kPairTile : kP2TileM;
+}
+
+template <bool A_MN, bool B_MN, class Ext>
+static int launch_pair(const CUtensorMap &mah, const CUtensorMap &mal, const CUtensorMap &mbh,
+                       const CUtensorMap &mbl, float *out, LinShape shape, const Ext &ext, cudaStream_t st) {
+  const int tm = pair_tile_m(shape.M, Ext::kLightEpilogue);
+  shape.tiles_m = (shape.M + tm - 1) / tm;
+  if (tm == kP2TileM) return launch_pair_umma256<A_MN, B_MN>(mah, mal, mbh, mbl, out, shape, ext, st);
+  return launch_pair_umma<A_MN, B_MN>(mah, mal, mbh, mbl, out, shape, ext, st);
+}
+
 static int pair_tn_splits(int M, int N, long long R) {
   if (M <= 0 || N <= 0 || R <= 0) return 1;
-  const long long tiles = (long long)((M + kPairTile - 1) / kPairTile) * ((N + kPairTile - 1) / kPairTile);
+  const int tm = pair_tile_m(M, true);  // the split products have light epilogues
+  const long long tiles = (long long)((M + tm - 1) / tm) * ((N + kPairTile - 1) / kPairTile);
   const long long max_splits = (R + 8 * kPairBK - 1) / (8 * kPairBK);
   const long long sms = sm_count();
   int best = 1;
@@ -215,7 +242,7 @@ pruned_tanh_pairs_kernel(const float *__restrict__ enc, const float *__restrict_
 // ---- epilogues of the three products ----------------------------------------------------------
 // logits = acc * (1/scales) + bias, and per row and tile (max, sum exp(logit - max))
 struct PjlFwdExt {
-  static constexpr bool kBatched = false, kCustomStore = false;
+  static constexpr bool kBatched = false, kCustomStore = false, kLightEpilogue = false;
   template <class R> __device__ void store_box(R &, int, int, int, int, float (&)[16], float (&)[16], const uint8_t *) const {}
   __device__ void tile_begin(int, int, uint8_t *, int) const {}
   const float *bias;
@@ -255,7 +282,7 @@ struct PjlFwdExt {
 
 // gz = acc * (1/scales) * (1 - act^2): the gradient with respect to enc + dec
 struct PjlGradInExt {
-  static constexpr bool kBatched = false, kCustomStore = false;
+  static constexpr bool kBatched = false, kCustomStore = false, kLightEpilogue = false;
   template <class R> __device__ void store_box(R &, int, int, int, int, float (&)[16], float (&)[16], const uint8_t *) const {}
   __device__ void tile_begin(int, int, uint8_t *, int) const {}
   const __half *act_hi, *act_lo;
@@ -303,7 +330,7 @@ struct PjlGradInExt {
 
 // W_grad partial sums: acc * (1/scales)
 struct PjlGradWExt {
-  static constexpr bool kBatched = false, kCustomStore = false;
+  static constexpr bool kBatched = false, kCustomStore = false, kLightEpilogue = true;
   template <class R> __device__ void store_box(R &, int, int, int, int, float (&)[16], float (&)[16], const uint8_t *) const {}
   __device__ void tile_begin(int, int, uint8_t *, int) const {}
   const float *scales;
@@ -329,25 +356,20 @@ __global__ void ordered_sum_kernel(const float *__restrict__ partial, float *__r
   out[i] = acc;
 }
 
-// the same for many parts of a short vector (column sums per CTA -> bias gradient): 32
-// columns per CTA, eight warps take the parts z = w, w + 8, ... and their sums are added
-// in warp order -- a fixed order, with eight loads in flight per column instead of one
+// column sums per row group -> bias gradient.  The partials are stored column-major,
+// partial[c][g]: one warp per column reads them as contiguous lines, every lane adds the
+// groups g = lane, lane + 32, ... in order and the lanes are combined by a fixed shuffle
+// tree -- the same order on every run.
 __global__ void __launch_bounds__(256)
-ordered_sum_tall_kernel(const float *__restrict__ partial, float *__restrict__ out, int n, int parts) {
-  __shared__ float s[8][33];
-  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-  const int i = blockIdx.x * 32 + lane;
+ordered_sum_cols_kernel(const float *__restrict__ partial, float *__restrict__ out, int n, int groups) {
+  const int lane = threadIdx.x & 31;
+  const int c = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (c >= n) return;
+  const float *src = partial + (size_t)c * groups;
   float acc = 0.f;
-  if (i < n)
-    for (int z = w; z < parts; z += 8) acc += partial[(size_t)z * n + i];
-  s[w][lane] = acc;
-  __syncthreads();
-  if (w == 0 && i < n) {
-    float t = 0.f;
-#pragma unroll
-    for (int k = 0; k < 8; ++k) t += s[k][lane];
-    out[i] = t;
-  }
+  for (int g = lane; g < groups; g += 32) acc += src[g];
+  acc = warp_sum(acc);
+  if (lane == 0) out[c] = acc;
 }
 
 // ---- bands ------------------------------------------------------------------------------------
@@ -420,7 +442,7 @@ band_grad_kernel(const float *__restrict__ g_px, const float *__restrict__ g_py,
 // as planes (|g| <= |gx| + |gy|, whose maximum sets the scale).  Thread <-> four columns,
 // CTA <-> a contiguous group of rows x a chunk of up to 1024 columns: the loads of four rows are
 // in flight together, and the column sums of g (the bias gradient) stay in registers across
-// the whole group -> one partial per group, added in order afterwards (no atomics).
+// the whole group -> one partial per group, added in a fixed order afterwards (no atomics).
 constexpr int kLsmRowsInFlight = 4;
 __global__ void __launch_bounds__(256)
 lsm_backward_pairs_kernel(const float *__restrict__ logits, const float4 *__restrict__ rowinfo,
@@ -468,13 +490,19 @@ lsm_backward_pairs_kernel(const float *__restrict__ logits, const float4 *__rest
       acc.x += g[0], acc.y += g[1], acc.z += g[2], acc.w += g[3];
     }
   }
-  if (col_ok) reinterpret_cast<float4 *>(cs_part + (size_t)blockIdx.y * C)[v] = acc;
+  if (col_ok) {  // column-major: partial[c][group]
+    float *dst = cs_part + (size_t)c0 * groups + blockIdx.y;
+    dst[0] = acc.x;
+    dst[(size_t)groups] = acc.y;
+    dst[(size_t)2 * groups] = acc.z;
+    dst[(size_t)3 * groups] = acc.w;
+  }
 }
 
 // ---- plain products on planes (the engine without the joiner around it) -------------------------
 // D = acc * inv_scale_a * inv_scale_b (+ bias[n])
 struct PlainPairExt {
-  static constexpr bool kBatched = false, kCustomStore = false;
+  static constexpr bool kBatched = false, kCustomStore = false, kLightEpilogue = true;
   template <class R> __device__ void store_box(R &, int, int, int, int, float (&)[16], float (&)[16], const uint8_t *) const {}
   __device__ void tile_begin(int, int, uint8_t *, int) const {}
   const float *bias, *inv_a, *inv_b;
@@ -547,13 +575,13 @@ extern "C" size_t frnnt_pruned_joiner_backward_scratch_bytes(int B, int T, int R
   return pjl_layout(B, T, R, S + 1, C, D).bwd_bytes;
 }
 
-extern "C" int frnnt_pruned_joiner_logprobs_forward(const float *enc, const float *dec,
-                                                    const int64_t *ranges, const float *weight,
-                                                    const float *bias, const int64_t *symbols,
-                                                    const int64_t *boundary, float *px, float *py,
-                                                    void *saved, void *scratch, int B, int T, int R,
-                                                    int S, int C, int D, int blank, int rnnt_type,
-                                                    void *stream) {
+// parts of a forward / backward call (bit mask); the diagnostic entry points re-launch one
+enum { kPartPlanes = 1, kPartProduct = 2, kPartRest = 4, kPartProduct2 = 8, kPartInputGrads = 16 };
+
+static int pjl_forward(const float *enc, const float *dec, const int64_t *ranges, const float *weight,
+                       const float *bias, const int64_t *symbols, const int64_t *boundary, float *px,
+                       float *py, void *saved, void *scratch, int B, int T, int R, int S, int C, int D,
+                       int blank, int rnnt_type, void *stream, unsigned parts) {
   int rc = pjl_check(B, T, R, S, C, D, blank, rnnt_type);
   if (rc != FRNNT_OK) return rc;
   if (B == 0 || T == 0) return FRNNT_OK;
@@ -582,39 +610,63 @@ extern "C" int frnnt_pruned_joiner_logprobs_forward(const float *enc, const floa
   if (rc == FRNNT_OK) rc = make_pair_map(&mbl, w_lo, C, D, D, false);
   if (rc != FRNNT_OK) return rc;
 
-  const long long nW = (long long)C * D;
-  const int wparts = parts_for(nW);
-  FRNNT_KERNEL(absmax_partial_kernel<<<wparts, 256, 0, st>>>(weight, nW, amax));
-  FRNNT_KERNEL(split_weights_kernel<<<wparts, 256, 0, st>>>(weight, C, D, (int)L.Cp, amax, wparts, w_hi, w_lo,
-                                                           wt_hi, wt_lo, scales));
-  {
+  if (parts & kPartPlanes) {
+    const long long nW = (long long)C * D;
+    const int wparts = parts_for(nW);
+    FRNNT_KERNEL(absmax_partial_kernel<<<wparts, 256, 0, st>>>(weight, nW, amax));
+    FRNNT_KERNEL(split_weights_kernel<<<wparts, 256, 0, st>>>(weight, C, D, (int)L.Cp, amax, wparts, w_hi, w_lo,
+                                                             wt_hi, wt_lo, scales));
     long long want = (rows + 7) / 8;
     const int grid = (int)(want < (long long)sm_count() * 32 ? want : (long long)sm_count() * 32);
     FRNNT_KERNEL(pruned_tanh_pairs_kernel<<<grid, 256, 0, st>>>(enc, dec, ranges, act_hi, act_lo, rows, R,
                                                                T * R, S + 1, D, scales));
+    FRNNT_CUDA(cudaGetLastError());
   }
-  FRNNT_CUDA(cudaGetLastError());
-  const int mt = (M + kPairTile - 1) / kPairTile;
-  const LinShape shape{M, C, D, ((D + kPairBK - 1) / kPairBK) * kPairBK, mt, L.tiles_n, 1};
-  rc = launch_pair_umma<false, false>(mah, mal, mbh, mbl, logits, shape,
-                                      PjlFwdExt{bias, stats, scales, C, L.tiles_n}, st);
-  if (rc != FRNNT_OK) return rc;
-  FRNNT_KERNEL(joiner_band_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(
-      logits, stats, symbols, ranges, lse, pxb, pyb, rows, T, R, S, C, blank, L.tiles_n));
-  dim3 grid2((unsigned)((T + 1 + 127) / 128), (unsigned)(S + 1), (unsigned)B);
-  FRNNT_KERNEL(band_to_lattice_kernel<float><<<grid2, 128, 0, st>>>(pxb, pyb, ranges, boundary, px, py, S, T, R,
-                                                                   rnnt_type));
-  FRNNT_CUDA(cudaGetLastError());
+  if (parts & kPartProduct) {
+    const int mt = (M + kPairTile - 1) / kPairTile;
+    const LinShape shape{M, C, D, ((D + kPairBK - 1) / kPairBK) * kPairBK, mt, L.tiles_n, 1};
+    rc = launch_pair<false, false>(mah, mal, mbh, mbl, logits, shape,
+                                   PjlFwdExt{bias, stats, scales, C, L.tiles_n}, st);
+    if (rc != FRNNT_OK) return rc;
+  }
+  if (parts & kPartRest) {
+    FRNNT_KERNEL(joiner_band_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(
+        logits, stats, symbols, ranges, lse, pxb, pyb, rows, T, R, S, C, blank, L.tiles_n));
+    dim3 grid2((unsigned)((T + 1 + 127) / 128), (unsigned)(S + 1), (unsigned)B);
+    FRNNT_KERNEL(band_to_lattice_kernel<float><<<grid2, 128, 0, st>>>(pxb, pyb, ranges, boundary, px, py, S, T, R,
+                                                                     rnnt_type));
+    FRNNT_CUDA(cudaGetLastError());
+  }
   return FRNNT_OK;
 }
 
-extern "C" int frnnt_pruned_joiner_logprobs_backward(const float *px_grad, const float *py_grad,
-                                                     const int64_t *ranges, const int64_t *symbols,
-                                                     const int64_t *boundary, void *saved,
-                                                     void *scratch, float *enc_grad, float *dec_grad,
-                                                     float *weight_grad, float *bias_grad, int B, int T,
-                                                     int R, int S, int C, int D, int blank, int rnnt_type,
-                                                     void *stream) {
+extern "C" int frnnt_pruned_joiner_logprobs_forward(const float *enc, const float *dec,
+                                                    const int64_t *ranges, const float *weight,
+                                                    const float *bias, const int64_t *symbols,
+                                                    const int64_t *boundary, float *px, float *py,
+                                                    void *saved, void *scratch, int B, int T, int R,
+                                                    int S, int C, int D, int blank, int rnnt_type,
+                                                    void *stream) {
+  return pjl_forward(enc, dec, ranges, weight, bias, symbols, boundary, px, py, saved, scratch, B, T, R, S, C, D,
+                     blank, rnnt_type, stream, ~0u);
+}
+
+extern "C" int frnnt_pruned_joiner_logprobs_forward_part(int part, const float *enc, const float *dec,
+                                                         const int64_t *ranges, const float *weight,
+                                                         const float *bias, const int64_t *symbols,
+                                                         const int64_t *boundary, float *px, float *py,
+                                                         void *saved, void *scratch, int B, int T, int R,
+                                                         int S, int C, int D, int blank, int rnnt_type,
+                                                         void *stream) {
+  FRNNT_REQUIRE(part >= 0 && part <= 2, FRNNT_EINVAL, "part must be 0 (planes), 1 (product) or 2 (lattices)");
+  return pjl_forward(enc, dec, ranges, weight, bias, symbols, boundary, px, py, saved, scratch, B, T, R, S, C, D,
+                     blank, rnnt_type, stream, 1u << part);
+}
+
+static int pjl_backward(const float *px_grad, const float *py_grad, const int64_t *ranges,
+                        const int64_t *symbols, const int64_t *boundary, void *saved, void *scratch,
+                        float *enc_grad, float *dec_grad, float *weight_grad, float *bias_grad, int B, int T,
+                        int R, int S, int C, int D, int blank, int rnnt_type, void *stream, unsigned parts) {
   int rc = pjl_check(B, T, R, S, C, D, blank, rnnt_type);
   if (rc != FRNNT_OK) return rc;
   if (B == 0 || T == 0) return FRNNT_OK;
@@ -653,24 +705,26 @@ extern "C" int frnnt_pruned_joiner_logprobs_backward(const float *px_grad, const
   if (rc != FRNNT_OK) return rc;
 
   const int gparts = parts_for(rows);
-  FRNNT_KERNEL(band_grad_kernel<<<gparts, 256, 0, st>>>(px_grad, py_grad, symbols, ranges, boundary, lse, rowinfo,
-                                                       gmax, rows, T, R, S, C, blank, rnnt_type));
-  {
+  if (parts & kPartPlanes) {
+    FRNNT_KERNEL(band_grad_kernel<<<gparts, 256, 0, st>>>(px_grad, py_grad, symbols, ranges, boundary, lse, rowinfo,
+                                                         gmax, rows, T, R, S, C, blank, rnnt_type));
     const int th = lsm_threads(C);
     dim3 grid((unsigned)((C / 4 + th - 1) / th), (unsigned)L.cs_ctas);
     FRNNT_KERNEL(lsm_backward_pairs_kernel<<<grid, th, 0, st>>>(logits, rowinfo, gmax, gparts, g_hi, g_lo, cs_part,
-                                                                scales, rows, C, Cp, blank, L.cs_ctas));
-  }
-  FRNNT_CUDA(cudaGetLastError());
-  if (bias_grad != nullptr) {
-    FRNNT_KERNEL(ordered_sum_tall_kernel<<<(unsigned)((C + 31) / 32), 256, 0, st>>>(cs_part, bias_grad, C, L.cs_ctas));
+                                                               scales, rows, C, Cp, blank, L.cs_ctas));
     FRNNT_CUDA(cudaGetLastError());
+    if (bias_grad != nullptr) {
+      FRNNT_KERNEL(ordered_sum_cols_kernel<<<(unsigned)((C + 7) / 8), 256, 0, st>>>(cs_part, bias_grad, C, L.cs_ctas));
+      FRNNT_CUDA(cudaGetLastError());
+    }
   }
   const int mt = (M + kPairTile - 1) / kPairTile;
-  if (enc_grad != nullptr) {
+  if (enc_grad != nullptr && (parts & kPartProduct)) {
     const LinShape shape{M, D, C, ((C + kPairBK - 1) / kPairBK) * kPairBK, mt, (D + kPairTile - 1) / kPairTile, 1};
-    rc = launch_pair_umma<false, false>(gih, gil, wth, wtl, gz, shape, PjlGradInExt{act_hi, act_lo, scales, D}, st);
+    rc = launch_pair<false, false>(gih, gil, wth, wtl, gz, shape, PjlGradInExt{act_hi, act_lo, scales, D}, st);
     if (rc != FRNNT_OK) return rc;
+  }
+  if (enc_grad != nullptr && (parts & kPartInputGrads)) {
     if (D % 4 == 0 && D <= 3200) {
       rc = frnnt_joiner_input_grads(gz, ranges, enc_grad, dec_grad, sc + L.jg, B, S + 1, T, R, D, stream);
     } else {
@@ -680,14 +734,14 @@ extern "C" int frnnt_pruned_joiner_logprobs_backward(const float *px_grad, const
     }
     if (rc != FRNNT_OK) return rc;
   }
-  if (weight_grad != nullptr) {
+  if (weight_grad != nullptr && (parts & kPartProduct2)) {
     const int splits = L.splits;
     const long long kblocks = (rows + kPairBK - 1) / kPairBK;
     const int k_per_split = (int)((kblocks + splits - 1) / splits) * kPairBK;
     const LinShape shape{C, D, M, k_per_split, (C + kPairTile - 1) / kPairTile, (D + kPairTile - 1) / kPairTile,
                          splits};
     float *out = splits == 1 ? weight_grad : dw_part;
-    rc = launch_pair_umma<true, true>(gwh, gwl, ach, acl, out, shape, PjlGradWExt{scales}, st);
+    rc = launch_pair<true, true>(gwh, gwl, ach, acl, out, shape, PjlGradWExt{scales}, st);
     if (rc != FRNNT_OK) return rc;
     if (splits > 1) {
       const long long n = (long long)C * D;
@@ -696,6 +750,29 @@ extern "C" int frnnt_pruned_joiner_logprobs_backward(const float *px_grad, const
     }
   }
   return FRNNT_OK;
+}
+
+extern "C" int frnnt_pruned_joiner_logprobs_backward(const float *px_grad, const float *py_grad,
+                                                     const int64_t *ranges, const int64_t *symbols,
+                                                     const int64_t *boundary, void *saved,
+                                                     void *scratch, float *enc_grad, float *dec_grad,
+                                                     float *weight_grad, float *bias_grad, int B, int T,
+                                                     int R, int S, int C, int D, int blank, int rnnt_type,
+                                                     void *stream) {
+  return pjl_backward(px_grad, py_grad, ranges, symbols, boundary, saved, scratch, enc_grad, dec_grad, weight_grad,
+                      bias_grad, B, T, R, S, C, D, blank, rnnt_type, stream, ~0u);
+}
+
+extern "C" int frnnt_pruned_joiner_logprobs_backward_part(int part, const float *px_grad, const float *py_grad,
+                                                          const int64_t *ranges, const int64_t *symbols,
+                                                          const int64_t *boundary, void *saved, void *scratch,
+                                                          float *enc_grad, float *dec_grad, float *weight_grad,
+                                                          float *bias_grad, int B, int T, int R, int S, int C,
+                                                          int D, int blank, int rnnt_type, void *stream) {
+  FRNNT_REQUIRE(part == 0 || part == 1 || part == 3 || part == 4, FRNNT_EINVAL,
+                "part must be 0 (planes of g), 1 (grad-input product), 3 (grad-weight product) or 4 (input gradients)");
+  return pjl_backward(px_grad, py_grad, ranges, symbols, boundary, saved, scratch, enc_grad, dec_grad, weight_grad,
+                      bias_grad, B, T, R, S, C, D, blank, rnnt_type, stream, 1u << part);
 }
 
 // ---- plain products on planes ---------------------------------------------------------------------
@@ -734,7 +811,7 @@ extern "C" int frnnt_pair_matmul_nt(const void *a_hi, const void *a_lo, const vo
   if (rc != FRNNT_OK) return rc;
   const LinShape shape{M, N, K, ((K + kPairBK - 1) / kPairBK) * kPairBK, (M + kPairTile - 1) / kPairTile,
                        (N + kPairTile - 1) / kPairTile, 1};
-  return launch_pair_umma<false, false>(mah, mal, mbh, mbl, d, shape,
+  return launch_pair<false, false>(mah, mal, mbh, mbl, d, shape,
                                         PlainPairExt{bias, inv_scale_a, inv_scale_b, N}, (cudaStream_t)stream);
 }
 
@@ -764,7 +841,7 @@ extern "C" int frnnt_pair_matmul_tn(const void *a_hi, const void *a_lo, const vo
                        (N + kPairTile - 1) / kPairTile, splits};
   cudaStream_t st = (cudaStream_t)stream;
   float *out = splits == 1 ? d : partials;
-  rc = launch_pair_umma<true, true>(mah, mal, mbh, mbl, out, shape,
+  rc = launch_pair<true, true>(mah, mal, mbh, mbl, out, shape,
                                     PlainPairExt{nullptr, inv_scale_a, inv_scale_b, N}, st);
   if (rc != FRNNT_OK) return rc;
   if (splits > 1) {

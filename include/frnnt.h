@@ -328,6 +328,26 @@ int frnnt_pruned_joiner_logprobs_backward(const float *px_grad, const float *py_
                                           float *bias_grad, int B, int T, int R, int S, int C, int D,
                                           int blank, int rnnt_type, void *stream);
 
+/* Diagnostics (for per-kernel timing; no counterpart in the reference): the same arguments
+ * as the two calls above, but only ONE part of the call is launched, on buffers that a
+ * complete forward (and, for the backward parts, backward) call has filled before.
+ * forward parts: 0 = planes of the weights and of tanh(enc + dec), 1 = the product
+ * (logits + log-sum-exp partials), 2 = bands and lattices.  backward parts: 0 = planes of
+ * d loss / d logits (+ bias gradient), 1 = grad-input product, 3 = grad-weight product,
+ * 4 = enc / dec gradients from the grad-input result. */
+int frnnt_pruned_joiner_logprobs_forward_part(int part, const float *enc, const float *dec,
+                                              const int64_t *ranges, const float *weight,
+                                              const float *bias, const int64_t *symbols,
+                                              const int64_t *boundary, float *px, float *py, void *saved,
+                                              void *scratch, int B, int T, int R, int S, int C, int D,
+                                              int blank, int rnnt_type, void *stream);
+int frnnt_pruned_joiner_logprobs_backward_part(int part, const float *px_grad, const float *py_grad,
+                                               const int64_t *ranges, const int64_t *symbols,
+                                               const int64_t *boundary, void *saved, void *scratch,
+                                               float *enc_grad, float *dec_grad, float *weight_grad,
+                                               float *bias_grad, int B, int T, int R, int S, int C, int D,
+                                               int blank, int rnnt_type, void *stream);
+
 /* ----------------------------------------------------------------------------
  * Products of matrices stored as pairs of fp16 planes (no counterpart in the reference)
  * ------------------------------------------------------------------------- */
