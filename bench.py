@@ -39,8 +39,8 @@ sys.path.insert(0, ROOT)
 from tests import workloads  # noqa: E402  (seeded synthetic inputs)
 
 L2_FLUSH_BYTES = 512 << 20
-# all-reduced loss of the c5 global batch (B=512, seed 0); None until measured
-C5_GLOBAL_LOSS = None
+# all-reduced loss of the c5 global batch (B=512, seed 0), measured on one GPU
+C5_GLOBAL_LOSS = 3130849.5
 
 # DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the kernels
 # the roofline lines name, workload c3, from the ncu captures summarised under profiles/
@@ -562,6 +562,8 @@ def main():
     ap.add_argument("--no-overlap", action="store_true",
                     help="keep the simple loss on the main stream (its backward then queues behind "
                          "the pruned branch's instead of overlapping with it)")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="enqueue every step eagerly instead of replaying a CUDA graph of it")
     ap.add_argument("--no-stages", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -643,9 +645,19 @@ def main():
     from fast_rnnt_b200 import sharding
 
     last_loss = [None]
+    # One CUDA graph per set of input buffers (the resident ones, and the two upload buffers
+    # of the e2e loop), captured at the first call, i.e. during warm-up; they share one pool.
+    graphs, pool = {}, (None if args.no_graph else torch.cuda.graph_pool_handle())
 
-    def step(t):
-        last_loss[0] = sharding.allreduce_loss(inner(t))
+    def step(t, key="resident"):
+        if args.no_graph:
+            loss = inner(t)
+        else:
+            if key not in graphs:
+                from fast_rnnt_b200.graphs import GraphedStep
+                graphs[key] = GraphedStep(inner, t, pool=pool)
+            loss = graphs[key]()
+        last_loss[0] = sharding.allreduce_loss(loss)
         return last_loss[0]
 
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
@@ -680,7 +692,8 @@ def main():
     with ClockSampler(local_rank) as clocks:
         n0 = lib.frnnt_launch_count()
         total_ms = timed(lambda: step(resident), args.steps, args.warmup)
-        launches = (lib.frnnt_launch_count() - n0) // (args.steps + args.warmup)
+        launches = (graphs["resident"].launches if graphs else
+                    (lib.frnnt_launch_count() - n0) // (args.steps + args.warmup))
     ms_per_step = total_ms / args.steps
     value = batch * world / (ms_per_step * 1e-3)
 
@@ -747,12 +760,12 @@ def main():
                 nxt = upload()
             # no L2 flush here: every step works on a fresh 155 MB upload (larger than the
             # 126 MB L2) and moves about 1.5 GB through the cache
-            loss = step(t)
+            loss = step(t, buf)
             loss_host.copy_(loss, non_blocking=True)
             free_ev[buf] = torch.cuda.Event()
             free_ev[buf].record(main_stream)
 
-    e2e_loop(args.warmup)
+    e2e_loop(max(args.warmup, 2))   # at least one step on each upload buffer (graph capture)
     barrier()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
@@ -777,6 +790,10 @@ def main():
             "streams": ("one" if args.no_overlap else
                         "two: the simple loss (forward, hence its backward) on a second stream, "
                         "so that its backward overlaps with the pruned branch's"),
+            "graph": (None if args.no_graph else
+                      "the step (forward + backward, both streams) is captured once per set of input "
+                      "buffers with fast_rnnt_b200.graphs.GraphedStep and replayed; the all-reduce of "
+                      "the loss and the uploads are not in the graph"),
             "clocks": clocks.summary(),
             "e2e": {"value": round(e2e_value, 1), "unit": "utt/s", "h2d_bytes_per_step": int(h2d),
                     "d2h_bytes_per_step": 4, "ms_per_step": round(e2e_ms, 4),

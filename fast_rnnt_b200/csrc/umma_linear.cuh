@@ -32,7 +32,7 @@
 //              adds (tcgen05.ld / add / tcgen05.st), one group behind the MMAs,
 //              and run the epilogue (tcgen05.ld -> policy -> 64-byte row
 //              segments) while the other warps are already on the next item.
-// No multicast, no clusters.  Every wait is bounded; a timeout poisons the tile.
+// One CTA per SM, every load is a plain per-CTA TMA load.  Every wait is bounded; a timeout poisons the tile.
 //
 // Policy interface (all __device__, called with z = batch or split index):
 //   static constexpr bool kBatched;   tensor maps are 3-D, z is their outer coordinate

@@ -31,7 +31,7 @@
 //              sum -- policy, 32x32 boxes staged in shared memory, TMA stores -- while the
 //              other set already folds the next tile: the epilogue has a whole tile's
 //              time and never holds an accumulator.
-// No multicast, no clusters.  Every wait is bounded; a timeout poisons the tile with NaN.
+// One CTA per SM, every load is a plain per-CTA TMA load.  Every wait is bounded; a timeout poisons the tile with NaN.
 //
 // Policy ("Ext") interface, all __device__:
 //   static constexpr bool kBatched;                the work-item index z is a batch index (the

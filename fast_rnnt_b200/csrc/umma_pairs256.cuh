@@ -3,8 +3,8 @@
 // Why: the 128 x 128 kernel is bound by the L2 -> shared-memory feed (64 KB of planes per
 // 64-wide K slice; measured ~48 bytes per clock and SM at best against 83 needed to keep
 // the tensor pipe busy).  A 256 x 128 tile shares every B slice between two row halves:
-// 96 KB per slice for twice the flops, a quarter less traffic per flop, without clusters
-// or multicast.
+// 96 KB per slice for twice the flops, a quarter less traffic per flop, with plain per-CTA
+// loads (no thread-block clusters).
 //
 // What changes against the 128 x 128 kernel:
 //   * a stage holds A hi / lo for both row halves (4 x 16 KB) and B hi / lo (2 x 16 KB);
