@@ -415,26 +415,49 @@ joiner_input_grads_kernel(const float *__restrict__ gz, const int64_t *__restric
   }
 }
 
-// dec_grad[b][s][:] += the chunks' partial rows for s, in chunk order
+// dec_grad[b][s][:] += the chunks' partial rows for s, in chunk order.  Each warp first finds
+// the chunks whose window holds s (lane <-> chunk, one ballot per 32 chunks), then fetches their
+// rows four at a time, so that the loads of a round are in flight together.
 __global__ void __launch_bounds__(kJgThreads)
 joiner_dec_reduce_kernel(const float *__restrict__ partial, const int *__restrict__ window,
                          float *__restrict__ dec_grad, int nch, int S1, int D) {
   const int b = blockIdx.y, s = blockIdx.x;
-  const int dvec = D / 4;
+  const int dvec = D / 4, lane = threadIdx.x & 31;
   const int *win = window + (size_t)b * nch * 2;
+  const float4 *P = reinterpret_cast<const float4 *>(partial) + (size_t)b * nch * kJgWindow * dvec;
   float4 *out = reinterpret_cast<float4 *>(dec_grad) + ((size_t)b * S1 + s) * dvec;
-  for (int v = threadIdx.x; v < dvec; v += kJgThreads) {
+  // whole warps walk the columns together (the ballots and shuffles below need all lanes)
+  for (int v0 = (threadIdx.x & ~31); v0 < dvec; v0 += kJgThreads) {
+    const int v = v0 + lane;
+    const bool col = v < dvec;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int ch = 0; ch < nch; ++ch) {
-      const int lo = win[2 * ch], n = win[2 * ch + 1];
-      if (s >= lo && s < lo + n) {
-        const float4 x = reinterpret_cast<const float4 *>(partial)[(((size_t)b * nch + ch) * kJgWindow + (s - lo)) * dvec + v];
-        acc.x += x.x, acc.y += x.y, acc.z += x.z, acc.w += x.w;
+    for (int base = 0; base < nch; base += 32) {
+      const int ch = base + lane;
+      const int lo = ch < nch ? win[2 * ch] : 0, n = ch < nch ? win[2 * ch + 1] : 0;
+      unsigned mask = __ballot_sync(0xffffffffu, s >= lo && s < lo + n);
+      while (mask) {
+        float4 x[4];
+        int cnt = 0;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (mask) {
+            const int bit = __ffs(mask) - 1;
+            mask &= mask - 1;
+            const int row = s - __shfl_sync(0xffffffffu, lo, bit);
+            if (col) x[u] = P[((size_t)(base + bit) * kJgWindow + row) * dvec + v];
+            cnt = u + 1;
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (u < cnt && col) acc.x += x[u].x, acc.y += x[u].y, acc.z += x[u].z, acc.w += x[u].w;
       }
     }
-    float4 o = out[v];
-    o.x += acc.x, o.y += acc.y, o.z += acc.z, o.w += acc.w;
-    out[v] = o;
+    if (col) {
+      float4 o = out[v];
+      o.x += acc.x, o.y += acc.y, o.z += acc.z, o.w += acc.w;
+      out[v] = o;
+    }
   }
 }
 
