@@ -48,8 +48,8 @@ C5_GLOBAL_LOSS = 3130849.5
 NCU_TRAFFIC_C3 = {
     # profiles/kernels_c3_half_batch_ncu_full.txt: captured at half batch, doubled (every kernel
     # streams its operands once, so its traffic grows with the number of rows)
-    "fused_fwd_product": 2 * 277.0e6, "fused_bwd_grad_input": 2 * 461.8e6,
-    "fused_bwd_grad_weight": 2 * 331.5e6,
+    "fused_fwd_product": 2 * 279.0e6, "fused_bwd_grad_input": 2 * 462.3e6,
+    "fused_bwd_grad_weight": 2 * 334.7e6,
     "mi_forward": 2 * 8.3e6, "mi_backward": 2 * 5.9e6, "mi_forward_pruned": 2 * 8.3e6,
     "mi_backward_pruned": 2 * 5.9e6,
 }
