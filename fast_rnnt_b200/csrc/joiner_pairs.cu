@@ -230,11 +230,13 @@ pruned_tanh_pairs_kernel(const float *__restrict__ enc, const float *__restrict_
       const float4 x0 = e[2 * v], x1 = e[2 * v + 1], y0 = d[2 * v], y1 = d[2 * v + 1];
       const float a[8] = {x0.x + y0.x, x0.y + y0.y, x0.z + y0.z, x0.w + y0.w,
                           x1.x + y1.x, x1.y + y1.y, x1.z + y1.z, x1.w + y1.w};
-      __align__(16) __half hi[8], lo[8];
-#pragma unroll
-      for (int c = 0; c < 8; ++c) fp16_pair(tanhf(a[c]), kActScale, hi[c], lo[c]);
-      oh[v] = *reinterpret_cast<const uint4 *>(hi);
-      ol[v] = *reinterpret_cast<const uint4 *>(lo);
+      const float t0[4] = {tanhf(a[0]), tanhf(a[1]), tanhf(a[2]), tanhf(a[3])};
+      const float t1[4] = {tanhf(a[4]), tanhf(a[5]), tanhf(a[6]), tanhf(a[7])};
+      uint2 h0, l0, h1, l1;
+      fp16_pair4(t0, kActScale, h0, l0);
+      fp16_pair4(t1, kActScale, h1, l1);
+      oh[v] = make_uint4(h0.x, h0.y, h1.x, h1.y);
+      ol[v] = make_uint4(l0.x, l0.y, l1.x, l1.y);
     }
   }
 }
@@ -476,17 +478,17 @@ lsm_backward_pairs_kernel(const float *__restrict__ logits, const float4 *__rest
       const float neg = -(gx + gy);
       const float x[4] = {q[u].x, q[u].y, q[u].z, q[u].w};
       float g[4];
-      __align__(8) __half hi[4], lo[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         float gg = neg * __expf(x[e] - l);
         if (c0 + e == y) gg += gx;
         if (c0 + e == blank) gg += gy;
         g[e] = gg;
-        fp16_pair(gg, scale, hi[e], lo[e]);
       }
-      reinterpret_cast<uint2 *>(g_hi + (size_t)(row + u) * Cp)[v] = *reinterpret_cast<const uint2 *>(hi);
-      reinterpret_cast<uint2 *>(g_lo + (size_t)(row + u) * Cp)[v] = *reinterpret_cast<const uint2 *>(lo);
+      uint2 hi, lo;
+      fp16_pair4(g, scale, hi, lo);
+      reinterpret_cast<uint2 *>(g_hi + (size_t)(row + u) * Cp)[v] = hi;
+      reinterpret_cast<uint2 *>(g_lo + (size_t)(row + u) * Cp)[v] = lo;
       acc.x += g[0], acc.y += g[1], acc.z += g[2], acc.w += g[3];
     }
   }

@@ -107,14 +107,12 @@ exp_planes_kernel(const float *__restrict__ lm, const float *__restrict__ am,
     float sum = 0.f;
     auto one = [&](int v, const float4 &q) {
       const float e[4] = {expf(q.x - m), expf(q.y - m), expf(q.z - m), expf(q.w - m)};
-      __align__(8) __half hi[4], lo[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        sum += e[i];
-        fp16_pair(e[i], kExpScale, hi[i], lo[i]);
-      }
-      dh[v] = *reinterpret_cast<const uint2 *>(hi);
-      dl[v] = *reinterpret_cast<const uint2 *>(lo);
+      for (int i = 0; i < 4; ++i) sum += e[i];
+      uint2 hi, lo;
+      fp16_pair4(e, kExpScale, hi, lo);
+      dh[v] = hi;
+      dl[v] = lo;
     };
 #pragma unroll
     for (int j = 0; j < 4; ++j) {

@@ -87,6 +87,24 @@ __device__ __forceinline__ void fp16_pair(float x, float scale, __half &hi, __ha
   lo = __float2half_rn(xs - __half2float(hi));
 }
 
+// two values at once, same results: the conversions to fp16 are packed (one instruction per
+// pair instead of one per value; the unpacked conversion shares the special-function pipe,
+// a quarter of the issue rate, with exp and tanh)
+__device__ __forceinline__ void fp16_pair2(float x0, float x1, float scale, __half2 &hi, __half2 &lo) {
+  const float a = x0 * scale, b = x1 * scale;
+  hi = __floats2half2_rn(a, b);
+  const float2 h = __half22float2(hi);
+  lo = __floats2half2_rn(a - h.x, b - h.y);
+}
+// four values -> the 8 bytes of each plane
+__device__ __forceinline__ void fp16_pair4(const float (&x)[4], float scale, uint2 &hi, uint2 &lo) {
+  __half2 h0, l0, h1, l1;
+  fp16_pair2(x[0], x[1], scale, h0, l0);
+  fp16_pair2(x[2], x[3], scale, h1, l1);
+  hi = make_uint2(*reinterpret_cast<const uint32_t *>(&h0), *reinterpret_cast<const uint32_t *>(&h1));
+  lo = make_uint2(*reinterpret_cast<const uint32_t *>(&l0), *reinterpret_cast<const uint32_t *>(&l1));
+}
+
 // power-of-two scale that brings a largest magnitude `amax` into [2^14, 2^15); 1 when
 // amax is zero or not finite (then the data decides the result anyway)
 __device__ __forceinline__ float fp16_pair_scale(float amax) {
