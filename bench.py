@@ -797,9 +797,12 @@ def main():
             "clocks": clocks.summary(),
             "e2e": {"value": round(e2e_value, 1), "unit": "utt/s", "h2d_bytes_per_step": int(h2d),
                     "d2h_bytes_per_step": 4, "ms_per_step": round(e2e_ms, 4),
+                    "h2d_gbs_per_rank": round(h2d / (e2e_ms * 1e-3) / 1e9, 1),
                     "note": "uploads every input of the step, reads back the loss; the input "
                             "gradients (about as many bytes as the inputs) stay on the device, "
-                            "where a training step consumes them"},
+                            "where a training step consumes them.  When ms_per_step here exceeds "
+                            "the device-resident one, the step is bound by the upload "
+                            "(h2d_gbs_per_rank against the host link's rate)"},
             "gpu_launches": int(launches),
             "loss_allreduced": float(last_loss[0]) if last_loss[0] is not None else None}
     if args.workload == "c5" and args.batch is None and C5_GLOBAL_LOSS is not None:
