@@ -41,12 +41,13 @@ enum { kScaleAct = 0, kScaleW = 1, kScaleG = 2 };  // slots of the inverse scale
 
 static inline size_t up256(size_t x) { return (x + 255) & ~(size_t)255; }
 
-// rows of an output tile.  The 256 x 128 kernel (umma_pairs256.cuh) moves a quarter fewer
-// bytes per flop, but its eight warps do both folding and epilogue; measured at C3 it wins
-// where the epilogue is trivial and the reduction long (grad-weight, plain products:
-// 0.235 -> 0.21 ms) and loses where the epilogue carries the log-sum-exp partials or the
-// tanh' activations (fused forward 0.41 -> 0.43 ms, backward 0.78 -> 0.88 ms), so only the
-// former use it.  FRNNT_PAIR_TILE=128 forces the 128 x 128 kernel everywhere.
+// rows of an output tile.  The large-tile kernel (umma_pairs256.cuh: 256 x 128, or 128 x 256
+// where the output is wider than 128 columns) moves a quarter fewer bytes per flop, but its
+// eight warps do both folding and epilogue with the running sums in registers; measured at C3
+// it wins where the epilogue is trivial and the reduction long (grad-weight, plain products:
+// 0.235 -> 0.21 -> 0.20 ms) and loses where the epilogue carries the log-sum-exp partials or the
+// tanh' activations (forward product 0.254 -> 0.260 ms, grad-input 0.28 -> 0.39 ms with 128 x 256),
+// so only the former use it.  FRNNT_PAIR_TILE=128 forces the 128 x 128 kernel everywhere.
 static int pair_tile_m(int M, bool light_epilogue) {
   static int forced = -1;
   if (forced < 0) {
@@ -60,6 +61,12 @@ template <bool A_MN, bool B_MN, class Ext>
 static int launch_pair(const CUtensorMap &mah, const CUtensorMap &mal, const CUtensorMap &mbh,
                        const CUtensorMap &mbl, float *out, LinShape shape, const Ext &ext, cudaStream_t st) {
   const int tm = pair_tile_m(shape.M, Ext::kLightEpilogue);
+  if (Ext::kLightEpilogue && shape.N > kPairTile && pair_tile_m(2 * kPairTile, true) != kPairTile) {
+    // 128 x 256: one MMA of N = 256 per product and step (grad-weight at C3: 0.212 -> 0.201 ms)
+    shape.tiles_m = (shape.M + kPairTile - 1) / kPairTile;
+    shape.tiles_n = (shape.N + 2 * kPairTile - 1) / (2 * kPairTile);
+    return launch_pair_umma256<A_MN, B_MN, Ext, true>(mah, mal, mbh, mbl, out, shape, ext, st);
+  }
   shape.tiles_m = (shape.M + tm - 1) / tm;
   if (tm == kP2TileM) return launch_pair_umma256<A_MN, B_MN>(mah, mal, mbh, mbl, out, shape, ext, st);
   return launch_pair_umma<A_MN, B_MN>(mah, mal, mbh, mbl, out, shape, ext, st);

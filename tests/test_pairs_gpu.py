@@ -34,10 +34,11 @@ def bound(a, b):
     return 2e-6 * float((a.abs().double() @ b.abs().double().t()).max())
 
 
-# M, N, K: one tile; ragged edges; several row tiles per CTA (pairs of 128-row tiles too),
-# odd numbers of row tiles, several K groups
-NT_SHAPES = [(128, 128, 64), (100, 72, 200), (700, 136, 96), (2048, 512, 512), (1300, 260, 328),
-             (40000, 500, 512)]
+# M, N, K: one tile; ragged edges; several row tiles per CTA, odd numbers of row tiles, several
+# K groups.  Outputs wider than 128 columns run on 128 x 256 tiles, narrower ones with more
+# than 128 rows on 256 x 128 tiles, the rest on 128 x 128 tiles.
+NT_SHAPES = [(128, 128, 64), (100, 72, 200), (700, 136, 96), (600, 128, 200), (2048, 512, 512),
+             (1300, 260, 328), (40000, 500, 512)]
 
 
 @pytest.mark.parametrize("M,N,K", NT_SHAPES)
@@ -70,7 +71,7 @@ def test_pair_matmul_nt(M, N, K, with_bias):
 
 
 # M, N, R: out [M][N] = a^T b over R rows (split over the CTAs when R is long)
-TN_SHAPES = [(128, 128, 64), (72, 200, 1000), (500, 512, 40000), (264, 136, 5000)]
+TN_SHAPES = [(128, 128, 64), (72, 200, 1000), (500, 512, 40000), (264, 136, 5000), (300, 100, 3000)]
 
 
 @pytest.mark.parametrize("M,N,R", TN_SHAPES)
