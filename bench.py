@@ -24,6 +24,7 @@ __graft_entry__.build() where a checkout exists), or, where that install is abse
 the CPU oracle port of the same algorithm.
 """
 import argparse
+import ctypes
 import json
 import os
 import statistics
@@ -451,7 +452,7 @@ def stage_table(fr, wl, dev, flush, hbm_gbs):
         _lib.call("frnnt_pruned_joiner_logprobs_forward", _lib.ptr(t["enc"]), _lib.ptr(t["dec"]),
                   _lib.ptr(ranges), _lib.ptr(W), _lib.ptr(t["joiner_b"]), _lib.ptr(sym), _lib.ptr(bnd),
                   _lib.ptr(ppxd), _lib.ptr(ppyd), _lib.ptr(pj_saved), _lib.ptr(pj_fs), B, T, R, S, C, D,
-                  0, 0, sp)
+                  0, 0, ctypes.c_double(0.0), sp)
 
     def pj_bwd():
         _lib.call("frnnt_pruned_joiner_logprobs_backward", _lib.ptr(gpx), _lib.ptr(gpy), _lib.ptr(ranges),

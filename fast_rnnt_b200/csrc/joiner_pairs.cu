@@ -590,7 +590,7 @@ enum { kPartPlanes = 1, kPartProduct = 2, kPartRest = 4, kPartProduct2 = 8, kPar
 static int pjl_forward(const float *enc, const float *dec, const int64_t *ranges, const float *weight,
                        const float *bias, const int64_t *symbols, const int64_t *boundary, float *px,
                        float *py, void *saved, void *scratch, int B, int T, int R, int S, int C, int D,
-                       int blank, int rnnt_type, void *stream, unsigned parts) {
+                       int blank, int rnnt_type, double delay_penalty, void *stream, unsigned parts) {
   int rc = pjl_check(B, T, R, S, C, D, blank, rnnt_type);
   if (rc != FRNNT_OK) return rc;
   if (B == 0 || T == 0) return FRNNT_OK;
@@ -643,7 +643,7 @@ static int pjl_forward(const float *enc, const float *dec, const int64_t *ranges
         logits, stats, symbols, ranges, lse, pxb, pyb, rows, T, R, S, C, blank, L.tiles_n));
     dim3 grid2((unsigned)((T + 1 + 127) / 128), (unsigned)(S + 1), (unsigned)B);
     FRNNT_KERNEL(band_to_lattice_kernel<float><<<grid2, 128, 0, st>>>(pxb, pyb, ranges, boundary, px, py, S, T, R,
-                                                                     rnnt_type));
+                                                                     rnnt_type, delay_penalty));
     FRNNT_CUDA(cudaGetLastError());
   }
   return FRNNT_OK;
@@ -655,9 +655,9 @@ extern "C" int frnnt_pruned_joiner_logprobs_forward(const float *enc, const floa
                                                     const int64_t *boundary, float *px, float *py,
                                                     void *saved, void *scratch, int B, int T, int R,
                                                     int S, int C, int D, int blank, int rnnt_type,
-                                                    void *stream) {
+                                                    double delay_penalty, void *stream) {
   return pjl_forward(enc, dec, ranges, weight, bias, symbols, boundary, px, py, saved, scratch, B, T, R, S, C, D,
-                     blank, rnnt_type, stream, ~0u);
+                     blank, rnnt_type, delay_penalty, stream, ~0u);
 }
 
 extern "C" int frnnt_pruned_joiner_logprobs_forward_part(int part, const float *enc, const float *dec,
@@ -669,7 +669,7 @@ extern "C" int frnnt_pruned_joiner_logprobs_forward_part(int part, const float *
                                                          void *stream) {
   FRNNT_REQUIRE(part >= 0 && part <= 2, FRNNT_EINVAL, "part must be 0 (planes), 1 (product) or 2 (lattices)");
   return pjl_forward(enc, dec, ranges, weight, bias, symbols, boundary, px, py, saved, scratch, B, T, R, S, C, D,
-                     blank, rnnt_type, stream, 1u << part);
+                     blank, rnnt_type, 0.0, stream, 1u << part);
 }
 
 static int pjl_backward(const float *px_grad, const float *py_grad, const int64_t *ranges,

@@ -197,7 +197,7 @@ template <typename real>
 static int lsm_forward_impl(const void *logits, const int64_t *symbols, const int64_t *ranges,
                             const int64_t *boundary, void *lse, void *pxb, void *pyb, void *px,
                             void *py, int B, int T, int R, int S, int C, int blank, int rnnt_type,
-                            cudaStream_t st) {
+                            double delay_penalty, cudaStream_t st) {
   constexpr int VWMAX = sizeof(real) == 4 ? 4 : 2;
   const long long rows = (long long)B * T * R;
   const bool vec_ok = (C % VWMAX == 0) && ((uintptr_t)logits % 16 == 0);
@@ -240,7 +240,7 @@ static int lsm_forward_impl(const void *logits, const int64_t *symbols, const in
     dim3 grid2((unsigned)((T + 1 + 127) / 128), (unsigned)(S + 1), (unsigned)B);
     FRNNT_KERNEL(band_to_lattice_kernel<real><<<grid2, 128, 0, st>>>((const real *)pxb, (const real *)pyb,
                                                        ranges, boundary, (real *)px, (real *)py,
-                                                       S, T, R, rnnt_type));
+                                                       S, T, R, rnnt_type, delay_penalty));
     FRNNT_CUDA(cudaGetLastError());
   }
   return FRNNT_OK;
@@ -289,7 +289,7 @@ extern "C" int frnnt_lsm_gather_forward(int dtype, const void *logits, const int
                                         const int64_t *ranges, const int64_t *boundary,
                                         void *lse, void *px_band, void *py_band, void *px,
                                         void *py, int B, int T, int R, int S, int C, int blank,
-                                        int rnnt_type, void *stream) {
+                                        int rnnt_type, double delay_penalty, void *stream) {
   int rc = lsm_check(dtype, B, T, R, S, C, blank, rnnt_type);
   if (rc != FRNNT_OK) return rc;
   if (B == 0 || T == 0) return FRNNT_OK;
@@ -300,9 +300,9 @@ extern "C" int frnnt_lsm_gather_forward(int dtype, const void *logits, const int
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == FRNNT_F32)
     return lsm_forward_impl<float>(logits, symbols, ranges, boundary, lse, px_band, py_band, px,
-                                   py, B, T, R, S, C, blank, rnnt_type, st);
+                                   py, B, T, R, S, C, blank, rnnt_type, delay_penalty, st);
   return lsm_forward_impl<double>(logits, symbols, ranges, boundary, lse, px_band, py_band, px, py,
-                                  B, T, R, S, C, blank, rnnt_type, st);
+                                  B, T, R, S, C, blank, rnnt_type, delay_penalty, st);
 }
 
 extern "C" int frnnt_lsm_gather_backward(int dtype, const void *logits, const int64_t *symbols,

@@ -26,13 +26,33 @@ __device__ __forceinline__ int band_symbol(const int64_t *symbols, const int64_t
   return (int)y;
 }
 
+// Delay penalty of the reference's loss functions (rnnt_loss.py:309-324 and its three copies):
+// px[b][s][t] += delay_penalty * ((T_b - 1) / 2 - t), with the roundings torch makes there --
+// with a boundary tensor the offset (an integer tensor divided by 2) and hence the whole
+// penalty are float32 whatever px's type is; without one they have px's type; the product is
+// rounded before it is added.  Zero when delay_penalty is not positive.
+template <typename real>
+__device__ __forceinline__ real delay_penalty_at(const int64_t *boundary, int b, int T, int t, double dp) {
+  if (!(dp > 0.0)) return (real)0;
+  if (boundary != nullptr) {
+    const float off = (float)(boundary[4 * b + 3] - 1) / 2.0f;
+    return (real)__fmul_rn(off - (float)t, (float)dp);
+  }
+  if (sizeof(real) == 4) return (real)__fmul_rn((float)(T - 1) / 2.0f - (float)t, (float)dp);
+  return (real)__dmul_rn((double)(T - 1) / 2.0 - (double)t, dp);
+}
+__device__ __forceinline__ float add_rn(float a, float b) { return __fadd_rn(a, b); }
+__device__ __forceinline__ double add_rn(double a, double b) { return __dadd_rn(a, b); }
+
 // bands -> lattices: row (ranges[b][t][0] + k) mod (S+1), -inf elsewhere, the -inf column
-// at t = T (regular), the -inf at t = t_end (regular + boundary), px += py[s+1] (constrained)
+// at t = T (regular), the -inf at t = t_end (regular + boundary), px += py[s+1] (constrained),
+// the delay penalty on px
 template <typename real>
 __global__ void band_to_lattice_kernel(const real *__restrict__ pxb, const real *__restrict__ pyb,
                                        const int64_t *__restrict__ ranges,
                                        const int64_t *__restrict__ boundary, real *__restrict__ px,
-                                       real *__restrict__ py, int S, int T, int R, int rnnt_type) {
+                                       real *__restrict__ py, int S, int T, int R, int rnnt_type,
+                                       double delay_penalty = 0.0) {
   const int b = blockIdx.z, s = blockIdx.y;
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   const int S1 = S + 1;
@@ -66,6 +86,7 @@ __global__ void band_to_lattice_kernel(const real *__restrict__ pxb, const real 
     } else if (rnnt_type == FRNNT_CONSTRAINED) {
       vx = vx + vy_next;
     }
+    if (delay_penalty > 0.0) vx = add_rn(vx, delay_penalty_at<real>(boundary, b, T, t, delay_penalty));
     px[((size_t)b * S + s) * T1 + t] = vx;
   }
 }

@@ -23,6 +23,7 @@
 #include <string.h>
 
 #include "common.cuh"
+#include "lsm_band.cuh"
 #include "simple_pairs.cuh"
 
 namespace frnnt {
@@ -355,6 +356,7 @@ struct SmoothCfg {
   // normalizer) are not worth that
   int am_only_off;
   double both, ls, as;  // 1-l-a, lm-only scale, am-only scale (zero lm scale replaced by 1e-20)
+  double delay_penalty = 0.0;  // added to px by the lattice-writing kernels when positive
 };
 
 template <typename real>
@@ -418,6 +420,7 @@ __global__ void assemble_kernel(const real *__restrict__ lm, const real *__restr
     } else if (rnnt_type == FRNNT_CONSTRAINED) {
       v += py_at(s + 1);
     }
+    if (cfg.delay_penalty > 0.0) v = add_rn(v, delay_penalty_at<real>(boundary, b, T, t, cfg.delay_penalty));
     px[((size_t)b * S + s) * T1 + t] = v;
   }
 }
@@ -738,7 +741,7 @@ static int simple_forward_impl(const void *lm_, const void *am_, const int64_t *
                                           rnnt_type, cfg.smoothed, cfg.am_only_off, (float)cfg.both,
                                           (float)cfg.ls, (float)cfg.as, (float *)px, (float *)py, (float *)norm,
                                           (float *)lmmax, (float *)lmsum, (float *)ammax, (const float *)amonly,
-                                          (const float *)loguni, pairs_saved, B, S, T, C, 0, st);
+                                          (const float *)loguni, pairs_saved, B, S, T, C, 0, st, cfg.delay_penalty);
     if (rc0 != FRNNT_OK) return rc0;
   } else {
     FRNNT_KERNEL(row_stats_kernel<real><<<warps_grid(lm_rows), 256, 0, st>>>(lm, lmmax, lmsum, lm_rows, C));
@@ -761,7 +764,7 @@ static int simple_forward_impl(const void *lm_, const void *am_, const int64_t *
                                        rnnt_type, cfg.smoothed, cfg.am_only_off, (float)cfg.both,
                                        (float)cfg.ls, (float)cfg.as, (float *)px, (float *)py, (float *)norm,
                                        (float *)lmmax, (float *)lmsum, (float *)ammax, (const float *)amonly,
-                                       (const float *)loguni, pairs_saved, B, S, T, C, 1, st);
+                                       (const float *)loguni, pairs_saved, B, S, T, C, 1, st, cfg.delay_penalty);
   if (use_tensor_cores<real>(lm, am, S1, T, C)) {
     rc = launch_norm_umma((const float *)lm, (const float *)am, (const float *)lmmax,
                           (const float *)ammax, (float *)norm, B, S1, T, C, st);
@@ -898,9 +901,9 @@ extern "C" size_t frnnt_simple_scratch_bytes(int dtype, int B, int S, int T, int
 extern "C" int frnnt_simple_logprobs_forward(int dtype, const void *lm, const void *am,
                                              const int64_t *symbols, const int64_t *boundary,
                                              int blank, int rnnt_type, int smoothed,
-                                             double lm_only_scale, double am_only_scale, void *px,
-                                             void *py, void *saved, void *scratch, int B, int S,
-                                             int T, int C, void *stream) {
+                                             double lm_only_scale, double am_only_scale,
+                                             double delay_penalty, void *px, void *py, void *saved,
+                                             void *scratch, int B, int S, int T, int C, void *stream) {
   int rc = simple_check(dtype, B, S, T, C, blank, rnnt_type);
   if (rc != FRNNT_OK) return rc;
   if (B == 0) return FRNNT_OK;
@@ -908,6 +911,7 @@ extern "C" int frnnt_simple_logprobs_forward(int dtype, const void *lm, const vo
                     scratch,
                 FRNNT_EINVAL, "NULL argument");
   SmoothCfg cfg = make_cfg(smoothed, lm_only_scale, am_only_scale);
+  cfg.delay_penalty = delay_penalty > 0.0 ? delay_penalty : 0.0;
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == FRNNT_F32)
     return simple_forward_impl<float>(lm, am, symbols, boundary, blank, rnnt_type, cfg, px, py,

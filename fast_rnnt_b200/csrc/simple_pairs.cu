@@ -17,6 +17,7 @@
 //             run on the same engine, L and A read back from the planes in the epilogue.
 #include <cuda_fp16.h>
 
+#include "lsm_band.cuh"
 #include "simple_pairs.cuh"
 #include "umma_pairs.cuh"
 
@@ -172,8 +173,9 @@ struct NormPairExt {
   int smoothed, am_only_off;
   float both, ls, as;
   int Sp;
+  double delay_penalty;
   struct Row {
-    float ammax_t, am_blk_t, amonly_t, py_next;
+    float ammax_t, am_blk_t, amonly_t, py_next, pen;
     const float *amrow;
     long long t_end;
   };
@@ -185,6 +187,7 @@ struct NormPairExt {
     r.amrow = am_sym + bt * Sp;
     r.t_end = (rnnt_type == FRNNT_REGULAR && boundary != nullptr) ? (long long)boundary[4 * b + 3] : -1;
     r.py_next = 0.f;
+    r.pen = delay_penalty_at<float>(boundary, b, T, t, delay_penalty);
   }
   __device__ void prefetch(Row &, int, int, int) const {}
   __device__ void finish(Row &, int, int, int, float (&)[16], int) const {}
@@ -265,6 +268,7 @@ struct NormPairExt {
         } else if (rnnt_type == FRNNT_CONSTRAINED) {
           v += r.py_next;
         }
+        if (delay_penalty > 0.0) v = __fadd_rn(v, r.pen);
         *xrow = v;
       }
       r.py_next = vy;
@@ -400,7 +404,7 @@ int launch_simple_forward_pairs(const float *lm, const float *am, const int64_t 
                                 int am_only_off, float both, float ls, float as, float *px, float *py,
                                 float *norm, float *lmmax, float *lmsum, float *ammax,
                                 const float *amonly, const float *loguni, void *pairs_saved, int B, int S,
-                                int T, int C, int stage, cudaStream_t st) {
+                                int T, int C, int stage, cudaStream_t st, double delay_penalty) {
   const SimplePairsLayout L(B, S, T, C);
   uint8_t *sv = (uint8_t *)pairs_saved;
   __half *lp_hi = (__half *)(sv + L.lp_hi), *lp_lo = (__half *)(sv + L.lp_lo);
@@ -429,7 +433,7 @@ int launch_simple_forward_pairs(const float *lm, const float *am, const int64_t 
                        (S1 + kPairTile - 1) / kPairTile, B};
   const NormPairExt ext{norm,   px,     py,     am_sym, symbols, boundary, lmmax,    ammax,       lm_blk, lm_sym,
                         lnorm,  am_blk, amonly, loguni, S,       T,        C,        blank,       rnnt_type,
-                        smoothed, am_only_off, both, ls, as, L.Sp};
+                        smoothed, am_only_off, both, ls, as, L.Sp, delay_penalty};
   // the policy stores the lattices itself; the engine's output map is unused and is made
   // over the normalizer buffer only because it has to be a valid map
   return launch_pair_umma<false, false>(mah, mal, mbh, mbl, norm, shape, ext, st);

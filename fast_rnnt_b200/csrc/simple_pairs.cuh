@@ -24,13 +24,14 @@ size_t simple_pairs_rowmax_offset(int B, int S, int T, int C);
 bool simple_pairs_supported(const void *lm, const void *am, int S1, int T, int C, int rnnt_type);
 
 // stage 0: row maxima / sums, exp planes, per-row scalars, the -inf column of px;
-// stage 1: normalizer product + lattices (needs amonly / loguni when the am-only branch is on)
+// stage 1: normalizer product + lattices (needs amonly / loguni when the am-only branch is on;
+// a positive delay_penalty is added to px as the reference's loss functions do)
 int launch_simple_forward_pairs(const float *lm, const float *am, const int64_t *symbols,
                                 const int64_t *boundary, int blank, int rnnt_type, int smoothed,
                                 int am_only_off, float both, float ls, float as, float *px, float *py,
                                 float *norm, float *lmmax, float *lmsum, float *ammax,
                                 const float *amonly, const float *loguni, void *pairs_saved, int B, int S,
-                                int T, int C, int stage, cudaStream_t st);
+                                int T, int C, int stage, cudaStream_t st, double delay_penalty = 0.0);
 
 // lm_grad / am_grad without the one-hot terms, from the gradient weights rw [B][S+1][Tp] and
 // the maxima of |rw| per row (see simple_pairs_rowmax_offset)

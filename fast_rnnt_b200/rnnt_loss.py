@@ -58,7 +58,7 @@ def fix_for_boundary(px: Tensor, boundary: Optional[Tensor] = None) -> Tensor:
 # ------------------------------------------------------------------------------
 class _SimpleLogprobs(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, lm, am, symbols, boundary, blank, rnnt_type, smoothed, ls, as_):
+    def forward(ctx, lm, am, symbols, boundary, blank, rnnt_type, smoothed, ls, as_, delay_penalty=0.0):
         B, T, C = am.shape
         S = lm.shape[1] - 1
         dev, dt = lm.device, _lib.dtype_code(lm.dtype)
@@ -71,8 +71,8 @@ class _SimpleLogprobs(torch.autograd.Function):
             scratch = _bytes(_lib.lib().frnnt_simple_scratch_bytes(dt, B, S, T, C), dev)
             _lib.call("frnnt_simple_logprobs_forward", _c_int(dt), _lib.ptr(lm), _lib.ptr(am),
                       _lib.ptr(symbols), _lib.ptr(boundary), blank, rnnt_type, int(smoothed),
-                      _c_f64(ls), _c_f64(as_), _lib.ptr(px), _lib.ptr(py), _lib.ptr(saved),
-                      _lib.ptr(scratch), B, S, T, C, _lib.stream_ptr(dev))
+                      _c_f64(ls), _c_f64(as_), _c_f64(delay_penalty), _lib.ptr(px), _lib.ptr(py),
+                      _lib.ptr(saved), _lib.ptr(scratch), B, S, T, C, _lib.stream_ptr(dev))
         ctx.save_for_backward(lm, am, symbols, boundary, saved)
         ctx.cfg = (blank, rnnt_type, int(smoothed), ls, as_)
         return px, py
@@ -98,11 +98,11 @@ class _SimpleLogprobs(torch.autograd.Function):
                       _c_f64(ls), _c_f64(as_), _lib.ptr(g_px), _lib.ptr(g_py), _lib.ptr(saved),
                       _lib.ptr(scratch), _lib.ptr(lm_grad), _lib.ptr(am_grad), B, S, T, C,
                       _lib.stream_ptr(dev))
-        return lm_grad, am_grad, None, None, None, None, None, None, None
+        return lm_grad, am_grad, None, None, None, None, None, None, None, None
 
 
 def _simple_logprobs(lm, am, symbols, termination_symbol, rnnt_type, boundary, smoothed,
-                     lm_only_scale=0.0, am_only_scale=0.0):
+                     lm_only_scale=0.0, am_only_scale=0.0, delay_penalty=0.0):
     assert lm.ndim == 3, lm.ndim
     assert am.ndim == 3, am.ndim
     assert lm.shape[0] == am.shape[0], (lm.shape[0], am.shape[0])
@@ -115,7 +115,7 @@ def _simple_logprobs(lm, am, symbols, termination_symbol, rnnt_type, boundary, s
     assert rnnt_type in ["regular", "modified", "constrained"], rnnt_type
     return _SimpleLogprobs.apply(lm, am, symbols, boundary, int(termination_symbol),
                                  _RNNT_TYPES[rnnt_type], smoothed, float(lm_only_scale),
-                                 float(am_only_scale))
+                                 float(am_only_scale), float(delay_penalty))
 
 
 def get_rnnt_logprobs(lm: Tensor, am: Tensor, symbols: Tensor, termination_symbol: int,
@@ -142,7 +142,7 @@ def get_rnnt_logprobs_smoothed(lm: Tensor, am: Tensor, symbols: Tensor, terminat
 # ------------------------------------------------------------------------------
 class _LsmGather(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, logits, symbols, ranges, boundary, blank, rnnt_type):
+    def forward(ctx, logits, symbols, ranges, boundary, blank, rnnt_type, delay_penalty=0.0):
         B, T, R, C = logits.shape
         S = symbols.shape[1]
         dev, dt = logits.device, _lib.dtype_code(logits.dtype)
@@ -156,7 +156,7 @@ class _LsmGather(torch.autograd.Function):
             _lib.call("frnnt_lsm_gather_forward", _c_int(dt), _lib.ptr(logits), _lib.ptr(symbols),
                       _lib.ptr(ranges), _lib.ptr(boundary), _lib.ptr(lse[0]), _lib.ptr(lse[1]),
                       _lib.ptr(lse[2]), _lib.ptr(px), _lib.ptr(py), B, T, R, S, C, blank,
-                      rnnt_type, _lib.stream_ptr(dev))
+                      rnnt_type, _c_f64(delay_penalty), _lib.stream_ptr(dev))
         ctx.save_for_backward(logits, symbols, ranges, boundary, lse)
         ctx.cfg = (blank, rnnt_type)
         return px, py
@@ -179,13 +179,19 @@ class _LsmGather(torch.autograd.Function):
                       _lib.ptr(symbols), _lib.ptr(ranges), _lib.ptr(boundary), _lib.ptr(lse[0]),
                       _lib.ptr(g_px), _lib.ptr(g_py), _lib.ptr(g_logits), B, T, R, S, C, blank,
                       rnnt_type, _lib.stream_ptr(dev))
-        return g_logits, None, None, None, None, None
+        return g_logits, None, None, None, None, None, None
 
 
 def get_rnnt_logprobs_joint(logits: Tensor, symbols: Tensor, termination_symbol: int,
                             boundary: Optional[Tensor] = None,
                             rnnt_type: str = "regular") -> Tuple[Tensor, Tensor]:
     """(px, py) from full joiner logits [B][T][S+1][C] (reference rnnt_loss.py:343-449)."""
+    return _logprobs_joint(logits, symbols, termination_symbol, boundary, rnnt_type, 0.0)
+
+
+def _logprobs_joint(logits, symbols, termination_symbol, boundary, rnnt_type, delay_penalty):
+    """get_rnnt_logprobs_joint with the delay penalty of the loss functions added to px by
+    the kernel that writes the lattices."""
     assert logits.ndim == 4, logits.ndim
     (B, T, S1, C) = logits.shape
     S = S1 - 1
@@ -193,7 +199,7 @@ def get_rnnt_logprobs_joint(logits: Tensor, symbols: Tensor, termination_symbol:
     validate_st_lengths(S, T, rnnt_type == "regular", boundary)
     assert rnnt_type in ["regular", "modified", "constrained"], rnnt_type
     return _LsmGather.apply(logits, symbols, None, boundary, int(termination_symbol),
-                            _RNNT_TYPES[rnnt_type])
+                            _RNNT_TYPES[rnnt_type], float(delay_penalty))
 
 
 def get_rnnt_logprobs_pruned(logits: Tensor, symbols: Tensor, ranges: Tensor,
@@ -201,6 +207,10 @@ def get_rnnt_logprobs_pruned(logits: Tensor, symbols: Tensor, ranges: Tensor,
                              rnnt_type: str = "regular") -> Tuple[Tensor, Tensor]:
     """(px, py) from pruned joiner logits [B][T][s_range][C] and the ranges
     [B][T][s_range] they were computed on (reference rnnt_loss.py:856-1024)."""
+    return _logprobs_pruned(logits, symbols, ranges, termination_symbol, boundary, rnnt_type, 0.0)
+
+
+def _logprobs_pruned(logits, symbols, ranges, termination_symbol, boundary, rnnt_type, delay_penalty):
     assert logits.ndim == 4, logits.ndim
     (B, T, s_range, C) = logits.shape
     assert ranges.shape == (B, T, s_range), f"{ranges.shape} == ({B}, {T}, {s_range})"
@@ -208,7 +218,7 @@ def get_rnnt_logprobs_pruned(logits: Tensor, symbols: Tensor, ranges: Tensor,
     validate_st_lengths(S, T, rnnt_type == "regular", boundary)
     assert rnnt_type in ["regular", "modified", "constrained"], rnnt_type
     return _LsmGather.apply(logits, symbols, ranges, boundary, int(termination_symbol),
-                            _RNNT_TYPES[rnnt_type])
+                            _RNNT_TYPES[rnnt_type], float(delay_penalty))
 
 
 class _PrunedJoinerLogprobs(torch.autograd.Function):
@@ -217,7 +227,7 @@ class _PrunedJoinerLogprobs(torch.autograd.Function):
     gradient products on the tensor cores, log-softmax and symbol / blank gather."""
 
     @staticmethod
-    def forward(ctx, enc, dec, ranges, weight, bias, symbols, boundary, blank, rnnt_type):
+    def forward(ctx, enc, dec, ranges, weight, bias, symbols, boundary, blank, rnnt_type, delay_penalty=0.0):
         B, T, D = enc.shape
         S = symbols.shape[1]
         R = ranges.shape[2]
@@ -235,7 +245,8 @@ class _PrunedJoinerLogprobs(torch.autograd.Function):
             _lib.call("frnnt_pruned_joiner_logprobs_forward", _lib.ptr(enc), _lib.ptr(dec),
                       _lib.ptr(ranges), _lib.ptr(weight), _lib.ptr(bias), _lib.ptr(symbols),
                       _lib.ptr(boundary), _lib.ptr(px), _lib.ptr(py), _lib.ptr(saved),
-                      _lib.ptr(scratch), B, T, R, S, C, D, blank, rnnt_type, _lib.stream_ptr(dev))
+                      _lib.ptr(scratch), B, T, R, S, C, D, blank, rnnt_type, _c_f64(delay_penalty),
+                      _lib.stream_ptr(dev))
         ctx.save_for_backward(ranges, symbols, boundary, saved)
         ctx.cfg = (B, T, R, S, C, D, blank, rnnt_type, bias is not None)
         return px, py
@@ -265,7 +276,7 @@ class _PrunedJoinerLogprobs(torch.autograd.Function):
                       _lib.ptr(scratch), _lib.ptr(enc_grad), _lib.ptr(dec_grad), _lib.ptr(w_grad),
                       _lib.ptr(b_grad), B, T, R, S, C, D, blank, rnnt_type, _lib.stream_ptr(dev))
         return (enc_grad if need[0] else None, dec_grad if need[1] else None, None, w_grad, b_grad,
-                None, None, None, None)
+                None, None, None, None, None)
 
 
 def get_rnnt_logprobs_pruned_joiner(am: Tensor, lm: Tensor, ranges: Tensor, joiner_weight: Tensor,
@@ -283,6 +294,12 @@ def get_rnnt_logprobs_pruned_joiner(am: Tensor, lm: Tensor, ranges: Tensor, join
     CUDA tensors, D a multiple of 8 and C a multiple of 4.  No counterpart in the
     reference (which leaves the joiner to the caller); the pruned tensors, and a
     second pass over the logits for their log-sum-exp, never exist."""
+    return _logprobs_pruned_joiner(am, lm, ranges, joiner_weight, joiner_bias, symbols,
+                                   termination_symbol, boundary, rnnt_type, 0.0)
+
+
+def _logprobs_pruned_joiner(am, lm, ranges, joiner_weight, joiner_bias, symbols, termination_symbol,
+                            boundary, rnnt_type, delay_penalty):
     assert am.ndim == 3 and lm.ndim == 3 and ranges.ndim == 3, (am.shape, lm.shape, ranges.shape)
     (B, T, D) = am.shape
     (B2, S1, D2) = lm.shape
@@ -297,7 +314,8 @@ def get_rnnt_logprobs_pruned_joiner(am: Tensor, lm: Tensor, ranges: Tensor, join
     validate_st_lengths(S, T, rnnt_type == "regular", boundary)
     assert rnnt_type in ["regular", "modified", "constrained"], rnnt_type
     return _PrunedJoinerLogprobs.apply(am, lm, ranges, joiner_weight, joiner_bias, symbols, boundary,
-                                       int(termination_symbol), _RNNT_TYPES[rnnt_type])
+                                       int(termination_symbol), _RNNT_TYPES[rnnt_type],
+                                       float(delay_penalty))
 
 
 # ------------------------------------------------------------------------------
@@ -400,19 +418,15 @@ def do_rnnt_pruning(am: Tensor, lm: Tensor, ranges: Tensor) -> Tuple[Tensor, Ten
 # ------------------------------------------------------------------------------
 # losses
 # ------------------------------------------------------------------------------
-def _finish(px, py, boundary, rnnt_type, delay_penalty, reduction, return_grad):
-    """delay penalty, recursion and reduction shared by the four losses
-    (reference rnnt_loss.py:309-340 and its three copies)."""
-    if delay_penalty > 0.0:
-        B, S, T0 = px.shape
-        T = T0 if rnnt_type != "regular" else T0 - 1
-        if boundary is None:
-            offset = torch.tensor((T - 1) / 2, dtype=px.dtype, device=px.device).expand(B, 1, 1)
-        else:
-            offset = (boundary[:, 3] - 1) / 2
-        penalty = offset.reshape(B, 1, 1) - torch.arange(T0, device=px.device).reshape(1, 1, T0)
-        penalty = penalty * delay_penalty
-        px = px + penalty.to(px.dtype)
+def _penalty(delay_penalty: float) -> float:
+    """The reference applies the delay penalty only when it is positive
+    (rnnt_loss.py:309); the lattice-writing kernels add it to px."""
+    return float(delay_penalty) if delay_penalty > 0.0 else 0.0
+
+
+def _finish(px, py, boundary, reduction, return_grad):
+    """recursion and reduction shared by the losses (reference rnnt_loss.py:326-340 and its
+    three copies)."""
     scores_and_grads = mutual_information_recursion(px=px, py=py, boundary=boundary,
                                                     return_grad=return_grad)
     negated_loss = scores_and_grads[0] if return_grad else scores_and_grads
@@ -433,10 +447,9 @@ def rnnt_loss_simple(lm: Tensor, am: Tensor, symbols: Tensor, termination_symbol
                      return_grad: bool = False,
                      ) -> Union[Tensor, Tuple[Tensor, Tuple[Tensor, Tensor]]]:
     """RNN-T loss with the additive "simple" joiner (reference rnnt_loss.py:230-340)."""
-    px, py = get_rnnt_logprobs(lm=lm, am=am, symbols=symbols,
-                               termination_symbol=termination_symbol, boundary=boundary,
-                               rnnt_type=rnnt_type)
-    return _finish(px, py, boundary, rnnt_type, delay_penalty, reduction, return_grad)
+    px, py = _simple_logprobs(lm, am, symbols, termination_symbol, rnnt_type, boundary, False,
+                              delay_penalty=_penalty(delay_penalty))
+    return _finish(px, py, boundary, reduction, return_grad)
 
 
 def rnnt_loss_smoothed(lm: Tensor, am: Tensor, symbols: Tensor, termination_symbol: int,
@@ -446,11 +459,9 @@ def rnnt_loss_smoothed(lm: Tensor, am: Tensor, symbols: Tensor, termination_symb
                        return_grad: bool = False,
                        ) -> Union[Tuple[Tensor, Tuple[Tensor, Tensor]], Tensor]:
     """Smoothed "simple" loss (reference rnnt_loss.py:1372-1494)."""
-    px, py = get_rnnt_logprobs_smoothed(lm=lm, am=am, symbols=symbols,
-                                        termination_symbol=termination_symbol,
-                                        lm_only_scale=lm_only_scale, am_only_scale=am_only_scale,
-                                        boundary=boundary, rnnt_type=rnnt_type)
-    return _finish(px, py, boundary, rnnt_type, delay_penalty, reduction, return_grad)
+    px, py = _simple_logprobs(lm, am, symbols, termination_symbol, rnnt_type, boundary, True,
+                              lm_only_scale, am_only_scale, delay_penalty=_penalty(delay_penalty))
+    return _finish(px, py, boundary, reduction, return_grad)
 
 
 def rnnt_loss(logits: Tensor, symbols: Tensor, termination_symbol: int,
@@ -458,10 +469,9 @@ def rnnt_loss(logits: Tensor, symbols: Tensor, termination_symbol: int,
               delay_penalty: float = 0.0, reduction: Optional[str] = "mean",
               return_grad: bool = False) -> Tensor:
     """Unpruned RNN-T loss on logits [B][T][S+1][C] (reference rnnt_loss.py:452-547)."""
-    px, py = get_rnnt_logprobs_joint(logits=logits, symbols=symbols,
-                                     termination_symbol=termination_symbol, boundary=boundary,
-                                     rnnt_type=rnnt_type)
-    return _finish(px, py, boundary, rnnt_type, delay_penalty, reduction, return_grad)
+    px, py = _logprobs_joint(logits, symbols, termination_symbol, boundary, rnnt_type,
+                             _penalty(delay_penalty))
+    return _finish(px, py, boundary, reduction, return_grad)
 
 
 def rnnt_loss_pruned(logits: Tensor, symbols: Tensor, ranges: Tensor, termination_symbol: int,
@@ -469,10 +479,9 @@ def rnnt_loss_pruned(logits: Tensor, symbols: Tensor, ranges: Tensor, terminatio
                      delay_penalty: float = 0.0, reduction: Optional[str] = "mean",
                      return_grad: bool = False) -> Tensor:
     """Pruned RNN-T loss on logits [B][T][s_range][C] (reference rnnt_loss.py:1027-1132)."""
-    px, py = get_rnnt_logprobs_pruned(logits=logits, symbols=symbols, ranges=ranges,
-                                      termination_symbol=termination_symbol, boundary=boundary,
-                                      rnnt_type=rnnt_type)
-    return _finish(px, py, boundary, rnnt_type, delay_penalty, reduction, return_grad)
+    px, py = _logprobs_pruned(logits, symbols, ranges, termination_symbol, boundary, rnnt_type,
+                              _penalty(delay_penalty))
+    return _finish(px, py, boundary, reduction, return_grad)
 
 
 def rnnt_loss_pruned_joiner(am: Tensor, lm: Tensor, ranges: Tensor, joiner_weight: Tensor,
@@ -483,8 +492,6 @@ def rnnt_loss_pruned_joiner(am: Tensor, lm: Tensor, ranges: Tensor, joiner_weigh
     """rnnt_loss_pruned (reference rnnt_loss.py:1027-1132) on the logits of the joiner
     ``linear(tanh(am_pruned + lm_pruned))``, computed by the fused operator behind
     get_rnnt_logprobs_pruned_joiner instead of being passed in."""
-    px, py = get_rnnt_logprobs_pruned_joiner(am=am, lm=lm, ranges=ranges,
-                                             joiner_weight=joiner_weight, joiner_bias=joiner_bias,
-                                             symbols=symbols, termination_symbol=termination_symbol,
-                                             boundary=boundary, rnnt_type=rnnt_type)
-    return _finish(px, py, boundary, rnnt_type, delay_penalty, reduction, return_grad)
+    px, py = _logprobs_pruned_joiner(am, lm, ranges, joiner_weight, joiner_bias, symbols,
+                                     termination_symbol, boundary, rnnt_type, _penalty(delay_penalty))
+    return _finish(px, py, boundary, reduction, return_grad)

@@ -174,12 +174,18 @@ size_t frnnt_simple_scratch_bytes(int dtype, int B, int S, int T, int C);
  * smoothed == 0 replaces get_rnnt_logprobs (fast_rnnt/python/fast_rnnt/rnnt_loss.py:66-227);
  * smoothed != 0 replaces get_rnnt_logprobs_smoothed (rnnt_loss.py:1135-1369) with its
  * lm_only_scale / am_only_scale (exact zeros become 1e-20 as in the reference).
- * rnnt_type is FRNNT_REGULAR / FRNNT_MODIFIED / FRNNT_CONSTRAINED; boundary may be NULL. */
+ * rnnt_type is FRNNT_REGULAR / FRNNT_MODIFIED / FRNNT_CONSTRAINED; boundary may be NULL.
+ * delay_penalty > 0 adds delay_penalty * ((T_b - 1) / 2 - t) to px[b][s][t] as the
+ * reference's loss functions do between the lattices and the recursion
+ * (rnnt_loss.py:309-324, :516-531, :1101-1116, :1463-1478; T_b = boundary[b][3], or T),
+ * with torch's roundings; 0 for the plain get_rnnt_logprobs* functions.  The same argument
+ * of frnnt_lsm_gather_forward and frnnt_pruned_joiner_logprobs_forward means the same. */
 int frnnt_simple_logprobs_forward(int dtype, const void *lm, const void *am,
                                   const int64_t *symbols, const int64_t *boundary, int blank,
                                   int rnnt_type, int smoothed, double lm_only_scale,
-                                  double am_only_scale, void *px, void *py, void *saved,
-                                  void *scratch, int B, int S, int T, int C, void *stream);
+                                  double am_only_scale, double delay_penalty, void *px, void *py,
+                                  void *saved, void *scratch, int B, int S, int T, int C,
+                                  void *stream);
 
 /* Gradient of the above w.r.t. lm and am given the gradients of px and py
  * (what autograd derives for the reference's composition of ATen ops).
@@ -203,7 +209,8 @@ int frnnt_simple_logprobs_backward(int dtype, const void *lm, const void *am,
 int frnnt_lsm_gather_forward(int dtype, const void *logits, const int64_t *symbols,
                              const int64_t *ranges, const int64_t *boundary, void *lse,
                              void *px_band, void *py_band, void *px, void *py, int B, int T,
-                             int R, int S, int C, int blank, int rnnt_type, void *stream);
+                             int R, int S, int C, int blank, int rnnt_type, double delay_penalty,
+                             void *stream);
 
 /* Gradient of the above w.r.t. the logits; logits_grad [B][T][R][C] is fully written. */
 int frnnt_lsm_gather_backward(int dtype, const void *logits, const int64_t *symbols,
@@ -315,7 +322,8 @@ int frnnt_pruned_joiner_logprobs_forward(const float *enc, const float *dec, con
                                          const float *weight, const float *bias,
                                          const int64_t *symbols, const int64_t *boundary, float *px,
                                          float *py, void *saved, void *scratch, int B, int T, int R,
-                                         int S, int C, int D, int blank, int rnnt_type, void *stream);
+                                         int S, int C, int D, int blank, int rnnt_type,
+                                         double delay_penalty, void *stream);
 
 /* Gradients of the above given the gradients of px and py: enc_grad [B][T][D] and
  * dec_grad [B][S+1][D] (both or neither), weight_grad [C][D], bias_grad [C] (each may be
