@@ -1,10 +1,10 @@
 // The fp16-pair engine (umma_pairs.cuh) with 256 x 128 output tiles per work item.
 //
-// Why: the 128 x 128 kernel is bound by the L2 -> shared-memory feed (64 KB of planes per
-// 64-wide K slice; measured ~48 bytes per clock and SM at best against 83 needed to keep
-// the tensor pipe busy).  A 256 x 128 tile shares every B slice between two row halves:
-// 96 KB per slice for twice the flops, a quarter less traffic per flop, with plain per-CTA
-// loads (no thread-block clusters).
+// Why: the 128 x 128 kernel keeps the tensor pipe about half busy: per 64-wide K slice it
+// takes 64 KB of planes into shared memory (measured 37-48 bytes per clock and SM) while
+// the MMAs read 96 KB of operands out of it.  A 256 x 128 tile shares every B slice between
+// two row halves: 96 KB per slice for twice the flops, a quarter less traffic per flop, with
+// plain per-CTA loads (no thread-block clusters).
 //
 // What changes against the 128 x 128 kernel:
 //   * a stage holds A hi / lo for both row halves (4 x 16 KB) and B hi / lo (2 x 16 KB);
