@@ -449,7 +449,7 @@ def stage_table(fr, wl, dev, flush, hbm_gbs):
     w_g, b_g = torch.empty(C, D, device=dev), torch.empty(C, device=dev)
 
     def pj_fwd():
-        _lib.call("frnnt_pruned_joiner_logprobs_forward", _lib.ptr(t["enc"]), _lib.ptr(t["dec"]),
+        _lib.call("frnnt_pruned_joiner_logprobs_forward", 0, _lib.ptr(t["enc"]), _lib.ptr(t["dec"]),
                   _lib.ptr(ranges), _lib.ptr(W), _lib.ptr(t["joiner_b"]), _lib.ptr(sym), _lib.ptr(bnd),
                   _lib.ptr(ppxd), _lib.ptr(ppyd), _lib.ptr(pj_saved), _lib.ptr(pj_fs), B, T, R, S, C, D,
                   0, 0, ctypes.c_double(0.0), sp)

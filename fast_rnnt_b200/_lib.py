@@ -12,7 +12,7 @@ import torch
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libfrnnt_sm100.so")
 
-F32, F64 = 0, 1
+F32, F64, F16, BF16 = 0, 1, 2, 3
 _lib = None
 
 _c_int, _c_vp, _c_sz, _c_f64 = ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_double
@@ -48,6 +48,18 @@ def dtype_code(dtype) -> int:
     if dtype == torch.float64:
         return F64
     raise TypeError(f"only float32 and float64 are supported (as in the reference), got {dtype}")
+
+
+_HALF_CODES = {torch.float16: F16, torch.bfloat16: BF16}
+
+
+def is_16bit(t) -> bool:
+    return t is not None and t.dtype in _HALF_CODES
+
+
+def input_code(dtype) -> int:
+    """dtype code of an INPUT that a kernel may read as 16-bit values."""
+    return _HALF_CODES[dtype] if dtype in _HALF_CODES else dtype_code(dtype)
 
 
 def ptr(t):

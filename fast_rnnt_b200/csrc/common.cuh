@@ -1,5 +1,7 @@
 // Shared host/device helpers of libfrnnt_sm100.so.
 #pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <math.h>
 #include <stdint.h>
@@ -40,6 +42,28 @@ int sm_count();
 
 inline int check_dtype(int dtype) { return dtype == FRNNT_F32 || dtype == FRNNT_F64; }
 inline size_t dtype_size(int dtype) { return dtype == FRNNT_F64 ? 8 : 4; }
+
+// ---- device: inputs that may be 16-bit (FRNNT_F16 / FRNNT_BF16), read as float32 ------------
+__device__ __forceinline__ float in_f32(float x) { return x; }
+__device__ __forceinline__ float in_f32(__half x) { return __half2float(x); }
+__device__ __forceinline__ float in_f32(__nv_bfloat16 x) { return __bfloat162float(x); }
+// four consecutive values starting at element 4 * v of a row (16- resp. 8-byte aligned)
+__device__ __forceinline__ float4 in_load4(const float *row, int v) {
+  return reinterpret_cast<const float4 *>(row)[v];
+}
+__device__ __forceinline__ float4 in_load4(const __half *row, int v) {
+  const uint2 q = reinterpret_cast<const uint2 *>(row)[v];
+  const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&q.x));
+  const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&q.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ float4 in_load4(const __nv_bfloat16 *row, int v) {
+  const uint2 q = reinterpret_cast<const uint2 *>(row)[v];
+  // a bfloat16 is the upper half of a float32
+  return make_float4(__uint_as_float(q.x << 16), __uint_as_float(q.x & 0xffff0000u),
+                     __uint_as_float(q.y << 16), __uint_as_float(q.y & 0xffff0000u));
+}
+inline bool is_half_input(int dtype) { return dtype == FRNNT_F16 || dtype == FRNNT_BF16; }
 
 // ---- device: math in the reference's operation order ------------------------
 template <typename real> __device__ __forceinline__ real neg_inf();

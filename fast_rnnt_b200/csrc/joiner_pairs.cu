@@ -35,7 +35,6 @@ namespace frnnt {
 
 constexpr float kActScale = 16384.f;  // 2^14: |tanh| <= 1, so the planes stay below 2^14
 constexpr int kMaxParts = 1024;       // per-CTA partial maxima of a reduction
-constexpr int kRowWarps = 8;
 
 enum { kScaleAct = 0, kScaleW = 1, kScaleG = 2 };  // slots of the inverse scales
 
@@ -215,8 +214,20 @@ split_weights_kernel(const float *__restrict__ W, int C, int D, int Cp, const fl
 
 // act[b][t][k][:] = tanh(enc[b][t][:] + dec[b][ranges[b][t][k]][:]) as planes; one warp per
 // row, eight columns per lane
+// eight consecutive inputs starting at element 8 * v of a row, as float32
+__device__ __forceinline__ void in_load8(const float *row, int v, float (&x)[8]) {
+  const float4 a = reinterpret_cast<const float4 *>(row)[2 * v], b = reinterpret_cast<const float4 *>(row)[2 * v + 1];
+  x[0] = a.x, x[1] = a.y, x[2] = a.z, x[3] = a.w, x[4] = b.x, x[5] = b.y, x[6] = b.z, x[7] = b.w;
+}
+template <typename T16>
+__device__ __forceinline__ void in_load8(const T16 *row, int v, float (&x)[8]) {
+  const float4 a = in_load4(row, 2 * v), b = in_load4(row, 2 * v + 1);
+  x[0] = a.x, x[1] = a.y, x[2] = a.z, x[3] = a.w, x[4] = b.x, x[5] = b.y, x[6] = b.z, x[7] = b.w;
+}
+
+template <typename TIn>
 __global__ void __launch_bounds__(256)
-pruned_tanh_pairs_kernel(const float *__restrict__ enc, const float *__restrict__ dec,
+pruned_tanh_pairs_kernel(const TIn *__restrict__ enc, const TIn *__restrict__ dec,
                          const int64_t *__restrict__ ranges, __half *__restrict__ act_hi,
                          __half *__restrict__ act_lo, long long rows, int R, int TR, int S1, int D,
                          float *__restrict__ scales) {
@@ -229,14 +240,16 @@ pruned_tanh_pairs_kernel(const float *__restrict__ enc, const float *__restrict_
     const long long b = row / TR, bt = row / R;
     long long s = ranges[row];
     s = s < 0 ? 0 : (s >= S1 ? S1 - 1 : s);
-    const float4 *e = reinterpret_cast<const float4 *>(enc + (size_t)bt * D);
-    const float4 *d = reinterpret_cast<const float4 *>(dec + ((size_t)b * S1 + s) * D);
+    const TIn *e = enc + (size_t)bt * D;
+    const TIn *d = dec + ((size_t)b * S1 + s) * D;
     uint4 *oh = reinterpret_cast<uint4 *>(act_hi + (size_t)row * D);
     uint4 *ol = reinterpret_cast<uint4 *>(act_lo + (size_t)row * D);
     for (int v = lane; v < d8; v += 32) {
-      const float4 x0 = e[2 * v], x1 = e[2 * v + 1], y0 = d[2 * v], y1 = d[2 * v + 1];
-      const float a[8] = {x0.x + y0.x, x0.y + y0.y, x0.z + y0.z, x0.w + y0.w,
-                          x1.x + y1.x, x1.y + y1.y, x1.z + y1.z, x1.w + y1.w};
+      float xe[8], xd[8], a[8];
+      in_load8(e, v, xe);
+      in_load8(d, v, xd);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) a[c] = xe[c] + xd[c];
       const float t0[4] = {tanhf(a[0]), tanhf(a[1]), tanhf(a[2]), tanhf(a[3])};
       const float t1[4] = {tanhf(a[4]), tanhf(a[5]), tanhf(a[6]), tanhf(a[7])};
       uint2 h0, l0, h1, l1;
@@ -587,7 +600,7 @@ extern "C" size_t frnnt_pruned_joiner_backward_scratch_bytes(int B, int T, int R
 // parts of a forward / backward call (bit mask); the diagnostic entry points re-launch one
 enum { kPartPlanes = 1, kPartProduct = 2, kPartRest = 4, kPartProduct2 = 8, kPartInputGrads = 16 };
 
-static int pjl_forward(const float *enc, const float *dec, const int64_t *ranges, const float *weight,
+static int pjl_forward(int input_dtype, const void *enc, const void *dec, const int64_t *ranges, const float *weight,
                        const float *bias, const int64_t *symbols, const int64_t *boundary, float *px,
                        float *py, void *saved, void *scratch, int B, int T, int R, int S, int C, int D,
                        int blank, int rnnt_type, double delay_penalty, void *stream, unsigned parts) {
@@ -627,8 +640,17 @@ static int pjl_forward(const float *enc, const float *dec, const int64_t *ranges
                                                              wt_hi, wt_lo, scales));
     long long want = (rows + 7) / 8;
     const int grid = (int)(want < (long long)sm_count() * 32 ? want : (long long)sm_count() * 32);
-    FRNNT_KERNEL(pruned_tanh_pairs_kernel<<<grid, 256, 0, st>>>(enc, dec, ranges, act_hi, act_lo, rows, R,
-                                                               T * R, S + 1, D, scales));
+    if (input_dtype == FRNNT_F16) {
+      FRNNT_KERNEL(pruned_tanh_pairs_kernel<__half><<<grid, 256, 0, st>>>(
+          (const __half *)enc, (const __half *)dec, ranges, act_hi, act_lo, rows, R, T * R, S + 1, D, scales));
+    } else if (input_dtype == FRNNT_BF16) {
+      FRNNT_KERNEL(pruned_tanh_pairs_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
+          (const __nv_bfloat16 *)enc, (const __nv_bfloat16 *)dec, ranges, act_hi, act_lo, rows, R, T * R, S + 1, D,
+          scales));
+    } else {
+      FRNNT_KERNEL(pruned_tanh_pairs_kernel<float><<<grid, 256, 0, st>>>(
+          (const float *)enc, (const float *)dec, ranges, act_hi, act_lo, rows, R, T * R, S + 1, D, scales));
+    }
     FRNNT_CUDA(cudaGetLastError());
   }
   if (parts & kPartProduct) {
@@ -649,15 +671,17 @@ static int pjl_forward(const float *enc, const float *dec, const int64_t *ranges
   return FRNNT_OK;
 }
 
-extern "C" int frnnt_pruned_joiner_logprobs_forward(const float *enc, const float *dec,
+extern "C" int frnnt_pruned_joiner_logprobs_forward(int input_dtype, const void *enc, const void *dec,
                                                     const int64_t *ranges, const float *weight,
                                                     const float *bias, const int64_t *symbols,
                                                     const int64_t *boundary, float *px, float *py,
                                                     void *saved, void *scratch, int B, int T, int R,
                                                     int S, int C, int D, int blank, int rnnt_type,
                                                     double delay_penalty, void *stream) {
-  return pjl_forward(enc, dec, ranges, weight, bias, symbols, boundary, px, py, saved, scratch, B, T, R, S, C, D,
-                     blank, rnnt_type, delay_penalty, stream, ~0u);
+  FRNNT_REQUIRE(input_dtype == FRNNT_F32 || is_half_input(input_dtype), FRNNT_EINVAL,
+                "input_dtype must be FRNNT_F32, FRNNT_F16 or FRNNT_BF16");
+  return pjl_forward(input_dtype, enc, dec, ranges, weight, bias, symbols, boundary, px, py, saved, scratch, B, T, R,
+                     S, C, D, blank, rnnt_type, delay_penalty, stream, ~0u);
 }
 
 extern "C" int frnnt_pruned_joiner_logprobs_forward_part(int part, const float *enc, const float *dec,
@@ -668,8 +692,8 @@ extern "C" int frnnt_pruned_joiner_logprobs_forward_part(int part, const float *
                                                          int S, int C, int D, int blank, int rnnt_type,
                                                          void *stream) {
   FRNNT_REQUIRE(part >= 0 && part <= 2, FRNNT_EINVAL, "part must be 0 (planes), 1 (product) or 2 (lattices)");
-  return pjl_forward(enc, dec, ranges, weight, bias, symbols, boundary, px, py, saved, scratch, B, T, R, S, C, D,
-                     blank, rnnt_type, 0.0, stream, 1u << part);
+  return pjl_forward(FRNNT_F32, enc, dec, ranges, weight, bias, symbols, boundary, px, py, saved, scratch, B, T, R,
+                     S, C, D, blank, rnnt_type, 0.0, stream, 1u << part);
 }
 
 static int pjl_backward(const float *px_grad, const float *py_grad, const int64_t *ranges,

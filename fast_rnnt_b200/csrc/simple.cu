@@ -687,7 +687,8 @@ static bool use_pairs(const void *lm, const void *am, int S1, int T, int C, int 
 }
 
 static int simple_check(int dtype, int B, int S, int T, int C, int blank, int rnnt_type) {
-  FRNNT_REQUIRE(check_dtype(dtype), FRNNT_EINVAL, "dtype must be FRNNT_F32 or FRNNT_F64");
+  FRNNT_REQUIRE(check_dtype(dtype) || is_half_input(dtype), FRNNT_EINVAL,
+                "dtype must be FRNNT_F32, FRNNT_F64, or FRNNT_F16 / FRNNT_BF16 for 16-bit lm and am");
   FRNNT_REQUIRE(B >= 0 && S >= 0 && T >= 0 && C >= 1, FRNNT_EINVAL,
                 "bad sizes B=%d S=%d T=%d C=%d", B, S, T, C);
   FRNNT_REQUIRE(blank >= 0 && blank < C, FRNNT_EINVAL, "blank=%d outside [0,%d)", blank, C);
@@ -722,8 +723,8 @@ template <typename real>
 static int simple_forward_impl(const void *lm_, const void *am_, const int64_t *symbols,
                                const int64_t *boundary, int blank, int rnnt_type, SmoothCfg cfg,
                                void *px, void *py, void *saved, void *scratch, int B, int S, int T,
-                               int C, cudaStream_t st) {
-  const real *lm = (const real *)lm_, *am = (const real *)am_;
+                               int C, cudaStream_t st, int input_dtype = FRNNT_F32) {
+  const real *lm = (const real *)lm_, *am = (const real *)am_;  // not dereferenced for 16-bit inputs
   const int S1 = S + 1;
   SavedLayout sv(sizeof(real), B, S, T, C);
   ScratchLayout sc(sizeof(real), B, S, T, C);
@@ -735,13 +736,17 @@ static int simple_forward_impl(const void *lm_, const void *am_, const int64_t *
   const long long lm_rows = (long long)B * S1, am_rows = (long long)B * T;
 
   const bool pairs = use_pairs<real>(lm, am, S1, T, C, rnnt_type);
+  FRNNT_REQUIRE(!is_half_input(input_dtype) || (pairs && (!cfg.smoothed || cfg.am_only_off)), FRNNT_EUNSUPPORTED,
+                "16-bit inputs are read by the tensor-core path without the am-only branch only "
+                "(frnnt_simple_reads_16bit_inputs)");
   void *pairs_saved = svb + sv.total;
   if (pairs) {
-    int rc0 = launch_simple_forward_pairs((const float *)lm, (const float *)am, symbols, boundary, blank,
+    int rc0 = launch_simple_forward_pairs(lm_, am_, symbols, boundary, blank,
                                           rnnt_type, cfg.smoothed, cfg.am_only_off, (float)cfg.both,
                                           (float)cfg.ls, (float)cfg.as, (float *)px, (float *)py, (float *)norm,
                                           (float *)lmmax, (float *)lmsum, (float *)ammax, (const float *)amonly,
-                                          (const float *)loguni, pairs_saved, B, S, T, C, 0, st, cfg.delay_penalty);
+                                          (const float *)loguni, pairs_saved, B, S, T, C, 0, st, cfg.delay_penalty,
+                                          input_dtype);
     if (rc0 != FRNNT_OK) return rc0;
   } else {
     FRNNT_KERNEL(row_stats_kernel<real><<<warps_grid(lm_rows), 256, 0, st>>>(lm, lmmax, lmsum, lm_rows, C));
@@ -760,7 +765,7 @@ static int simple_forward_impl(const void *lm_, const void *am_, const int64_t *
   }
   int rc;
   if (pairs)
-    return launch_simple_forward_pairs((const float *)lm, (const float *)am, symbols, boundary, blank,
+    return launch_simple_forward_pairs(lm_, am_, symbols, boundary, blank,
                                        rnnt_type, cfg.smoothed, cfg.am_only_off, (float)cfg.both,
                                        (float)cfg.ls, (float)cfg.as, (float *)px, (float *)py, (float *)norm,
                                        (float *)lmmax, (float *)lmsum, (float *)ammax, (const float *)amonly,
@@ -887,15 +892,25 @@ using namespace frnnt;
 
 // float32 calls may take the tensor-core path, whose planes and tables follow the regular areas
 extern "C" size_t frnnt_simple_saved_bytes(int dtype, int B, int S, int T, int C) {
+  if (is_half_input(dtype)) dtype = FRNNT_F32;
   if (!check_dtype(dtype) || B < 0 || S < 0 || T < 0 || C < 0) return 0;
   return SavedLayout(dtype_size(dtype), B, S, T, C).total +
          (dtype == FRNNT_F32 ? SimplePairsLayout(B, S, T, C).saved_bytes : 0);
 }
 
 extern "C" size_t frnnt_simple_scratch_bytes(int dtype, int B, int S, int T, int C) {
+  if (is_half_input(dtype)) dtype = FRNNT_F32;
   if (!check_dtype(dtype) || B < 0 || S < 0 || T < 0 || C < 0) return 0;
   return ScratchLayout(dtype_size(dtype), B, S, T, C).total +
          (dtype == FRNNT_F32 ? SimplePairsLayout(B, S, T, C).scratch_bytes : 0);
+}
+
+extern "C" int frnnt_simple_reads_16bit_inputs(int S, int T, int C, int rnnt_type, int smoothed,
+                                               double am_only_scale) {
+  if (S < 0 || T < 1 || C < 1) return 0;
+  if (smoothed && am_only_scale != 0.0) return 0;
+  // 256-byte aligned rows stand in for the caller's tensors (torch's allocations are)
+  return use_pairs<float>((const void *)256, (const void *)256, S + 1, T, C, rnnt_type) ? 1 : 0;
 }
 
 extern "C" int frnnt_simple_logprobs_forward(int dtype, const void *lm, const void *am,
@@ -913,9 +928,9 @@ extern "C" int frnnt_simple_logprobs_forward(int dtype, const void *lm, const vo
   SmoothCfg cfg = make_cfg(smoothed, lm_only_scale, am_only_scale);
   cfg.delay_penalty = delay_penalty > 0.0 ? delay_penalty : 0.0;
   cudaStream_t st = (cudaStream_t)stream;
-  if (dtype == FRNNT_F32)
+  if (dtype != FRNNT_F64)
     return simple_forward_impl<float>(lm, am, symbols, boundary, blank, rnnt_type, cfg, px, py,
-                                      saved, scratch, B, S, T, C, st);
+                                      saved, scratch, B, S, T, C, st, dtype);
   return simple_forward_impl<double>(lm, am, symbols, boundary, blank, rnnt_type, cfg, px, py,
                                      saved, scratch, B, S, T, C, st);
 }
@@ -939,7 +954,12 @@ extern "C" int frnnt_simple_logprobs_backward(int dtype, const void *lm, const v
   // gradient (<= 1e-19 relative) is below the resolution of either dtype and is skipped.
   const int am_only_active = smoothed && am_only_scale != 0.0;
   cudaStream_t st = (cudaStream_t)stream;
-  if (dtype == FRNNT_F32)
+  if (is_half_input(dtype)) {
+    // lm and am are not read on this path (the forward kept what the backward needs)
+    FRNNT_REQUIRE(use_pairs<float>(lm, am, S + 1, T, C, rnnt_type) && T > 0 && !am_only_active,
+                  FRNNT_EUNSUPPORTED, "16-bit inputs: see frnnt_simple_reads_16bit_inputs");
+  }
+  if (dtype != FRNNT_F64)
     return simple_backward_impl<float>(lm, am, symbols, boundary, blank, rnnt_type, cfg,
                                        am_only_active, px_grad, py_grad, saved, scratch, lm_grad,
                                        am_grad, B, S, T, C, st);

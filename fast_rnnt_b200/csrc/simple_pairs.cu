@@ -70,8 +70,9 @@ bool simple_pairs_supported(const void *lm, const void *am, int S1, int T, int C
 
 // ---- forward, pass 1: row maxima, exp planes, per-row scalars -----------------------------------
 // one warp per row of lm (rows 0 .. B*S1-1) or am (the rest); 16-byte loads
+template <typename TIn>
 __global__ void __launch_bounds__(256)
-exp_planes_kernel(const float *__restrict__ lm, const float *__restrict__ am,
+exp_planes_kernel(const TIn *__restrict__ lm, const TIn *__restrict__ am,
                   const int64_t *__restrict__ symbols, __half *__restrict__ lp_hi,
                   __half *__restrict__ lp_lo, __half *__restrict__ ap_hi, __half *__restrict__ ap_lo,
                   float *__restrict__ lmmax, float *__restrict__ lmsum, float *__restrict__ ammax,
@@ -86,7 +87,7 @@ exp_planes_kernel(const float *__restrict__ lm, const float *__restrict__ am,
   for (long long row = warp0; row < rows; row += nwarps) {
     const bool is_lm = row < rows_lm;
     const long long r = is_lm ? row : row - rows_lm;
-    const float4 *src = reinterpret_cast<const float4 *>((is_lm ? lm : am) + r * C);
+    const TIn *src = (is_lm ? lm : am) + r * C;
     uint2 *dh = reinterpret_cast<uint2 *>((is_lm ? lp_hi : ap_hi) + r * Cp);
     uint2 *dl = reinterpret_cast<uint2 *>((is_lm ? lp_lo : ap_lo) + r * Cp);
     // the first four vectors of a lane stay in registers (rows up to 512 entries are read once)
@@ -96,12 +97,12 @@ exp_planes_kernel(const float *__restrict__ lm, const float *__restrict__ am,
     for (int j = 0; j < 4; ++j) {
       const int v = lane + 32 * j;
       if (v < nvec) {
-        keep[j] = src[v];
+        keep[j] = in_load4(src, v);
         m = fmaxf(fmaxf(m, fmaxf(keep[j].x, keep[j].y)), fmaxf(keep[j].z, keep[j].w));
       }
     }
     for (int v = lane + 128; v < nvec; v += 32) {
-      const float4 q = src[v];
+      const float4 q = in_load4(src, v);
       m = fmaxf(fmaxf(m, fmaxf(q.x, q.y)), fmaxf(q.z, q.w));
     }
     m = warp_max(m);
@@ -120,12 +121,12 @@ exp_planes_kernel(const float *__restrict__ lm, const float *__restrict__ am,
       const int v = lane + 32 * j;
       if (v < nvec) one(v, keep[j]);
     }
-    for (int v = lane + 128; v < nvec; v += 32) one(v, src[v]);
+    for (int v = lane + 128; v < nvec; v += 32) one(v, in_load4(src, v));
     sum = warp_sum(sum);
     if (!is_lm) {
       // am[t][symbol of every lattice row]: gathered here, where the row has just been read
       // (L1 hits), so that the product's epilogue reads them as whole 128-byte lines
-      const float *x = am + r * C;
+      const TIn *x = am + r * C;
       const int64_t *sy = symbols + (size_t)(r / T) * S;
       float *dst = am_sym + (size_t)r * Sp;
       for (int s = lane; s < Sp; s += 32) {
@@ -133,29 +134,29 @@ exp_planes_kernel(const float *__restrict__ lm, const float *__restrict__ am,
         if (s < S) {
           long long y = sy[s];
           if (y < 0 || y >= C) y = blank;
-          v = x[y];
+          v = in_f32(x[y]);
         }
         dst[s] = v;
       }
     }
     if (lane == 0) {
-      const float *x = (is_lm ? lm : am) + r * C;
+      const TIn *x = (is_lm ? lm : am) + r * C;
       if (is_lm) {
         const int b = (int)(r / S1), s = (int)(r % S1);
         lmmax[r] = m;
         lmsum[r] = sum;
         lnorm[r] = logf(sum) + m;
-        lm_blk[r] = x[blank];
+        lm_blk[r] = in_f32(x[blank]);
         if (s < S) {
           long long y = symbols[(size_t)b * S + s];
           if (y < 0 || y >= C) y = blank;
-          lm_sym[r] = x[y];
+          lm_sym[r] = in_f32(x[y]);
           // the -inf column of the regular type, which no frame owns
           if (regular) px[((size_t)b * S + s) * (T + 1) + T] = -INFINITY;
         }
       } else {
         ammax[r] = m;
-        am_blk[r] = x[blank];
+        am_blk[r] = in_f32(x[blank]);
       }
     }
   }
@@ -399,12 +400,12 @@ sp_split_kernel(const float *__restrict__ x, long long rows, int Tp, int Tq,
   }
 }
 
-int launch_simple_forward_pairs(const float *lm, const float *am, const int64_t *symbols,
+int launch_simple_forward_pairs(const void *lm, const void *am, const int64_t *symbols,
                                 const int64_t *boundary, int blank, int rnnt_type, int smoothed,
                                 int am_only_off, float both, float ls, float as, float *px, float *py,
                                 float *norm, float *lmmax, float *lmsum, float *ammax,
                                 const float *amonly, const float *loguni, void *pairs_saved, int B, int S,
-                                int T, int C, int stage, cudaStream_t st, double delay_penalty) {
+                                int T, int C, int stage, cudaStream_t st, double delay_penalty, int input_dtype) {
   const SimplePairsLayout L(B, S, T, C);
   uint8_t *sv = (uint8_t *)pairs_saved;
   __half *lp_hi = (__half *)(sv + L.lp_hi), *lp_lo = (__half *)(sv + L.lp_lo);
@@ -417,9 +418,19 @@ int launch_simple_forward_pairs(const float *lm, const float *am, const int64_t 
     const long long rows = (long long)B * (S1 + T);
     long long want = (rows + 7) / 8;
     const int grid = (int)(want < (long long)sm_count() * 32 ? want : (long long)sm_count() * 32);
-    FRNNT_KERNEL(exp_planes_kernel<<<grid, 256, 0, st>>>(lm, am, symbols, lp_hi, lp_lo, ap_hi, ap_lo, lmmax, lmsum,
-                                                        ammax, lm_blk, lm_sym, lnorm, am_blk, am_sym, px, B, S, T, C,
-                                                        L.Cp, L.Sp, blank, rnnt_type == FRNNT_REGULAR));
+#define FRNNT_EXP_PLANES(TIn)                                                                                   \
+  FRNNT_KERNEL(exp_planes_kernel<TIn><<<grid, 256, 0, st>>>((const TIn *)lm, (const TIn *)am, symbols, lp_hi, lp_lo,  \
+                                                           ap_hi, ap_lo, lmmax, lmsum, ammax, lm_blk, lm_sym, lnorm, \
+                                                           am_blk, am_sym, px, B, S, T, C, L.Cp, L.Sp, blank,        \
+                                                           rnnt_type == FRNNT_REGULAR))
+    if (input_dtype == FRNNT_F16) {
+      FRNNT_EXP_PLANES(__half);
+    } else if (input_dtype == FRNNT_BF16) {
+      FRNNT_EXP_PLANES(__nv_bfloat16);
+    } else {
+      FRNNT_EXP_PLANES(float);
+    }
+#undef FRNNT_EXP_PLANES
     FRNNT_CUDA(cudaGetLastError());
     return FRNNT_OK;
   }

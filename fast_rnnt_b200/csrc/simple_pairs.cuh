@@ -26,12 +26,14 @@ bool simple_pairs_supported(const void *lm, const void *am, int S1, int T, int C
 // stage 0: row maxima / sums, exp planes, per-row scalars, the -inf column of px;
 // stage 1: normalizer product + lattices (needs amonly / loguni when the am-only branch is on;
 // a positive delay_penalty is added to px as the reference's loss functions do)
-int launch_simple_forward_pairs(const float *lm, const float *am, const int64_t *symbols,
+// lm / am: float32, or 16-bit values when input_dtype is FRNNT_F16 / FRNNT_BF16 (only stage 0 reads them)
+int launch_simple_forward_pairs(const void *lm, const void *am, const int64_t *symbols,
                                 const int64_t *boundary, int blank, int rnnt_type, int smoothed,
                                 int am_only_off, float both, float ls, float as, float *px, float *py,
                                 float *norm, float *lmmax, float *lmsum, float *ammax,
                                 const float *amonly, const float *loguni, void *pairs_saved, int B, int S,
-                                int T, int C, int stage, cudaStream_t st, double delay_penalty = 0.0);
+                                int T, int C, int stage, cudaStream_t st, double delay_penalty = 0.0,
+                                int input_dtype = FRNNT_F32);
 
 // lm_grad / am_grad without the one-hot terms, from the gradient weights rw [B][S+1][Tp] and
 // the maxima of |rw| per row (see simple_pairs_rowmax_offset)

@@ -133,8 +133,7 @@ pair_umma256_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_co
                 tma_load_3d(sbw + (2 + j) * kPairOpBytes, &map_blo, k0, t.n0 + 128 * j, zc, &bar_full[s]);
               }
             }
-            continue;
-          }
+          } else {
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             const uint32_t sa = st + (uint32_t)h * 2 * kPairOpBytes;
@@ -160,6 +159,7 @@ pair_umma256_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_co
           } else {
             tma_load_3d(sb, &map_bhi, k0, t.n0, zc, &bar_full[s]);
             tma_load_3d(sb + kPairOpBytes, &map_blo, k0, t.n0, zc, &bar_full[s]);
+          }
           }
         }
       }

@@ -4,7 +4,15 @@ fast_rnnt/python/fast_rnnt/rnnt_loss.py of the reference.
 Every public function keeps the reference's name, arguments, defaults and
 return values; the work runs in libfrnnt_sm100.so through autograd Functions
 (one fused forward and one analytic backward per function instead of the
-reference's chains of ATen ops).  CUDA tensors of float32 / float64 only.
+reference's chains of ATen ops).  CUDA tensors of float32 / float64, as in the reference.
+
+float16 / bfloat16 inputs (no counterpart in the reference, which dispatches float and
+double only) are accepted with this definition: the result is that of the float32 call on
+the inputs converted to float32 (an exact conversion) -- lattices and losses are float32,
+bit-identical; gradients arrive as float32 and autograd rounds them to the input's type.
+The two kernels that read the large inputs of the pruned pipeline read 16-bit values
+directly (lm / am of the simple losses when the am-only branch is off, enc / dec of the
+fused joiner); everywhere else the inputs are converted first.
 """
 from typing import Optional, Tuple, Union
 
@@ -61,12 +69,13 @@ class _SimpleLogprobs(torch.autograd.Function):
     def forward(ctx, lm, am, symbols, boundary, blank, rnnt_type, smoothed, ls, as_, delay_penalty=0.0):
         B, T, C = am.shape
         S = lm.shape[1] - 1
-        dev, dt = lm.device, _lib.dtype_code(lm.dtype)
+        dev, dt = lm.device, _lib.input_code(lm.dtype)   # 16-bit lm / am: float32 everywhere else
+        out_dtype = torch.float32 if _lib.is_16bit(lm) else lm.dtype
         T1 = T + 1 if rnnt_type == 0 else T
         lm, am, symbols, boundary = _contig(lm), _contig(am), _contig(symbols), _contig(boundary)
         with torch.cuda.device(dev):
-            px = torch.empty(B, S, T1, dtype=lm.dtype, device=dev)
-            py = torch.empty(B, S + 1, T, dtype=lm.dtype, device=dev)
+            px = torch.empty(B, S, T1, dtype=out_dtype, device=dev)
+            py = torch.empty(B, S + 1, T, dtype=out_dtype, device=dev)
             saved = _bytes(_lib.lib().frnnt_simple_saved_bytes(dt, B, S, T, C), dev)
             scratch = _bytes(_lib.lib().frnnt_simple_scratch_bytes(dt, B, S, T, C), dev)
             _lib.call("frnnt_simple_logprobs_forward", _c_int(dt), _lib.ptr(lm), _lib.ptr(am),
@@ -83,15 +92,16 @@ class _SimpleLogprobs(torch.autograd.Function):
         blank, rnnt_type, smoothed, ls, as_ = ctx.cfg
         B, T, C = am.shape
         S = lm.shape[1] - 1
-        dev, dt = lm.device, _lib.dtype_code(lm.dtype)
+        dev, dt = lm.device, _lib.input_code(lm.dtype)
+        out_dtype = torch.float32 if _lib.is_16bit(lm) else lm.dtype
         T1 = T + 1 if rnnt_type == 0 else T
         with torch.cuda.device(dev):
-            g_px = (torch.zeros(B, S, T1, dtype=lm.dtype, device=dev) if g_px is None
+            g_px = (torch.zeros(B, S, T1, dtype=out_dtype, device=dev) if g_px is None
                     else g_px.contiguous())
-            g_py = (torch.zeros(B, S + 1, T, dtype=lm.dtype, device=dev) if g_py is None
+            g_py = (torch.zeros(B, S + 1, T, dtype=out_dtype, device=dev) if g_py is None
                     else g_py.contiguous())
-            lm_grad = torch.empty_like(lm)
-            am_grad = torch.empty_like(am)
+            lm_grad = torch.empty(lm.shape, dtype=out_dtype, device=dev)   # autograd casts it
+            am_grad = torch.empty(am.shape, dtype=out_dtype, device=dev)
             scratch = _bytes(_lib.lib().frnnt_simple_scratch_bytes(dt, B, S, T, C), dev)
             _lib.call("frnnt_simple_logprobs_backward", _c_int(dt), _lib.ptr(lm), _lib.ptr(am),
                       _lib.ptr(symbols), _lib.ptr(boundary), blank, rnnt_type, smoothed,
@@ -113,6 +123,9 @@ def _simple_logprobs(lm, am, symbols, termination_symbol, rnnt_type, boundary, s
     assert lm.dtype == am.dtype
     validate_st_lengths(S, T, rnnt_type == "regular", boundary)
     assert rnnt_type in ["regular", "modified", "constrained"], rnnt_type
+    if _lib.is_16bit(lm) and not _lib.lib().frnnt_simple_reads_16bit_inputs(
+            S, T, C, _RNNT_TYPES[rnnt_type], int(smoothed), _c_f64(float(am_only_scale))):
+        lm, am = lm.float(), am.float()   # the am-only branch and the SIMT paths read float32
     return _SimpleLogprobs.apply(lm, am, symbols, boundary, int(termination_symbol),
                                  _RNNT_TYPES[rnnt_type], smoothed, float(lm_only_scale),
                                  float(am_only_scale), float(delay_penalty))
@@ -193,6 +206,8 @@ def _logprobs_joint(logits, symbols, termination_symbol, boundary, rnnt_type, de
     """get_rnnt_logprobs_joint with the delay penalty of the loss functions added to px by
     the kernel that writes the lattices."""
     assert logits.ndim == 4, logits.ndim
+    if _lib.is_16bit(logits):
+        logits = logits.float()
     (B, T, S1, C) = logits.shape
     S = S1 - 1
     assert symbols.shape == (B, S), symbols.shape
@@ -212,6 +227,8 @@ def get_rnnt_logprobs_pruned(logits: Tensor, symbols: Tensor, ranges: Tensor,
 
 def _logprobs_pruned(logits, symbols, ranges, termination_symbol, boundary, rnnt_type, delay_penalty):
     assert logits.ndim == 4, logits.ndim
+    if _lib.is_16bit(logits):
+        logits = logits.float()
     (B, T, s_range, C) = logits.shape
     assert ranges.shape == (B, T, s_range), f"{ranges.shape} == ({B}, {T}, {s_range})"
     (B, S) = symbols.shape
@@ -242,7 +259,8 @@ class _PrunedJoinerLogprobs(torch.autograd.Function):
             py = torch.empty(B, S + 1, T, dtype=torch.float32, device=dev)
             saved = _bytes(lib.frnnt_pruned_joiner_saved_bytes(B, T, R, S, C, D), dev)
             scratch = _bytes(lib.frnnt_pruned_joiner_forward_scratch_bytes(B, T, R, S, C, D), dev)
-            _lib.call("frnnt_pruned_joiner_logprobs_forward", _lib.ptr(enc), _lib.ptr(dec),
+            _lib.call("frnnt_pruned_joiner_logprobs_forward", _c_int(_lib.input_code(enc.dtype)),
+                      _lib.ptr(enc), _lib.ptr(dec),
                       _lib.ptr(ranges), _lib.ptr(weight), _lib.ptr(bias), _lib.ptr(symbols),
                       _lib.ptr(boundary), _lib.ptr(px), _lib.ptr(py), _lib.ptr(saved),
                       _lib.ptr(scratch), B, T, R, S, C, D, blank, rnnt_type, _c_f64(delay_penalty),
@@ -309,7 +327,12 @@ def _logprobs_pruned_joiner(am, lm, ranges, joiner_weight, joiner_bias, symbols,
     S = S1 - 1
     assert symbols.shape == (B, S), symbols.shape
     assert joiner_weight.ndim == 2 and joiner_weight.shape[1] == D, joiner_weight.shape
-    assert am.dtype == torch.float32 and lm.dtype == torch.float32
+    assert am.dtype == lm.dtype and am.dtype in (torch.float32, torch.float16, torch.bfloat16), \
+        (am.dtype, lm.dtype)
+    if _lib.is_16bit(joiner_weight):
+        joiner_weight = joiner_weight.float()
+    if _lib.is_16bit(joiner_bias):
+        joiner_bias = joiner_bias.float()
     assert joiner_weight.dtype == torch.float32
     validate_st_lengths(S, T, rnnt_type == "regular", boundary)
     assert rnnt_type in ["regular", "modified", "constrained"], rnnt_type

@@ -44,6 +44,12 @@ extern "C" {
 
 #define FRNNT_F32 0
 #define FRNNT_F64 1
+/* 16-bit INPUTS (IEEE half, bfloat16), accepted where a function says so: the named inputs
+ * are read as 16-bit values and converted (exactly) to float32 on load; lattices, saved
+ * state, gradients and every other argument are float32, and the results are those of the
+ * FRNNT_F32 call on the converted inputs, bit for bit. */
+#define FRNNT_F16 2
+#define FRNNT_BF16 3
 
 #define FRNNT_OK 0
 #define FRNNT_EINVAL (-1)      /* null pointer, bad dtype, negative size, misalignment */
@@ -180,6 +186,14 @@ size_t frnnt_simple_scratch_bytes(int dtype, int B, int S, int T, int C);
  * (rnnt_loss.py:309-324, :516-531, :1101-1116, :1463-1478; T_b = boundary[b][3], or T),
  * with torch's roundings; 0 for the plain get_rnnt_logprobs* functions.  The same argument
  * of frnnt_lsm_gather_forward and frnnt_pruned_joiner_logprobs_forward means the same. */
+/* 1 if frnnt_simple_logprobs_forward / _backward accept dtype FRNNT_F16 / FRNNT_BF16 (16-bit lm
+ * and am, everything else float32) for these sizes: the float32 tensor-core path must apply
+ * (C a multiple of 4, ...) and the am-only branch must be off (not smoothed, or
+ * am_only_scale == 0), because only that path reads lm and am in a single kernel.  Otherwise
+ * convert the inputs to float32 first (same results). */
+int frnnt_simple_reads_16bit_inputs(int S, int T, int C, int rnnt_type, int smoothed,
+                                    double am_only_scale);
+
 int frnnt_simple_logprobs_forward(int dtype, const void *lm, const void *am,
                                   const int64_t *symbols, const int64_t *boundary, int blank,
                                   int rnnt_type, int smoothed, double lm_only_scale,
@@ -312,13 +326,16 @@ int frnnt_joiner_input_grads(const float *gz, const int64_t *ranges, float *enc_
  * planes (x * 2^e = hi + lo, 22 significant bits, e chosen per operand from its largest
  * magnitude): fp32-level accuracy at the fp16 rate.  The log-sum-exp over C comes out of
  * the forward product's epilogue.
+ * input_dtype is FRNNT_F32, or FRNNT_F16 / FRNNT_BF16 for 16-bit enc and dec (the
+ * gradients enc_grad / dec_grad of the backward call stay float32).
  * `saved` (frnnt_pruned_joiner_saved_bytes) must stay untouched until the backward call;
  * `scratch` is per-call (…_forward_scratch_bytes / …_backward_scratch_bytes); both
  * 256-byte aligned. */
 size_t frnnt_pruned_joiner_saved_bytes(int B, int T, int R, int S, int C, int D);
 size_t frnnt_pruned_joiner_forward_scratch_bytes(int B, int T, int R, int S, int C, int D);
 size_t frnnt_pruned_joiner_backward_scratch_bytes(int B, int T, int R, int S, int C, int D);
-int frnnt_pruned_joiner_logprobs_forward(const float *enc, const float *dec, const int64_t *ranges,
+int frnnt_pruned_joiner_logprobs_forward(int input_dtype, const void *enc, const void *dec,
+                                         const int64_t *ranges,
                                          const float *weight, const float *bias,
                                          const int64_t *symbols, const int64_t *boundary, float *px,
                                          float *py, void *saved, void *scratch, int B, int T, int R,
