@@ -565,6 +565,9 @@ def main():
                          "the pruned branch's instead of overlapping with it)")
     ap.add_argument("--no-graph", action="store_true",
                     help="enqueue every step eagerly instead of replaying a CUDA graph of it")
+    ap.add_argument("--input-dtype", default="f32", choices=["f32", "bf16", "f16"],
+                    help="f32: the benchmark.  bf16 / f16: the same step on 16-bit am / lm / enc / dec "
+                         "(float32 arithmetic); reported with that label, stages and CPU legs skipped")
     ap.add_argument("--no-stages", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -639,6 +642,12 @@ def main():
         del full
     else:
         wl = workloads.pipeline_workload(args.workload, batch=batch, seed=rank)
+    if args.input_dtype != "f32":
+        # NOT the benchmark's configuration (the reference takes float32): am / lm / enc / dec as
+        # 16-bit tensors, read by the kernels directly, all arithmetic still float32
+        half = torch.bfloat16 if args.input_dtype == "bf16" else torch.float16
+        for k in ("am", "lm", "enc", "dec"):
+            wl[k] = wl[k].to(half)
     host = {k: wl[k].pin_memory() for k in TENSOR_KEYS}
     resident = {k: v.to(dev) for k, v in host.items()}
     inner = make_step(fr, wl, args.joiner, overlap=not args.no_overlap)
@@ -795,7 +804,10 @@ def main():
     line = {"metric": "utterances/sec", "value": round(value, 1), "unit": "utt/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": cfg,
+            "vs_baseline": None,
+            "dtype": ("f32" if args.input_dtype == "f32" else
+                      f"f32 arithmetic on {args.input_dtype} inputs (not the benchmark's configuration)"),
+            "data": "synthetic", "config": cfg,
             "joiner_impl": joiner_impl[args.joiner],
             "streams": ("one" if args.no_overlap else
                         "two: the simple loss (forward, hence its backward) on a second stream, "
@@ -822,6 +834,8 @@ def main():
                                       "number at every count of ranks"}
         assert rel < 1e-5, line["loss_check"]
 
+    if args.input_dtype != "f32":
+        args.no_stages = args.no_cpu_baseline = True
     if rank == 0 and not args.no_stages:
         stages, cells = stage_table(fr, wl, dev, flush, hbm_gbs)
         in_step = STEP_STAGES[args.joiner]
