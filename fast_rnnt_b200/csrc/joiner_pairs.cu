@@ -48,12 +48,9 @@ static inline size_t up256(size_t x) { return (x + 255) & ~(size_t)255; }
 // tanh' activations (forward product 0.254 -> 0.260 ms, grad-input 0.28 -> 0.39 ms with 128 x 256),
 // so only the former use it.  FRNNT_PAIR_TILE=128 forces the 128 x 128 kernel everywhere.
 static int pair_tile_m(int M, bool light_epilogue) {
-  static int forced = -1;
-  if (forced < 0) {
-    const char *e = getenv("FRNNT_PAIR_TILE");
-    forced = (e != nullptr && atoi(e) == 128) ? 128 : 0;
-  }
-  return (forced == 128 || !light_epilogue || M <= kPairTile) ? kPairTile : kP2TileM;
+  const char *e = getenv("FRNNT_PAIR_TILE");  // read at every call: tests switch it
+  const bool forced = e != nullptr && atoi(e) == 128;
+  return (forced || !light_epilogue || M <= kPairTile) ? kPairTile : kP2TileM;
 }
 
 template <bool A_MN, bool B_MN, class Ext>
