@@ -415,6 +415,109 @@ joiner_input_grads_kernel(const float *__restrict__ gz, const int64_t *__restric
   }
 }
 
+// The same pass with the window in REGISTERS instead of shared memory, for ranges whose R rows
+// per frame are consecutive and whose first row never moves back (what get_rnnt_prune_ranges
+// writes): acc[i] holds the partial sum of lattice row base + i; when the frame's first row has
+// moved on, the rows left behind are complete for this chunk and leave for the scratch (or,
+// beyond kJgWindow rows per chunk, for dec_grad by atomicAdd, as in the kernel above).  No
+// shared-memory traffic for the window, no barrier per chunk: 0.116 -> 0.096 ms at B=64, T=500,
+// R=5, D=512.  A chunk whose ranges are not of that form adds every row to dec_grad with
+// atomicAdd.
+template <bool WITH_ENC, int R>
+__global__ void __maxnreg__(88)
+joiner_input_grads_ring_kernel(const float *__restrict__ gz, const int64_t *__restrict__ ranges,
+                               float *__restrict__ enc_grad, float *__restrict__ dec_grad,
+                               float *__restrict__ partial, int *__restrict__ window, int T, int S1, int D) {
+  __shared__ int s0_sh[kJgFrames];
+  const int b = blockIdx.y, ch = blockIdx.x, nch = gridDim.x;
+  const int t0 = ch * kJgFrames, t1 = min(T, t0 + kJgFrames), nt = t1 - t0;
+  const int dvec = D / 4;
+  const int64_t *rg = ranges + ((size_t)b * T + t0) * R;
+  // is this chunk of the regular form?  (one entry per thread; nt * R <= 128)
+  bool ok = true;
+  for (int e = threadIdx.x; e < nt * R; e += kJgThreads) {
+    const int t = e / R, k = e - t * R;
+    const long long first = rg[(size_t)t * R], s = rg[e];
+    ok = ok && s == first + k && first >= 0 && first + R <= S1;
+    if (k == 0) {
+      s0_sh[t] = (int)first;
+      if (t > 0) {
+        const long long step = first - rg[(size_t)(t - 1) * R];
+        ok = ok && step >= 0 && step <= kJgWindow;
+      }
+    }
+  }
+  const bool regular = __syncthreads_and(ok);
+  const int s_lo = regular ? s0_sh[0] : 0;
+  if (threadIdx.x == 0) {
+    window[((size_t)b * nch + ch) * 2] = s_lo;
+    window[((size_t)b * nch + ch) * 2 + 1] = regular ? min(kJgWindow, s0_sh[nt - 1] + R - s_lo) : 0;
+  }
+  const float4 *G = reinterpret_cast<const float4 *>(gz) + ((size_t)b * T + t0) * R * dvec;
+  float4 *E = WITH_ENC ? reinterpret_cast<float4 *>(enc_grad) + ((size_t)b * T + t0) * dvec : nullptr;
+  float4 *P = reinterpret_cast<float4 *>(partial) + ((size_t)b * nch + ch) * kJgWindow * dvec;
+  auto add4 = [](float4 &a, const float4 &x) { a.x += x.x, a.y += x.y, a.z += x.z, a.w += x.w; };
+  auto to_dec = [&](long long s, int v, const float4 &x) {
+    if (s < 0 || s >= S1) return;
+    float *dst = dec_grad + ((size_t)b * S1 + s) * D + 4 * v;
+    atomicAdd(dst, x.x), atomicAdd(dst + 1, x.y), atomicAdd(dst + 2, x.z), atomicAdd(dst + 3, x.w);
+  };
+  for (int v = threadIdx.x; v < dvec; v += kJgThreads) {
+    if (!regular) {
+      for (int t = 0; t < nt; ++t) {
+        float4 e = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int k = 0; k < R; ++k) {
+          const float4 x = G[((size_t)t * R + k) * dvec + v];
+          add4(e, x);
+          to_dec(rg[(size_t)t * R + k], v, x);
+        }
+        if (WITH_ENC) E[(size_t)t * dvec + v] = e;
+      }
+      continue;
+    }
+    float4 acc[R];
+#pragma unroll
+    for (int i = 0; i < R; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    int base = s_lo;  // lattice row of acc[0]
+    // the row that leaves the ring: complete for this chunk
+    auto retire = [&](const float4 &a) {
+      const int sl = base - s_lo;
+      if (sl < kJgWindow) P[(size_t)sl * dvec + v] = a;
+      else to_dec(base, v, a);
+      ++base;
+    };
+    constexpr int F = R <= 5 ? 2 : 1;  // frames per round: their F * R row loads are in flight together
+    for (int t = 0; t < nt; t += F) {
+      const bool two = F == 2 && t + 1 < nt;
+      float4 x[F][R];
+#pragma unroll
+      for (int k = 0; k < R; ++k) {
+        x[0][k] = G[((size_t)t * R + k) * dvec + v];
+        if (F == 2 && two) x[F - 1][k] = G[((size_t)(t + 1) * R + k) * dvec + v];
+      }
+#pragma unroll
+      for (int f = 0; f < F; ++f) {
+        if (f == 1 && !two) break;
+        for (int d = s0_sh[t + f] - base; d > 0; --d) {  // the same for the whole CTA
+          retire(acc[0]);
+#pragma unroll
+          for (int i = 0; i + 1 < R; ++i) acc[i] = acc[i + 1];
+          acc[R - 1] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        float4 e = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int k = 0; k < R; ++k) {
+          add4(e, x[f][k]);
+          add4(acc[k], x[f][k]);
+        }
+        if (WITH_ENC) E[(size_t)(t + f) * dvec + v] = e;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < R; ++i) retire(acc[i]);
+  }
+}
+
 // dec_grad[b][s][:] += the chunks' partial rows for s, in chunk order.  Each warp first finds
 // the chunks whose window holds s (lane <-> chunk, one ballot per 32 chunks), then fetches their
 // rows four at a time, so that the loads of a round are in flight together.
@@ -651,7 +754,25 @@ extern "C" int frnnt_joiner_input_grads(const float *gz, const int64_t *ranges, 
   float *partial = (float *)scratch;
   int *window = (int *)(partial + (size_t)B * nch * kJgWindow * D);
   const size_t smem = (size_t)kJgWindow * D * sizeof(float);
-  if (enc_grad != nullptr) {
+  if (R <= 8) {  // the window in registers; wider bands keep it in shared memory
+    const dim3 grid((unsigned)nch, (unsigned)B);
+#define FRNNT_JG_RING(RR)                                                                                         \
+  case RR:                                                                                                        \
+    if (enc_grad != nullptr)                                                                                      \
+      FRNNT_KERNEL(joiner_input_grads_ring_kernel<true, RR><<<grid, kJgThreads, 0, st>>>(gz, ranges, enc_grad,     \
+                                                                                       dec_grad, partial, window, \
+                                                                                       T, S1, D));                \
+    else                                                                                                          \
+      FRNNT_KERNEL(joiner_input_grads_ring_kernel<false, RR><<<grid, kJgThreads, 0, st>>>(gz, ranges, nullptr,     \
+                                                                                        dec_grad, partial, window,\
+                                                                                        T, S1, D));               \
+    break;
+    switch (R) {
+      FRNNT_JG_RING(1) FRNNT_JG_RING(2) FRNNT_JG_RING(3) FRNNT_JG_RING(4)
+      FRNNT_JG_RING(5) FRNNT_JG_RING(6) FRNNT_JG_RING(7) FRNNT_JG_RING(8)
+    }
+#undef FRNNT_JG_RING
+  } else if (enc_grad != nullptr) {
     FRNNT_CUDA(cudaFuncSetAttribute(joiner_input_grads_kernel<true>,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     FRNNT_KERNEL(joiner_input_grads_kernel<true><<<dim3((unsigned)nch, (unsigned)B), kJgThreads, smem, st>>>(
