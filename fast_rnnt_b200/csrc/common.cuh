@@ -65,6 +65,15 @@ __device__ __forceinline__ float4 in_load4(const __nv_bfloat16 *row, int v) {
 }
 inline bool is_half_input(int dtype) { return dtype == FRNNT_F16 || dtype == FRNNT_BF16; }
 
+// row / d and row % d for a row index that is 64 bits wide for safety but nearly always fits
+// 32: the 32-bit division is an order of magnitude fewer instructions than the 64-bit one
+__device__ __forceinline__ long long div_rows(long long row, int d) {
+  return (unsigned long long)row <= 0xffffffffull ? (long long)((unsigned)row / (unsigned)d) : row / d;
+}
+__device__ __forceinline__ int mod_rows(long long row, int d) {
+  return (unsigned long long)row <= 0xffffffffull ? (int)((unsigned)row % (unsigned)d) : (int)(row % d);
+}
+
 // ---- device: math in the reference's operation order ------------------------
 template <typename real> __device__ __forceinline__ real neg_inf();
 template <> __device__ __forceinline__ float neg_inf<float>() { return -INFINITY; }

@@ -234,7 +234,7 @@ pruned_tanh_pairs_kernel(const TIn *__restrict__ enc, const TIn *__restrict__ de
   const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
   const int d8 = D / 8;
   for (long long row = warp0; row < rows; row += nwarps) {
-    const long long b = row / TR, bt = row / R;
+    const long long b = div_rows(row, TR), bt = div_rows(row, R);
     long long s = ranges[row];
     s = s < 0 ? 0 : (s >= S1 ? S1 - 1 : s);
     const TIn *e = enc + (size_t)bt * D;
@@ -411,8 +411,8 @@ joiner_band_kernel(const float *__restrict__ logits, const float2 *__restrict__ 
     sum += q.y * __expf(base - m0);
   }
   const float l = logf(sum) + m0;
-  const long long bt = row / R;
-  const int k = (int)(row % R), b = (int)(bt / T);
+  const long long bt = div_rows(row, R);
+  const int k = mod_rows(row, R), b = (int)div_rows(bt, T);
   const int y = band_symbol(symbols, ranges, b, (size_t)row, k, S, blank, C);
   const float *x = logits + (size_t)row * C;
   lse[row] = l;
@@ -435,9 +435,9 @@ band_grad_kernel(const float *__restrict__ g_px, const float *__restrict__ g_py,
   const int T1 = (rnnt_type == FRNNT_REGULAR) ? T + 1 : T;
   float mx = 0.f;
   for (long long row = (long long)blockIdx.x * 256 + threadIdx.x; row < rows; row += (long long)gridDim.x * 256) {
-    const long long bt = row / R;
-    const int k = (int)(row % R);
-    const int b = (int)(bt / T), t = (int)(bt % T);
+    const long long bt = div_rows(row, R);
+    const int k = mod_rows(row, R);
+    const int b = (int)div_rows(bt, T), t = mod_rows(bt, T);
     const int s = band_row(ranges, (size_t)bt, R, k, S1);
     float gx = 0.f, gy = g_py[((size_t)b * S1 + s) * T + t];
     const bool masked = rnnt_type == FRNNT_REGULAR && boundary != nullptr &&

@@ -132,9 +132,9 @@ lsm_rows_forward_kernel(const real *__restrict__ logits, const int64_t *__restri
     sum = group_reduce<real, GROUP>(sum, false, scratch, gid, lig);
     if (valid && lig == 0) {
       const real l = log_r(sum) + m0;
-      const long long bt = row / R;
-      const int k = (int)(row % R);
-      const int b = (int)(bt / T);
+      const long long bt = div_rows(row, R);
+      const int k = mod_rows(row, R);
+      const int b = (int)div_rows(bt, T);
       const int y = band_symbol(symbols, ranges, b, (size_t)row, k, S, blank, C);
       const real *x = logits + row * (long long)C;
       lse[row] = l;
@@ -160,9 +160,9 @@ lsm_rows_backward_kernel(const real *__restrict__ logits, const int64_t *__restr
   const long long warp0 = ((long long)blockIdx.x * kRowCta + threadIdx.x) >> 5;
   const long long nwarps = ((long long)gridDim.x * kRowCta) >> 5;
   for (long long row = warp0; row < rows; row += nwarps) {
-    const long long bt = row / R;
-    const int k = (int)(row % R);
-    const int b = (int)(bt / T), t = (int)(bt % T);
+    const long long bt = div_rows(row, R);
+    const int k = mod_rows(row, R);
+    const int b = (int)div_rows(bt, T), t = mod_rows(bt, T);
     const int s = band_row(ranges, (size_t)bt, R, k, S1);
     real gx = 0, gy = 0;
     {

@@ -156,7 +156,7 @@ __global__ void prune_gather_kernel(const vec *__restrict__ lm, const int64_t *_
   const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
   for (long long row = warp0; row < rows; row += nwarps) {
-    const long long b = row / TR;
+    const long long b = div_rows(row, TR);
     long long s = ranges[row];
     s = s < 0 ? 0 : (s >= S1 ? S1 - 1 : s);  // never read outside lm
     const vec *src = lm + ((size_t)b * S1 + s) * dvec;
@@ -250,7 +250,7 @@ __global__ void pruned_tanh_kernel(const real *__restrict__ enc, const real *__r
   const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
   const int dvec = D / VW;
   for (long long row = warp0; row < rows; row += nwarps) {
-    const long long b = row / TR, bt = row / R;
+    const long long b = div_rows(row, TR), bt = div_rows(row, R);
     long long s = ranges[row];
     s = s < 0 ? 0 : (s >= S1 ? S1 - 1 : s);
     const vec *e = reinterpret_cast<const vec *>(enc + (size_t)bt * D);

@@ -127,7 +127,7 @@ exp_planes_kernel(const TIn *__restrict__ lm, const TIn *__restrict__ am,
       // am[t][symbol of every lattice row]: gathered here, where the row has just been read
       // (L1 hits), so that the product's epilogue reads them as whole 128-byte lines
       const TIn *x = am + r * C;
-      const int64_t *sy = symbols + (size_t)(r / T) * S;
+      const int64_t *sy = symbols + (size_t)div_rows(r, T) * S;
       float *dst = am_sym + (size_t)r * Sp;
       for (int s = lane; s < Sp; s += 32) {
         float v = 0.f;
@@ -142,7 +142,7 @@ exp_planes_kernel(const TIn *__restrict__ lm, const TIn *__restrict__ am,
     if (lane == 0) {
       const TIn *x = (is_lm ? lm : am) + r * C;
       if (is_lm) {
-        const int b = (int)(r / S1), s = (int)(r % S1);
+        const int b = (int)div_rows(r, S1), s = mod_rows(r, S1);
         lmmax[r] = m;
         lmsum[r] = sum;
         lnorm[r] = logf(sum) + m;
