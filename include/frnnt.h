@@ -10,6 +10,10 @@
  *     documented as a host pointer; tensors are contiguous and row-major;
  *   - `dtype` is FRNNT_F32 or FRNNT_F64 (the reference dispatches over float
  *     and double only, fast_rnnt/csrc/mutual_information_cuda.cu:715, :788);
+ *     two forwards also read their large inputs as FRNNT_F16 / FRNNT_BF16 (see there);
+ *   - three environment variables, read at call time, select an alternative kernel for
+ *     the same result: FRNNT_CONTRACTION=tf32|simt, FRNNT_MI=row_per_thread,
+ *     FRNNT_PAIR_TILE=128;
  *   - symbols, boundaries and ranges are int64, as in the reference's API;
  *   - `stream` is a cudaStream_t passed as void*; work is enqueued on it and
  *     nothing synchronises;
